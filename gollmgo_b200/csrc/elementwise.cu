@@ -1,0 +1,126 @@
+// Embedding gather, residual-add + RMSNorm, SiLU(gate)*up.
+//
+// The residual stream is float32 everywhere (the reference keeps it so:
+// kernels/gollmgo_model.cu:46-61); the activations that feed matrix products
+// are TA = float (true 32-bit path) or bfloat16 (serving path).
+#include "common.cuh"
+
+// ---------------------------------------------------------------- embedding
+// out[t, :] = float(table[ids[t], :])   (reference: kernels/gollmgo_ops.cu:538-552,
+// which leaves the row stale for an id out of range; here the row is zeroed and
+// *bad_id is set, and the host has already refused such ids.)
+template <typename TW>
+__global__ void embed_gather_kernel(const int* __restrict__ ids, const TW* __restrict__ table,
+                                    float* __restrict__ out, int H, int V, int* bad_id) {
+  const int t = blockIdx.x;
+  const int id = ids[t];
+  float* o = out + (size_t)t * H;
+  if (id < 0 || id >= V) {
+    if (threadIdx.x == 0 && bad_id) atomicExch(bad_id, 1);
+    for (int i = threadIdx.x; i < H; i += blockDim.x) o[i] = 0.f;
+    return;
+  }
+  const TW* row = table + (size_t)id * H;
+  for (int i = threadIdx.x; i < H; i += blockDim.x) o[i] = to_f32(row[i]);
+}
+
+extern "C" int gg_embed_gather(const int* ids, const void* table, int table_dtype, float* out,
+                               int T, int H, int V, int* bad_id, cudaStream_t stream) {
+  GG_REQUIRE(T >= 0 && H > 0 && V > 0, "embed_gather: bad sizes T=%d H=%d V=%d", T, H, V);
+  if (T == 0) return GG_OK;
+  const int threads = H >= 1024 ? 256 : 128;
+  if (table_dtype == GG_F32)
+    embed_gather_kernel<float><<<T, threads, 0, stream>>>(ids, (const float*)table, out, H, V, bad_id);
+  else if (table_dtype == GG_BF16)
+    embed_gather_kernel<__nv_bfloat16><<<T, threads, 0, stream>>>(ids, (const __nv_bfloat16*)table, out, H, V, bad_id);
+  else
+    return gg_fail(GG_ERR_INVALID, "embed_gather: unknown dtype %d", table_dtype);
+  return gg_check_launch("embed_gather");
+}
+
+// ---------------------------------------------------------------- add + rmsnorm
+// x = resid[r, :] (+ delta[r, :]);  if write_back: resid[r, :] = x;
+// out[i, :] = TA( x * rsqrt(mean(x^2) + eps) * w )          r = rows ? rows[i] : i
+// Formula: kernels/gollmgo_ops.cu:593-629; the residual add it is fused with is
+// kernels/gollmgo_ops.cu:642-650.  Sum of squares, rsqrt and products in float32.
+template <typename TA>
+__global__ void add_rmsnorm_kernel(float* __restrict__ resid, const TA* __restrict__ delta,
+                                   const float* __restrict__ w, TA* __restrict__ out,
+                                   const int* __restrict__ rows, int H, float eps, int write_back) {
+  extern __shared__ float xs[];          // H floats + 33 for the reduction
+  float* red = xs + H;
+  const int i = blockIdx.x;
+  const int r = rows ? rows[i] : i;
+  float* xr = resid + (size_t)r * H;
+  const TA* dr = delta ? delta + (size_t)r * H : nullptr;
+  float ss = 0.f;
+  for (int c = threadIdx.x; c < H; c += blockDim.x) {
+    float x = xr[c];
+    if (dr) x += to_f32(dr[c]);
+    xs[c] = x;
+    if (write_back && dr) xr[c] = x;
+    ss += x * x;
+  }
+  const float total = block_sum(ss, red);
+  const float rinv = rsqrtf(total / (float)H + eps);
+  TA* o = out + (size_t)i * H;
+  for (int c = threadIdx.x; c < H; c += blockDim.x) o[c] = from_f32<TA>(xs[c] * rinv * w[c]);
+}
+
+template <typename TA>
+static int launch_add_rmsnorm(float* resid, const void* delta, const float* w, void* out,
+                              const int* rows, int n, int H, float eps, int write_back,
+                              cudaStream_t stream) {
+  const size_t smem = (size_t)(H + 33) * sizeof(float);
+  GG_REQUIRE(smem <= 227 * 1024, "add_rmsnorm: width %d needs %zu B of shared memory (max 232448)", H, smem);
+  if (smem > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(add_rmsnorm_kernel<TA>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return gg_fail(GG_ERR_CUDA, "add_rmsnorm: %s", cudaGetErrorString(e));
+  }
+  const int threads = H >= 2048 ? 512 : (H >= 512 ? 256 : 128);
+  add_rmsnorm_kernel<TA><<<n, threads, smem, stream>>>(resid, (const TA*)delta, w, (TA*)out, rows, H, eps, write_back);
+  return gg_check_launch("add_rmsnorm");
+}
+
+extern "C" int gg_add_rmsnorm(float* resid, const void* delta, const float* w, void* out,
+                              int act_dtype, const int* rows, int n, int H, float eps,
+                              int write_back, cudaStream_t stream) {
+  GG_REQUIRE(n >= 0 && H > 0 && eps > 0.f, "add_rmsnorm: bad sizes n=%d H=%d eps=%g", n, H, (double)eps);
+  if (n == 0) return GG_OK;
+  if (act_dtype == GG_F32) return launch_add_rmsnorm<float>(resid, delta, w, out, rows, n, H, eps, write_back, stream);
+  if (act_dtype == GG_BF16) return launch_add_rmsnorm<__nv_bfloat16>(resid, delta, w, out, rows, n, H, eps, write_back, stream);
+  return gg_fail(GG_ERR_INVALID, "add_rmsnorm: unknown dtype %d", act_dtype);
+}
+
+// ---------------------------------------------------------------- silu(gate) * up
+// in: [T, 2*I] with gate in columns [0, I) and up in [I, 2I); out: [T, I]
+// out = TA( g / (1 + exp(-g)) * u )     (kernels/gollmgo_ops.cu:361-374)
+template <typename TA>
+__global__ void silu_mul_kernel(const TA* __restrict__ in, TA* __restrict__ out, int T, int I) {
+  const size_t n = (size_t)T * I;
+  for (size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x; e < n;
+       e += (size_t)gridDim.x * blockDim.x) {
+    const size_t t = e / I;
+    const int c = (int)(e - t * I);
+    const float g = to_f32(in[t * 2 * I + c]);
+    const float u = to_f32(in[t * 2 * I + I + c]);
+    out[e] = from_f32<TA>(g / (1.f + expf(-g)) * u);
+  }
+}
+
+extern "C" int gg_silu_mul(const void* in, void* out, int act_dtype, int T, int I,
+                           cudaStream_t stream) {
+  GG_REQUIRE(T >= 0 && I > 0, "silu_mul: bad sizes T=%d I=%d", T, I);
+  if (T == 0) return GG_OK;
+  const size_t n = (size_t)T * I;
+  const int threads = 256;
+  size_t blocks = (n + threads - 1) / threads;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  if (act_dtype == GG_F32)
+    silu_mul_kernel<float><<<(int)blocks, threads, 0, stream>>>((const float*)in, (float*)out, T, I);
+  else if (act_dtype == GG_BF16)
+    silu_mul_kernel<__nv_bfloat16><<<(int)blocks, threads, 0, stream>>>((const __nv_bfloat16*)in, (__nv_bfloat16*)out, T, I);
+  else
+    return gg_fail(GG_ERR_INVALID, "silu_mul: unknown dtype %d", act_dtype);
+  return gg_check_launch("silu_mul");
+}

@@ -1,0 +1,179 @@
+"""Python face of the CUDA library: one function per launcher, taking torch tensors.
+
+There is no CPU fallback and no other implementation behind these names: if the
+library cannot be built or loaded, importing a function's first use raises.  All
+launches go to torch's current CUDA stream, so they can be captured in a graph.
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Optional
+
+import torch
+
+from . import build
+
+F32, BF16 = 0, 1
+
+
+class KernelError(RuntimeError):
+    """A launcher refused its arguments or CUDA reported an error."""
+
+
+_LIB = None
+
+
+def lib():
+    global _LIB
+    if _LIB is None:
+        path = build.ensure_built()
+        try:
+            handle = ctypes.CDLL(path)
+        except OSError as e:
+            raise KernelError(f"cannot load the CUDA library {path}: {e}") from None
+        handle.gg_last_error.restype = ctypes.c_char_p
+        _LIB = handle
+    return _LIB
+
+
+def library_file() -> str:
+    lib()
+    return build.library_path()
+
+
+def _p(t: Optional[torch.Tensor]):
+    return ctypes.c_void_p(t.data_ptr()) if t is not None else ctypes.c_void_p(0)
+
+
+def _stream():
+    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _check(rc: int) -> None:
+    if rc != 0:
+        raise KernelError(lib().gg_last_error().decode())
+
+
+def dtype_code(dt: torch.dtype) -> int:
+    if dt == torch.float32:
+        return F32
+    if dt == torch.bfloat16:
+        return BF16
+    raise KernelError(f"kernels take float32 or bfloat16, not {dt}")
+
+
+def _cuda(*tensors):
+    for t in tensors:
+        if t is not None and (not t.is_cuda or not t.is_contiguous()):
+            raise KernelError("kernel arguments must be contiguous CUDA tensors")
+
+
+def device_capability() -> int:
+    return int(lib().gg_device_capability())
+
+
+def embed_gather(ids: torch.Tensor, table: torch.Tensor, out: torch.Tensor,
+                 bad_id: Optional[torch.Tensor] = None) -> None:
+    """out[t, :] = float32(table[ids[t], :]); ids int32 [T], out float32 [T, H]."""
+    _cuda(ids, table, out)
+    T, (V, H) = ids.numel(), table.shape
+    if out.dtype != torch.float32 or out.shape[-1] != H or ids.dtype != torch.int32:
+        raise KernelError("embed_gather: out must be float32 [T, H], ids int32")
+    _check(lib().gg_embed_gather(_p(ids), _p(table), dtype_code(table.dtype), _p(out),
+                                 T, H, V, _p(bad_id), _stream()))
+
+
+def add_rmsnorm(resid: torch.Tensor, delta: Optional[torch.Tensor], weight: torch.Tensor,
+                out: torch.Tensor, eps: float, rows: Optional[torch.Tensor] = None,
+                write_back: bool = True) -> None:
+    """x = resid[r] (+ delta[r]); resid[r] = x if write_back; out[i] = rmsnorm(x) * weight,
+    r = rows[i] if rows is given else i.  resid float32, weight float32, out/delta same dtype."""
+    _cuda(resid, delta, weight, out, rows)
+    H = resid.shape[-1]
+    n = rows.numel() if rows is not None else out.shape[0]
+    if resid.dtype != torch.float32 or weight.dtype != torch.float32 or weight.numel() != H:
+        raise KernelError("add_rmsnorm: residual and weight must be float32 of one width")
+    if delta is not None and delta.dtype != out.dtype:
+        raise KernelError("add_rmsnorm: delta and out differ in dtype")
+    _check(lib().gg_add_rmsnorm(_p(resid), _p(delta), _p(weight), _p(out), dtype_code(out.dtype),
+                                _p(rows), n, H, ctypes.c_float(eps), int(write_back), _stream()))
+
+
+def silu_mul(gate_up: torch.Tensor, out: torch.Tensor) -> None:
+    """out[t, i] = silu(gate_up[t, i]) * gate_up[t, I + i]."""
+    _cuda(gate_up, out)
+    T, I = out.shape
+    if gate_up.shape != (T, 2 * I) or gate_up.dtype != out.dtype:
+        raise KernelError("silu_mul: input must be [T, 2I] of the output's dtype")
+    _check(lib().gg_silu_mul(_p(gate_up), _p(out), dtype_code(out.dtype), T, I, _stream()))
+
+
+def rope_kv_write(qkv: torch.Tensor, positions: torch.Tensor, slot_mapping: Optional[torch.Tensor],
+                  inv_freq: Optional[torch.Tensor], kcache: Optional[torch.Tensor],
+                  vcache: Optional[torch.Tensor], nh: int, nkv: int, d: int, page_size: int,
+                  interleaved: bool = False, write_cache: bool = True) -> None:
+    """Rotate q and k heads of qkv [T, (nh+2nkv)*d] in place and scatter k, v into the
+    paged cache [pages, nkv, page_size, d] at slot_mapping[t]."""
+    _cuda(qkv, positions, slot_mapping, inv_freq, kcache, vcache)
+    T = qkv.shape[0]
+    if qkv.shape[1] != (nh + 2 * nkv) * d:
+        raise KernelError("rope_kv_write: qkv width is not (nh + 2 nkv) * d")
+    if inv_freq is not None and inv_freq.dtype != torch.float64:
+        raise KernelError("rope_kv_write: inverse frequencies must be float64")
+    if kcache is not None and kcache.dtype != qkv.dtype:
+        raise KernelError("rope_kv_write: cache and activations differ in dtype")
+    rot = 2 * inv_freq.numel() if inv_freq is not None else 0
+    _check(lib().gg_rope_kv_write(_p(qkv), dtype_code(qkv.dtype), _p(positions), _p(slot_mapping),
+                                  _p(inv_freq), _p(kcache), _p(vcache), T, nh, nkv, d, rot,
+                                  page_size, int(interleaved), int(write_cache), _stream()))
+
+
+def attn_prefill(q: torch.Tensor, q_stride: int, kcache: torch.Tensor, vcache: torch.Tensor,
+                 block_tables: torch.Tensor, bt_stride: int, cu_q_lens: torch.Tensor,
+                 context_lens: torch.Tensor, tile_seq: torch.Tensor, tile_q0: torch.Tensor,
+                 num_tiles: int, out: torch.Tensor, nh: int, nkv: int, d: int, page_size: int,
+                 window: int, scale: float) -> None:
+    """Causal attention of prompt portions over the paged cache (general kernel)."""
+    _check(lib().gg_attn_prefill(_p(q), ctypes.c_longlong(q_stride), _p(kcache), _p(vcache),
+                                 dtype_code(kcache.dtype), _p(block_tables), bt_stride,
+                                 _p(cu_q_lens), _p(context_lens), _p(tile_seq), _p(tile_q0),
+                                 num_tiles, _p(out), nh, nkv, d, page_size, window,
+                                 ctypes.c_float(scale), _stream()))
+
+
+def attn_decode(q: torch.Tensor, q_stride: int, kcache: torch.Tensor, vcache: torch.Tensor,
+                block_tables: torch.Tensor, bt_stride: int, cu_q_lens: torch.Tensor,
+                context_lens: torch.Tensor, dec_seqs: torch.Tensor, n_dec: int, num_splits: int,
+                part_o: torch.Tensor, part_ml: torch.Tensor, out: torch.Tensor, nh: int, nkv: int,
+                d: int, page_size: int, window: int, scale: float) -> None:
+    """Attention of single decoded tokens, split over the context and merged."""
+    if part_o.numel() < n_dec * nh * num_splits * d or part_ml.numel() < n_dec * nh * num_splits * 2:
+        raise KernelError("attn_decode: scratch too small")
+    _check(lib().gg_attn_decode(_p(q), ctypes.c_longlong(q_stride), _p(kcache), _p(vcache),
+                                dtype_code(kcache.dtype), _p(block_tables), bt_stride,
+                                _p(cu_q_lens), _p(context_lens), _p(dec_seqs), n_dec, num_splits,
+                                _p(part_o), _p(part_ml), _p(out), nh, nkv, d, page_size, window,
+                                ctypes.c_float(scale), _stream()))
+
+
+def argmax(logits: torch.Tensor, out: torch.Tensor) -> None:
+    """out[r] = first index of the maximum of logits[r, :] (float32 [R, V])."""
+    _cuda(logits, out)
+    R, V = logits.shape
+    if logits.dtype != torch.float32 or out.dtype != torch.int32:
+        raise KernelError("argmax: logits float32, out int32")
+    _check(lib().gg_argmax(_p(logits), R, V, _p(out), _stream()))
+
+
+def sample(logits: torch.Tensor, temperature: torch.Tensor, top_k: Optional[torch.Tensor],
+           top_p: Optional[torch.Tensor], seeds: torch.Tensor, draw_index: torch.Tensor,
+           out: torch.Tensor) -> None:
+    """Per row: greedy if temperature <= 1e-9, else top-k / top-p / seeded categorical."""
+    _cuda(logits, temperature, top_k, top_p, seeds, draw_index, out)
+    R, V = logits.shape
+    if logits.dtype != torch.float32 or out.dtype != torch.int32 or temperature.dtype != torch.float32:
+        raise KernelError("sample: logits/temperature float32, out int32")
+    if seeds.dtype != torch.int64 or draw_index.dtype != torch.int64:
+        raise KernelError("sample: seeds and draw indices must be int64")
+    _check(lib().gg_sample(_p(logits), R, V, _p(temperature), _p(top_k), _p(top_p), _p(seeds),
+                           _p(draw_index), _p(out), _stream()))

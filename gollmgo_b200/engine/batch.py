@@ -1,0 +1,216 @@
+"""One step's batch: flat token arrays plus per-sequence metadata, built on the
+host and sent to the device in one copy.
+
+The reference's Batch (internal/backend/runner.go:30-53) carries a per-token slot
+list for every sequence, rebuilt each step, and its CUDA bridge splits a mixed
+batch into a prompt call and a decode call (internal/backend/cuda/model_bridge.go:305-383).
+Here a batch is any mix of portions (one token or many) and runs as one forward
+pass; the device gets block tables, not per-token slot lists.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import List, Optional, Sequence
+
+import numpy as np
+import torch
+
+ATTN_TILE_ROWS = 16        # query rows of one attention tile (csrc/attention.cu: ATT_BQ)
+
+
+@dataclass
+class StepEntry:
+    """The next tokens of one request and the places among them whose logits are wanted."""
+    request_id: object
+    tokens: Sequence[int]
+    want: Sequence[int] = ()
+
+
+class StepBatch:
+    """Device views (int32 unless noted) and host facts of one step."""
+    num_tokens: int
+    num_seqs: int
+    num_logit_rows: int
+    num_tiles: int
+    num_decode: int
+    bt_stride: int
+    token_ids: torch.Tensor
+    positions: torch.Tensor
+    cu_q_lens: torch.Tensor
+    context_lens: torch.Tensor
+    state_slots: torch.Tensor
+    logit_rows: torch.Tensor
+    tile_seq: torch.Tensor
+    tile_q0: torch.Tensor
+    dec_seqs: torch.Tensor
+    slot_mapping: List[torch.Tensor]
+    block_tables: List[torch.Tensor]
+    # host side
+    request_ids: List[object]
+    q_lens: List[int]
+    q_starts: List[int]
+
+
+def _align(n: int) -> int:
+    return (n + 3) & ~3
+
+
+class BatchLayout:
+    """Offsets of every array in the packed int32 buffer, for given capacities."""
+
+    def __init__(self, T: int, B: int, R: int, NT: int, ND: int, G: int, stride: int):
+        self.T, self.B, self.R, self.NT, self.ND, self.G, self.stride = T, B, R, NT, ND, G, stride
+        off = 0
+
+        def take(n):
+            nonlocal off
+            o = off
+            off += _align(max(n, 1))
+            return o
+        self.token_ids = take(T)
+        self.positions = take(T)
+        self.slot_mapping = [take(T) for _ in range(G)]
+        self.cu_q_lens = take(B + 1)
+        self.context_lens = take(B)
+        self.state_slots = take(B)
+        self.logit_rows = take(R)
+        self.tile_seq = take(NT)
+        self.tile_q0 = take(NT)
+        self.dec_seqs = take(ND)
+        self.block_tables = [take(B * stride) for _ in range(G)]
+        self.size = off
+
+
+class BatchBuilder:
+    """Turns step entries into a StepBatch, reserving cache room on the way.
+
+    ``fixed_seqs`` and ``fixed_stride`` pin the layout (a captured decode step
+    replays with the same addresses): sequences are padded to ``fixed_seqs`` with
+    empty ones that no kernel touches.
+    """
+
+    def __init__(self, cache, device, capacity_ints: int = 1 << 16):
+        self.cache = cache
+        self.device = torch.device(device)
+        self.G = len(cache.groups)
+        self._host = None
+        self._dev = None
+        self._copied = None
+        self._ensure(capacity_ints)
+
+    def _ensure(self, n: int) -> None:
+        if self._host is not None and self._host.numel() >= n:
+            return
+        n = max(n, 1 << 12)
+        cuda = self.device.type == "cuda"
+        self._host = torch.empty(n, dtype=torch.int32, pin_memory=cuda)
+        self._dev = torch.empty(n, dtype=torch.int32, device=self.device)
+        self._copied = None
+
+    def build(self, entries: Sequence[StepEntry], fixed_seqs: Optional[int] = None,
+              fixed_stride: Optional[int] = None, static_dev: Optional[torch.Tensor] = None) -> StepBatch:
+        cache, ps, G = self.cache, self.cache.page_size, self.G
+        if not entries:
+            raise ValueError("a step needs at least one entry")
+        ids = [e.request_id for e in entries]
+        if len(set(ids)) != len(ids):
+            raise ValueError("a request appears twice in one step")
+        # all-or-nothing: check room for every entry before touching the cache
+        for e in entries:
+            if len(e.tokens) == 0:
+                raise ValueError(f"request {e.request_id!r}: a step entry needs at least one token")
+            for w in e.want:
+                if not (0 <= w < len(e.tokens)):
+                    raise ValueError(f"request {e.request_id!r}: wanted place {w} is outside its "
+                                     f"{len(e.tokens)} tokens")
+        appended = []
+        try:
+            for e in entries:
+                appended.append(cache.append(e.request_id, len(e.tokens)))
+        except Exception:
+            # undo: what was appended in this call is rolled back by truncation
+            for e, a in zip(entries, appended):
+                cache.rollback(e.request_id, a.start)
+            raise
+        B = len(entries)
+        q_lens = [len(e.tokens) for e in entries]
+        q_starts = [a.start for a in appended]
+        T = sum(q_lens)
+        tiles = [(b, q0) for b in range(B) if q_lens[b] > 1 for q0 in range(0, q_lens[b], ATTN_TILE_ROWS)]
+        dec = [b for b in range(B) if q_lens[b] == 1]
+        max_pages = max(len(cache.block_table(e.request_id, g)) for e in entries for g in range(G)) if G else 1
+        Bp = fixed_seqs if fixed_seqs is not None else B
+        if Bp < B:
+            raise ValueError("more sequences than the fixed layout holds")
+        stride = fixed_stride if fixed_stride is not None else max(1, max_pages)
+        if stride < max_pages:
+            raise ValueError(f"a sequence holds {max_pages} pages, the fixed block table has {stride}")
+        Tp = T + (Bp - B)            # padded sequences are given one dummy token each
+        rows, base = [], 0
+        for e, n in zip(entries, q_lens):
+            rows.extend(base + w for w in e.want)
+            base += n
+        rows.extend(range(T, Tp))    # ... whose logits are computed and ignored
+        R = len(rows)
+        lay = BatchLayout(Tp, Bp, R, len(tiles), len(dec) + (Bp - B), G, stride)
+        if static_dev is None:
+            self._ensure(lay.size)
+            if self._copied is not None:
+                self._copied.synchronize()
+        host = self._host if static_dev is None else torch.empty(lay.size, dtype=torch.int32,
+                                                                  pin_memory=self.device.type == "cuda")
+        h = host.numpy()
+        h[:lay.size] = 0
+        flat_tokens = np.fromiter((t for e in entries for t in e.tokens), dtype=np.int64, count=T)
+        h[lay.token_ids:lay.token_ids + T] = flat_tokens
+        pos = np.concatenate([np.arange(s, s + n, dtype=np.int32) for s, n in zip(q_starts, q_lens)])
+        h[lay.positions:lay.positions + T] = pos
+        for g in range(G):
+            sm = h[lay.slot_mapping[g]:lay.slot_mapping[g] + Tp]
+            sm[:] = -1
+            sm[:T] = np.fromiter((s for a in appended for s in a.slots[g]), dtype=np.int32, count=T)
+        cu = np.zeros(Bp + 1, dtype=np.int32)
+        cu[1:B + 1] = np.cumsum(q_lens)
+        cu[B + 1:] = T + np.arange(1, Bp - B + 1)
+        h[lay.cu_q_lens:lay.cu_q_lens + Bp + 1] = cu
+        h[lay.context_lens:lay.context_lens + B] = [s + n for s, n in zip(q_starts, q_lens)]
+        h[lay.state_slots:lay.state_slots + B] = [cache.state_slot(e.request_id) for e in entries]
+        h[lay.state_slots + B:lay.state_slots + Bp] = -1
+        h[lay.logit_rows:lay.logit_rows + R] = rows
+        if tiles:
+            h[lay.tile_seq:lay.tile_seq + len(tiles)] = [t[0] for t in tiles]
+            h[lay.tile_q0:lay.tile_q0 + len(tiles)] = [t[1] for t in tiles]
+        nd = len(dec) + (Bp - B)
+        h[lay.dec_seqs:lay.dec_seqs + len(dec)] = dec
+        h[lay.dec_seqs + len(dec):lay.dec_seqs + nd] = -1
+        for g in range(G):
+            bt = h[lay.block_tables[g]:lay.block_tables[g] + Bp * stride].reshape(Bp, stride)
+            bt[:] = -1
+            for b, e in enumerate(entries):
+                pages = cache.block_table(e.request_id, g)
+                bt[b, :len(pages)] = pages
+        dev = self._dev if static_dev is None else static_dev
+        if dev.numel() < lay.size:
+            raise ValueError("static batch buffer is too small for this layout")
+        if self.device.type == "cuda":
+            dev[:lay.size].copy_(host[:lay.size], non_blocking=True)
+            if static_dev is None:
+                self._copied = torch.cuda.Event()
+                self._copied.record()
+        else:
+            dev[:lay.size].copy_(host[:lay.size])
+
+        sb = StepBatch()
+        sb.num_tokens, sb.num_seqs, sb.num_logit_rows = Tp, Bp, R
+        sb.num_tiles, sb.num_decode, sb.bt_stride = len(tiles), nd, stride
+        v = lambda off, n: dev[off:off + max(n, 1)]
+        sb.token_ids, sb.positions = v(lay.token_ids, Tp), v(lay.positions, Tp)
+        sb.cu_q_lens, sb.context_lens = v(lay.cu_q_lens, Bp + 1), v(lay.context_lens, Bp)
+        sb.state_slots, sb.logit_rows = v(lay.state_slots, Bp), v(lay.logit_rows, R)[:R]
+        sb.tile_seq, sb.tile_q0 = v(lay.tile_seq, len(tiles)), v(lay.tile_q0, len(tiles))
+        sb.dec_seqs = v(lay.dec_seqs, nd)
+        sb.slot_mapping = [v(o, Tp) for o in lay.slot_mapping]
+        sb.block_tables = [v(o, Bp * stride) for o in lay.block_tables]
+        sb.request_ids, sb.q_lens, sb.q_starts = ids, q_lens, q_starts
+        sb.layout = lay
+        return sb

@@ -1,0 +1,188 @@
+"""The step function: run a batch of (request, its next tokens) through the model,
+from the cache, and return the logits at the wanted places.
+
+``ModelRunner`` owns the model, the cache manager and the batch builder.  A step
+runs only the tokens it is given, as one batch; what earlier steps left in the
+cache is what those tokens attend to.  Steps that hold one token per sequence
+can be captured in a CUDA graph per batch bucket and replayed: every size a
+kernel reads that changes between steps (context lengths, block tables, slots)
+lives in device memory.
+
+Reference: Runner.Step (internal/backend/runner.go:83-92) and
+CUDARunnerWithModel.Step (internal/backend/cuda/model_bridge.go:207-239); its
+decode graph is keyed by (batch, longest context) and re-captured as contexts
+grow (kernels/gollmgo_model.cu:1004-1054).
+"""
+from __future__ import annotations
+
+import os
+from typing import Dict, List, Optional, Sequence
+
+import torch
+
+from .. import architectures  # noqa: F401  (registers the architectures)
+from ..cache import CacheManager, PagedKVNeed
+from ..config import EngineConfig, read_config_json
+from ..csrc import ops
+from ..parts import BuildContext, build_model, set_matmul_precision
+from ..weights import checkpoint_source, random_source
+from .batch import BatchBuilder, BatchLayout, StepBatch, StepEntry
+
+_DTYPES = {"bfloat16": torch.bfloat16, "float32": torch.float32}
+GRAPH_BUCKETS = (1, 2, 4, 8, 16, 24, 32, 48, 64, 96, 128, 192, 256)
+
+
+class ModelRunner:
+    def __init__(self, config_dict: dict, engine_config: EngineConfig, weights=None,
+                 weights_seed: Optional[int] = None):
+        """``weights``: a model folder; or ``weights_seed``: random weights on the device."""
+        engine_config.validate()
+        if not torch.cuda.is_available():
+            raise RuntimeError("gollmgo_b200 runs on a CUDA device (sm_100a); none is visible")
+        self.ecfg = engine_config
+        self.device = torch.device("cuda", engine_config.device)
+        torch.cuda.set_device(self.device)
+        cap = ops.device_capability()          # loads (and if needed builds) the CUDA library
+        if cap < 100:
+            raise RuntimeError(f"the kernels are built for sm_100a; this device is sm_{cap}")
+        set_matmul_precision()
+        self.dtype = _DTYPES[engine_config.dtype]
+        max_tokens = engine_config.max_token_budget
+        ctx = BuildContext(self.dtype, self.device, max_tokens, engine_config.max_batch_size,
+                           engine_config.block_size)
+        self.ctx = ctx
+        self.config, self.spec, self.model = build_model(config_dict, ctx)
+        manifest = self.model.manifest()
+        if weights is not None:
+            get = checkpoint_source(weights, manifest, self.dtype, self.device)
+        elif weights_seed is not None:
+            get = random_source(manifest, weights_seed, self.device, self.dtype)
+        else:
+            raise ValueError("give a model folder or a seed for random weights")
+        self.model.load(get)
+        self.max_model_len = engine_config.max_model_len or self.spec.max_positions
+        needs = self.model.cache_needs()
+        self.num_pages = engine_config.num_blocks or self._pages_from_memory(needs)
+        self.cache = CacheManager(needs, engine_config.block_size, self.num_pages,
+                                  max_requests=max(engine_config.max_batch_size, 4) * 2,
+                                  dtype=self.dtype, device=self.device)
+        self.caches = [self._cache_view(i, n) for i, n in enumerate(needs)]
+        self.builder = BatchBuilder(self.cache, self.device)
+        self._graphs: Dict[int, "_CapturedStep"] = {}
+        self.steps = 0
+        self.launch_count = 0
+
+    # ------------------------------------------------------------------ set-up
+    def _pages_from_memory(self, needs) -> int:
+        """Pages per group from the memory left after weights and workspace
+        (reference sizing: cmd/gollmgo/gpu.go:151-177)."""
+        per_page = CacheManager.bytes_per_page(needs, self.ecfg.block_size,
+                                               torch.empty((), dtype=self.dtype).element_size())
+        # every layer of a group shares the page id, so one page id costs per_page per layer;
+        # bytes_per_page already sums over cache entries
+        free, _ = torch.cuda.mem_get_info(self.device)
+        reserve = self.ctx.workspace.nbytes() + (512 << 20)
+        avail = int((free - reserve) * self.ecfg.max_memory_fraction)
+        if per_page <= 0:
+            return 64
+        return max(64, avail // per_page)
+
+    def _cache_view(self, cache_id: int, need):
+        if isinstance(need, PagedKVNeed):
+            return self.cache.layer_cache(cache_id)
+        if need is None:
+            return None
+        return self.cache.state_buffers[cache_id]
+
+    # ------------------------------------------------------------------ requests
+    def admit(self, request_id) -> None:
+        self.cache.admit(request_id)
+
+    def release(self, request_id) -> None:
+        self.cache.free(request_id)
+
+    def has(self, request_id) -> bool:
+        return request_id in self.cache.requests
+
+    # ------------------------------------------------------------------ the step
+    def _validate(self, entries: Sequence[StepEntry]) -> None:
+        V = self.spec.vocab_size
+        total = 0
+        for e in entries:
+            total += len(e.tokens)
+            for t in e.tokens:
+                if not (0 <= int(t) < V):
+                    raise ValueError(f"request {e.request_id!r}: token id {t} is outside [0, {V})")
+            if e.request_id in self.cache.requests and \
+                    self.cache.num_tokens(e.request_id) + len(e.tokens) > self.max_model_len:
+                raise ValueError(f"request {e.request_id!r} would exceed max_model_len "
+                                 f"{self.max_model_len}")
+        if total > self.ctx.max_tokens:
+            raise ValueError(f"step of {total} tokens exceeds max_token_budget {self.ctx.max_tokens}")
+        if len(entries) > self.ctx.max_seqs:
+            raise ValueError(f"step of {len(entries)} sequences exceeds max_batch_size {self.ctx.max_seqs}")
+
+    def step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
+        """Run one batch.  Requests not seen before are admitted.  Returns float32
+        logits [wanted places, vocab] on the device, in the order of the entries
+        and of each entry's ``want``."""
+        self._validate(entries)
+        for e in entries:
+            if e.request_id not in self.cache.requests:
+                self.cache.admit(e.request_id)
+        decode_only = all(len(e.tokens) == 1 and list(e.want) == [0] for e in entries)
+        if decode_only and self.ecfg.cuda_graphs:
+            bucket = next((b for b in GRAPH_BUCKETS if b >= len(entries)), None)
+            if bucket is not None and bucket <= self.ctx.max_seqs:
+                return self._graph_step(entries, bucket)
+        batch = self.builder.build(entries)
+        logits = self.model.forward(batch, self.caches)
+        self.steps += 1
+        return logits
+
+    # ------------------------------------------------------------------ captured decode steps
+    def _graph_stride(self) -> int:
+        return -(-self.max_model_len // self.cache.page_size)
+
+    def _graph_step(self, entries, bucket: int) -> torch.Tensor:
+        cs = self._graphs.get(bucket)
+        stride = self._graph_stride()
+        if cs is None:
+            lay = BatchLayout(bucket, bucket, bucket, 0, bucket, len(self.cache.groups), stride)
+            cs = _CapturedStep(torch.zeros(lay.size, dtype=torch.int32, device=self.device))
+            self._graphs[bucket] = cs
+        batch = self.builder.build(entries, fixed_seqs=bucket, fixed_stride=stride, static_dev=cs.meta)
+        if cs.graph is None:
+            torch.cuda.synchronize(self.device)
+            # warm-up on a side stream, then capture
+            s = torch.cuda.Stream(self.device)
+            s.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(s):
+                self.model.forward(batch, self.caches)
+            torch.cuda.current_stream().wait_stream(s)
+            torch.cuda.synchronize(self.device)
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                cs.logits = self.model.forward(batch, self.caches)
+            cs.graph = g
+        cs.graph.replay()
+        self.steps += 1
+        return cs.logits[:len(entries)]
+
+    # ------------------------------------------------------------------ facts
+    def memory_report(self) -> dict:
+        return {"weights_bytes": self.model.weight_bytes(),
+                "workspace_bytes": self.ctx.workspace.nbytes(),
+                "cache_pages": self.num_pages, "page_size": self.cache.page_size}
+
+
+class _CapturedStep:
+    def __init__(self, meta: torch.Tensor):
+        self.meta = meta
+        self.graph = None
+        self.logits = None
+
+
+def load_runner(model_dir: str, engine_config: EngineConfig) -> ModelRunner:
+    """Runner for the model in ``model_dir`` (config.json + *.safetensors)."""
+    return ModelRunner(read_config_json(model_dir), engine_config, weights=model_dir)

@@ -1,0 +1,109 @@
+"""The attention mixer: q/k/v projections, position encoding, cache write,
+grouped-query attention over the paged cache, output projection.
+
+Order of operations follows the reference's run_layer (kernels/gollmgo_model.cu:581-713):
+projections without bias, rotation of q and k, write of k and v at this step's
+slots, attention over everything the cache holds for the sequence (this step's
+tokens included), output projection.  q, k and v come from one product with the
+three weights stacked.
+"""
+from __future__ import annotations
+
+import math
+
+import torch
+
+from ..cache import PagedKVNeed
+from ..csrc import ops
+from ..weights import WeightSpec
+from .linear import linear
+from .registry import build_position, register_mixer
+
+MAX_SPLITS = 64
+
+
+def decode_splits(n_dec: int, ctas_per_split: int, num_sms: int) -> int:
+    """Slices of the context per decoded token: enough that the grid fills the
+    machine about twice.  Depends only on the batch, never on context lengths,
+    so a captured step stays valid as contexts grow."""
+    per = max(1, n_dec * ctas_per_split)
+    return max(1, min(MAX_SPLITS, -(-2 * num_sms // per)))
+
+
+class Attention:
+    """params: hidden_size, num_heads, num_kv_heads, head_dim, window (None = all
+    keys), position (PartSpec)."""
+
+    def __init__(self, spec, ctx):
+        self.ctx = ctx
+        self.hidden = int(spec["hidden_size"])
+        self.nh = int(spec["num_heads"])
+        self.nkv = int(spec["num_kv_heads"])
+        self.d = int(spec["head_dim"])
+        self.window = spec.get("window") or None
+        if self.nh % self.nkv:
+            raise ValueError(f"{self.nh} heads are not a multiple of {self.nkv} kv heads")
+        if self.d > 256:
+            raise ValueError(f"head size {self.d} is beyond what the attention kernels take (256)")
+        self.position = build_position(spec["position"], ctx)
+        self.scale = 1.0 / math.sqrt(self.d)
+        self.qkv_width = (self.nh + 2 * self.nkv) * self.d
+        self.num_sms = torch.cuda.get_device_properties(ctx.device).multi_processor_count \
+            if ctx.device.type == "cuda" else 148
+        ws, T = ctx.workspace, ctx.max_tokens
+        ws.reserve("qkv", T * self.qkv_width, ctx.act_dtype)
+        ws.reserve("attn_out", T * self.nh * self.d, ctx.act_dtype)
+        ws.reserve("mixer_out", T * self.hidden, ctx.act_dtype)
+        gchunks = -(-(self.nh // self.nkv) // 16)
+        self._ctas_per_split = self.nkv * gchunks
+        rows = max(n * decode_splits(n, self._ctas_per_split, self.num_sms)
+                   for n in range(1, ctx.max_seqs + 1))
+        ws.reserve("attn_part_o", rows * self.nh * self.d, torch.float32)
+        ws.reserve("attn_part_ml", rows * self.nh * 2, torch.float32)
+        self.w_qkv = None
+        self.w_o = None
+
+    def cache_need(self):
+        return PagedKVNeed(self.nkv, self.d, self.window)
+
+    def weights(self):
+        return {"q_proj.weight": WeightSpec((self.nh * self.d, self.hidden)),
+                "k_proj.weight": WeightSpec((self.nkv * self.d, self.hidden)),
+                "v_proj.weight": WeightSpec((self.nkv * self.d, self.hidden)),
+                "o_proj.weight": WeightSpec((self.hidden, self.nh * self.d))}
+
+    def load(self, get):
+        q, k, v = get("q_proj.weight"), get("k_proj.weight"), get("v_proj.weight")
+        dt = torch.float32 if torch.float32 in (q.dtype, k.dtype, v.dtype) else q.dtype
+        self.w_qkv = torch.cat([q.to(dt), k.to(dt), v.to(dt)], dim=0).contiguous()
+        self.w_o = get("o_proj.weight").contiguous()
+
+    def forward(self, x, batch, cache, writes_cache=True):
+        T = x.shape[0]
+        ws = self.ctx.workspace
+        kc, vc, group = cache
+        qkv = ws.get("qkv", T, self.qkv_width)
+        linear(x, self.w_qkv, qkv)
+        ops.rope_kv_write(qkv, batch.positions, batch.slot_mapping[group], self.position.rope_table(),
+                          kc, vc, self.nh, self.nkv, self.d, self.ctx.page_size,
+                          self.position.interleaved, writes_cache)
+        out = ws.get("attn_out", T, self.nh * self.d)
+        window = int(self.window or 0)
+        bt = batch.block_tables[group]
+        if batch.num_tiles:
+            ops.attn_prefill(qkv, self.qkv_width, kc, vc, bt, batch.bt_stride, batch.cu_q_lens,
+                             batch.context_lens, batch.tile_seq, batch.tile_q0, batch.num_tiles,
+                             out, self.nh, self.nkv, self.d, self.ctx.page_size, window, self.scale)
+        if batch.num_decode:
+            splits = decode_splits(batch.num_decode, self._ctas_per_split, self.num_sms)
+            ops.attn_decode(qkv, self.qkv_width, kc, vc, bt, batch.bt_stride, batch.cu_q_lens,
+                            batch.context_lens, batch.dec_seqs, batch.num_decode, splits,
+                            ws.get("attn_part_o", 1, batch.num_decode * self.nh * splits * self.d),
+                            ws.get("attn_part_ml", 1, batch.num_decode * self.nh * splits * 2),
+                            out, self.nh, self.nkv, self.d, self.ctx.page_size, window, self.scale)
+        y = ws.get("mixer_out", T, self.hidden)
+        linear(out, self.w_o, y)
+        return y
+
+
+register_mixer("attention", Attention)

@@ -1,0 +1,54 @@
+"""Build-time context shared by the parts of one model: dtype, device, step
+limits, and a workspace of named activation buffers that parts share.
+"""
+from __future__ import annotations
+
+from typing import Dict, Optional, Tuple
+
+import torch
+
+
+class Workspace:
+    """Named buffers, one allocation per name sized for the largest request.
+    Parts ask for a buffer by name at build time and take a view of its first
+    rows each step; two parts that use the same name share the memory, so a
+    name must not be live across a call into another part that uses it."""
+
+    def __init__(self, device):
+        self.device = device
+        self._want: Dict[str, Tuple[int, torch.dtype]] = {}
+        self._bufs: Dict[str, torch.Tensor] = {}
+
+    def reserve(self, name: str, numel: int, dtype: torch.dtype) -> None:
+        old = self._want.get(name)
+        if old is not None and old[1] != dtype:
+            raise ValueError(f"workspace buffer {name!r} wanted as {old[1]} and {dtype}")
+        self._want[name] = (max(numel, old[0] if old else 0), dtype)
+        if name in self._bufs and self._bufs[name].numel() < self._want[name][0]:
+            del self._bufs[name]
+
+    def get(self, name: str, rows: int, cols: int) -> torch.Tensor:
+        """View [rows, cols] of the named buffer."""
+        buf = self._bufs.get(name)
+        if buf is None:
+            numel, dtype = self._want[name]
+            buf = torch.empty(numel, dtype=dtype, device=self.device)
+            self._bufs[name] = buf
+        n = rows * cols
+        if n > buf.numel():
+            raise ValueError(f"workspace buffer {name!r} holds {buf.numel()} elements, {n} asked")
+        return buf[:n].view(rows, cols)
+
+    def nbytes(self) -> int:
+        return sum(n * torch.empty((), dtype=dt).element_size() for n, dt in self._want.values())
+
+
+class BuildContext:
+    def __init__(self, act_dtype: torch.dtype, device, max_tokens: int, max_seqs: int,
+                 page_size: int, workspace: Optional[Workspace] = None):
+        self.act_dtype = act_dtype
+        self.device = torch.device(device)
+        self.max_tokens = max_tokens          # most tokens in one step
+        self.max_seqs = max_seqs              # most sequences in one step
+        self.page_size = page_size
+        self.workspace = workspace or Workspace(self.device)

@@ -1,0 +1,55 @@
+"""The SiLU-gated feed-forward: down( silu(x Wg^T) * (x Wu^T) ), no biases
+(kernels/gollmgo_model.cu:746-776, kernels/gollmgo_ops.cu:361-374).  Gate and up
+weights are stacked so one product makes both.
+"""
+from __future__ import annotations
+
+import torch
+
+from ..csrc import ops
+from ..weights import WeightSpec
+from .linear import linear
+from .registry import register_feed_forward
+
+
+class GatedMLP:
+    """params: hidden_size, intermediate_size, activation ("silu")."""
+
+    def __init__(self, spec, ctx):
+        self.ctx = ctx
+        self.hidden = int(spec["hidden_size"])
+        self.inter = int(spec["intermediate_size"])
+        act = spec.get("activation", "silu")
+        if act != "silu":
+            raise ValueError(f"activation {act!r} is not supported (known: silu)")
+        ws, T = ctx.workspace, ctx.max_tokens
+        ws.reserve("gate_up", T * 2 * self.inter, ctx.act_dtype)
+        ws.reserve("ffn_act", T * self.inter, ctx.act_dtype)
+        ws.reserve("ffn_out", T * self.hidden, ctx.act_dtype)
+        self.w_gate_up = None
+        self.w_down = None
+
+    def weights(self):
+        return {"gate_proj.weight": WeightSpec((self.inter, self.hidden)),
+                "up_proj.weight": WeightSpec((self.inter, self.hidden)),
+                "down_proj.weight": WeightSpec((self.hidden, self.inter))}
+
+    def load(self, get):
+        g, u = get("gate_proj.weight"), get("up_proj.weight")
+        dt = torch.float32 if torch.float32 in (g.dtype, u.dtype) else g.dtype
+        self.w_gate_up = torch.cat([g.to(dt), u.to(dt)], dim=0).contiguous()
+        self.w_down = get("down_proj.weight").contiguous()
+
+    def forward(self, x, batch):
+        T = x.shape[0]
+        ws = self.ctx.workspace
+        gu = ws.get("gate_up", T, 2 * self.inter)
+        linear(x, self.w_gate_up, gu)
+        a = ws.get("ffn_act", T, self.inter)
+        ops.silu_mul(gu, a)
+        y = ws.get("ffn_out", T, self.hidden)
+        linear(a, self.w_down, y)
+        return y
+
+
+register_feed_forward("gated_mlp", GatedMLP)

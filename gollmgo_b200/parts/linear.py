@@ -1,0 +1,33 @@
+"""Matrix products of the model: out = x @ w^T through the vendor library, as in
+the reference (cublasGemmEx with float32 accumulation: kernels/gollmgo_model.cu:143-169).
+
+In the float32 mode the product is a true float32 one: the TF32 matrix mode and
+reduced-precision accumulation are switched off for the process by
+``set_matmul_precision``.
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+
+def set_matmul_precision() -> None:
+    """No TF32 for float32 products, no bfloat16 accumulation across split-K."""
+    torch.backends.cuda.matmul.allow_tf32 = False
+    torch.backends.cudnn.allow_tf32 = False
+    torch.set_float32_matmul_precision("highest")
+    torch.backends.cuda.matmul.allow_bf16_reduced_precision_reduction = False
+    torch.backends.cuda.matmul.allow_fp16_reduced_precision_reduction = False
+
+
+def linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """out[T, N] = x[T, K] @ w[N, K]^T, rounded to out's dtype.  A weight stored in
+    float32 is multiplied in float32 even when the activations are bfloat16."""
+    if w.dtype == x.dtype and out.dtype == x.dtype:
+        torch.mm(x, w.t(), out=out)
+    elif w.dtype == x.dtype and out.dtype == torch.float32:
+        out.copy_(torch.mm(x, w.t(), out_dtype=torch.float32))
+    else:
+        out.copy_(torch.mm(x.to(torch.float32), w.to(torch.float32).t()))
+    return out

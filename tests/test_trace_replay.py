@@ -1,0 +1,38 @@
+"""Replay through bin/trace_run, compared with the plain implementation: the same
+requests whole, with the last 32 tokens one by one, in portions of changing size,
+and mixed with other requests on a pool so small that pages are used again; in
+float32 and in bfloat16; for tiny configurations that differ in every size."""
+import pytest
+import torch
+
+import tiny_configs
+import trace_tools as tt
+
+pytestmark = pytest.mark.gpu
+
+LENGTHS = {"tiny_a": [7, 13, 1, 70, 45, 101], "tiny_b": [1, 5, 37, 70, 130, 96],
+           "tiny_c": [3, 66, 40, 150, 97, 129]}
+TOL = {"float32": 2e-4, "bfloat16": 6e-2}
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["tiny_a", "tiny_b", "tiny_c"])
+def test_replay_matches_plain(tmp_path, cuda_device, name, dtype):
+    config, page, std, jitter = tiny_configs.get(name)
+    model_dir = tt.model_folder(str(tmp_path), name, config, seed=11, std=std, jitter=jitter,
+                                dtype="float32" if dtype == "float32" else "bfloat16")
+    weights = tt.load_weights(model_dir)
+    requests = tt.random_requests(config["vocab_size"], LENGTHS[name], seed=5)
+    reference = tt.plain_logits(weights, config, requests)
+    trace = tt.Trace()
+    tt.whole(trace, requests)
+    tt.tail_decode(trace, requests)
+    tt.portions(trace, requests)
+    peak_single = trace.peak
+    tt.mixed(trace, requests, max_live=4, seed=3)
+    tt.mixed(trace, dict(reversed(list(requests.items()))), max_live=3, seed=4, tag="n")
+    out = str(tmp_path / "out")
+    tt.run_trace(model_dir, dtype, trace, out, block_size=page)
+    worst = tt.compare(trace, out, reference, config["vocab_size"], TOL[dtype])
+    print(f"{name} {dtype}: {len(trace.steps)} steps, pool {trace.peak} tokens "
+          f"(single-request peak {peak_single}), worst relative error {worst:.2e}")
