@@ -1,0 +1,6 @@
+"""gollmgo_b200: a single-GPU inference engine for the Llama dense decoder on B200
+(sm_100a): configuration, weights, parts, paged cache, one step function, a
+continuous-batching scheduler, sampling, trace replay."""
+from . import architectures  # noqa: F401  registers "LlamaForCausalLM"
+
+__version__ = "0.1.0"
