@@ -1,0 +1,229 @@
+"""Command line: ``python -m gollmgo_b200 generate | bench | doctor``.
+
+Option names and meanings are the reference's where it has them
+(cmd/gollmgo/main.go:52-60 serve flags --config --model --device --log-level;
+:227-240 bench flags --mode --num-prompts --prompt-len --output-len
+--warmup-requests --repetitions --model --config; :591-632 doctor).  The engine
+keys of --config are those of its server config (internal/config/config.go:33-78).
+``serve`` (the HTTP server) is not part of this engine.
+"""
+from __future__ import annotations
+
+import argparse
+import datetime
+import json
+import os
+import subprocess
+import sys
+import time
+
+
+def _engine_flags(ap: argparse.ArgumentParser) -> None:
+    ap.add_argument("--model", default="", help="local model folder (config.json + *.safetensors)")
+    ap.add_argument("--config", default="", help="JSON file with engine keys: max_batch_size, "
+                    "max_token_budget, max_queue_depth, prefill_chunk_size, block_size, max_memory_fraction")
+    ap.add_argument("--device", type=int, default=0, help="CUDA device index")
+    ap.add_argument("--log-level", default="info", choices=["debug", "info", "warn", "error"])
+    ap.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"])
+    ap.add_argument("--random-weights", default="", metavar="CONFIG_JSON",
+                    help="a config.json to run with random weights instead of --model")
+    ap.add_argument("--seed", type=int, default=0, help="seed of the random weights")
+    ap.add_argument("--max-batch-size", type=int)
+    ap.add_argument("--max-token-budget", type=int)
+    ap.add_argument("--max-queue-depth", type=int)
+    ap.add_argument("--prefill-chunk-size", type=int)
+    ap.add_argument("--block-size", type=int)
+    ap.add_argument("--num-blocks", type=int, help="cache pages (default: from --max-memory-fraction)")
+    ap.add_argument("--max-memory-fraction", type=float)
+    ap.add_argument("--max-model-len", type=int)
+    ap.add_argument("--no-cuda-graphs", action="store_true")
+
+
+def _log(args, level: str, msg: str, **kv) -> None:
+    order = ["debug", "info", "warn", "error"]
+    if order.index(level) >= order.index(args.log_level):
+        extra = " ".join(f"{k}={v}" for k, v in kv.items())
+        print(f"time={datetime.datetime.now().isoformat(timespec='seconds')} level={level.upper()} "
+              f"msg=\"{msg}\" {extra}".rstrip(), file=sys.stderr, flush=True)
+
+
+def _make_engine(args):
+    from .config import EngineConfig
+    from .engine.llm_engine import Engine
+    ecfg = EngineConfig(dtype=args.dtype, device=args.device, cuda_graphs=not args.no_cuda_graphs)
+    if args.config:
+        with open(args.config) as f:
+            data = json.load(f)
+        data = {**data, **data.get("server", {})}       # reference: internal/config/load.go:21-30
+        for k in ("max_batch_size", "max_token_budget", "max_queue_depth", "prefill_chunk_size",
+                  "block_size", "max_memory_fraction"):
+            if k in data:
+                setattr(ecfg, k, data[k])
+    for k in ("max_batch_size", "max_token_budget", "max_queue_depth", "prefill_chunk_size",
+              "block_size", "num_blocks", "max_memory_fraction", "max_model_len"):
+        v = getattr(args, k)
+        if v is not None:
+            setattr(ecfg, k, v)
+    t0 = time.time()
+    if args.random_weights:
+        with open(args.random_weights) as f:
+            cfg = json.load(f)
+        eng = Engine(config=cfg, weights_seed=args.seed, engine_config=ecfg)
+    elif args.model:
+        eng = Engine(args.model, engine_config=ecfg)
+    else:
+        raise SystemExit("error: give --model DIR or --random-weights CONFIG_JSON")
+    rep = eng.runner.memory_report()
+    _log(args, "info", "engine ready", seconds=f"{time.time() - t0:.1f}", dtype=args.dtype,
+         weights_gb=f"{rep['weights_bytes'] / 1e9:.2f}", cache_pages=rep["cache_pages"],
+         page_size=rep["page_size"])
+    return eng
+
+
+def cmd_generate(argv) -> int:
+    ap = argparse.ArgumentParser(prog="gollmgo_b200 generate")
+    _engine_flags(ap)
+    ap.add_argument("--prompt-ids", action="append", default=[],
+                    help="comma-separated token ids; may be given several times")
+    ap.add_argument("--prompt-len", type=int, default=0, help="instead: a synthetic prompt of this length")
+    ap.add_argument("--num-prompts", type=int, default=1)
+    ap.add_argument("--max-tokens", type=int, default=256)
+    ap.add_argument("--temperature", type=float, default=0.0)
+    ap.add_argument("--top-k", type=int, default=0)
+    ap.add_argument("--top-p", type=float, default=0.0)
+    ap.add_argument("--sampling-seed", type=int, default=None)
+    ap.add_argument("--ignore-eos", action="store_true")
+    args = ap.parse_args(argv)
+    from .sampling import SamplingParams
+    eng = _make_engine(args)
+    V = eng.spec.vocab_size
+    prompts = [[int(t) for t in p.split(",") if t.strip()] for p in args.prompt_ids]
+    if not prompts:
+        n = args.prompt_len or 8
+        prompts = [[(j + i) % min(V, 255) for j in range(n)] for i in range(args.num_prompts)]
+    params = SamplingParams(temperature=args.temperature, top_k=args.top_k, top_p=args.top_p,
+                            seed=args.sampling_seed, max_tokens=args.max_tokens,
+                            ignore_eos=args.ignore_eos)
+    outs = eng.generate(prompts, params)
+    for o in outs:
+        print(json.dumps({"request_id": o.request_id, "prompt_token_ids": o.prompt_token_ids,
+                          "token_ids": o.token_ids, "finish_reason": o.finish_reason}))
+    return 0
+
+
+def _percentile(xs, q):
+    if not xs:
+        return 0.0
+    xs = sorted(xs)
+    k = (len(xs) - 1) * q
+    lo, hi = int(k), min(int(k) + 1, len(xs) - 1)
+    return xs[lo] + (xs[hi] - xs[lo]) * (k - lo)
+
+
+def _git_sha() -> str:
+    try:
+        return subprocess.run(["git", "rev-parse", "--short", "HEAD"], capture_output=True, text=True,
+                              cwd=os.path.dirname(os.path.abspath(__file__))).stdout.strip() or "unknown"
+    except OSError:
+        return "unknown"
+
+
+def cmd_bench(argv) -> int:
+    ap = argparse.ArgumentParser(prog="gollmgo_b200 bench")
+    _engine_flags(ap)
+    ap.add_argument("--mode", default="offline", choices=["offline", "synthetic"],
+                    help="offline/synthetic: synthetic token prompts through the engine "
+                         "(the reference's serving mode needs its HTTP server and is not built)")
+    ap.add_argument("--num-prompts", type=int, default=100)
+    ap.add_argument("--prompt-len", type=int, default=128)
+    ap.add_argument("--output-len", type=int, default=128)
+    ap.add_argument("--warmup-requests", type=int, default=0)
+    ap.add_argument("--repetitions", type=int, default=1)
+    args = ap.parse_args(argv)
+    import torch
+    from .sampling import SamplingParams
+    eng = _make_engine(args)
+    V = eng.spec.vocab_size
+    params = SamplingParams(max_tokens=args.output_len, ignore_eos=True)
+    # prompts as the reference's offline bench makes them: prompt[j] = (j + i) % 255
+    # (cmd/gollmgo/main.go:335-422)
+    mk = lambda n, off=0: [[(j + i + off) % min(V, 255) for j in range(args.prompt_len)] for i in range(n)]
+    if args.warmup_requests:
+        eng.generate(mk(args.warmup_requests, 7), params)
+    result = None
+    for rep in range(args.repetitions):
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        outs = eng.generate(mk(args.num_prompts), params)
+        torch.cuda.synchronize()
+        elapsed = time.perf_counter() - t0
+        toks = sum(len(o.token_ids) for o in outs)
+        itl = [b - a for o in outs for a, b in zip(o.token_times, o.token_times[1:])]
+        ttft = [o.ttft_s for o in outs if o.ttft_s is not None]
+        e2e = [o.e2e_s for o in outs if o.e2e_s is not None]
+        ms = lambda xs, q: round(_percentile(xs, q) * 1e3, 3)
+        result = {
+            "timestamp": datetime.datetime.now(datetime.timezone.utc).isoformat(timespec="seconds"),
+            "git_sha": _git_sha(), "hardware": torch.cuda.get_device_name(args.device),
+            "mode": args.mode, "num_prompts": args.num_prompts, "measured_requests": len(outs),
+            "prompt_len": args.prompt_len, "output_len": args.output_len,
+            "warmup_requests": args.warmup_requests, "repetitions": args.repetitions,
+            "prompt_generation": "synthetic token ids", "token_count_mode": "exact",
+            "elapsed_seconds": round(elapsed, 4), "tokens_per_second": round(toks / elapsed, 2),
+            "requests_per_second": round(len(outs) / elapsed, 3), "error_count": 0,
+            "ttft_p50_ms": ms(ttft, .5), "ttft_p95_ms": ms(ttft, .95), "ttft_p99_ms": ms(ttft, .99),
+            "e2e_p50_ms": ms(e2e, .5), "e2e_p95_ms": ms(e2e, .95), "e2e_p99_ms": ms(e2e, .99),
+            "itl_p50_ms": ms(itl, .5), "itl_p95_ms": ms(itl, .95), "itl_p99_ms": ms(itl, .99),
+            "dtype": args.dtype, "engine_steps": eng.stats.steps, "preemptions": eng.stats.preemptions,
+            "pages_high_water": eng.stats.pages_high_water,
+        }
+        _log(args, "info", "repetition done", rep=rep, tokens_per_second=result["tokens_per_second"])
+    print(json.dumps(result, indent=2))
+    return 0
+
+
+def cmd_doctor(argv) -> int:
+    ap = argparse.ArgumentParser(prog="gollmgo_b200 doctor")
+    ap.add_argument("--device", type=int, default=0)
+    args = ap.parse_args(argv)
+    import shutil
+    import torch
+    ok = True
+
+    def line(name, good, detail):
+        nonlocal ok
+        ok &= bool(good)
+        print(f"[{'ok' if good else 'FAIL'}] {name}: {detail}")
+    line("python", True, sys.version.split()[0])
+    line("torch", True, torch.__version__)
+    line("nvcc", shutil.which("nvcc") or os.path.exists("/usr/local/cuda/bin/nvcc"),
+         shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc")
+    has = torch.cuda.is_available()
+    line("cuda device", has, torch.cuda.get_device_name(args.device) if has else "none visible")
+    if has:
+        p = torch.cuda.get_device_properties(args.device)
+        line("compute capability", p.major >= 10, f"sm_{p.major}{p.minor}, {p.multi_processor_count} SMs, "
+             f"{p.total_memory / 2**30:.0f} GiB")
+        try:
+            from .csrc import ops
+            line("kernel library", True, ops.library_file())
+        except Exception as e:  # noqa: BLE001
+            line("kernel library", False, str(e))
+    return 0 if ok else 1
+
+
+def main(argv=None) -> int:
+    argv = list(sys.argv[1:] if argv is None else argv)
+    cmds = {"generate": cmd_generate, "bench": cmd_bench, "doctor": cmd_doctor}
+    if not argv or argv[0] in ("-h", "--help") or argv[0] not in cmds:
+        print("usage: python -m gollmgo_b200 <command> [flags]\n\ncommands:\n"
+              "  generate  generate tokens for prompts given as token ids\n"
+              "  bench     run synthetic prompts through the engine and print a result JSON\n"
+              "  doctor    check the toolchain, the device and the kernel library\n",
+              file=sys.stderr)
+        return 0 if argv and argv[0] in ("-h", "--help") else 1
+    return cmds[argv[0]](argv[1:])
+
+
+if __name__ == "__main__":
+    sys.exit(main())

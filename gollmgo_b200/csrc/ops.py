@@ -49,9 +49,14 @@ def _stream():
     return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
 
 
-def _check(rc: int) -> None:
+launches = 0          # kernels of this library launched by this process (a captured graph counts once)
+
+
+def _check(rc: int, n: int = 1) -> None:
+    global launches
     if rc != 0:
         raise KernelError(lib().gg_last_error().decode())
+    launches += n
 
 
 def dtype_code(dt: torch.dtype) -> int:
@@ -153,7 +158,7 @@ def attn_decode(q: torch.Tensor, q_stride: int, kcache: torch.Tensor, vcache: to
                                 dtype_code(kcache.dtype), _p(block_tables), bt_stride,
                                 _p(cu_q_lens), _p(context_lens), _p(dec_seqs), n_dec, num_splits,
                                 _p(part_o), _p(part_ml), _p(out), nh, nkv, d, page_size, window,
-                                ctypes.c_float(scale), _stream()))
+                                ctypes.c_float(scale), _stream()), 2)
 
 
 def argmax(logits: torch.Tensor, out: torch.Tensor) -> None:

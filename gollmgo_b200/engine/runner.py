@@ -162,10 +162,13 @@ class ModelRunner:
             torch.cuda.current_stream().wait_stream(s)
             torch.cuda.synchronize(self.device)
             g = torch.cuda.CUDAGraph()
+            before = ops.launches
             with torch.cuda.graph(g):
                 cs.logits = self.model.forward(batch, self.caches)
+            cs.launches = ops.launches - before
             cs.graph = g
         cs.graph.replay()
+        ops.launches += cs.launches
         self.steps += 1
         return cs.logits[:len(entries)]
 
@@ -181,6 +184,7 @@ class _CapturedStep:
         self.meta = meta
         self.graph = None
         self.logits = None
+        self.launches = 0
 
 
 def load_runner(model_dir: str, engine_config: EngineConfig) -> ModelRunner:

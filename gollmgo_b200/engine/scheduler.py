@@ -1,0 +1,210 @@
+"""First-come-first-served continuous batching with chunked prefill.
+
+Each ``schedule()`` plans one step under ``max_batch_size`` sequences and
+``max_token_budget`` tokens, in the reference's order
+(internal/scheduler/fcfs.go:72-164): first every decoding sequence, one token
+each; then sequences in the middle of their prompt, a portion each
+(``prefill_chunk_size`` at most, cut to the budget that is left, down to one
+token); then new requests in arrival order.
+
+Where this differs from the reference, on purpose:
+  * the plan says how many tokens each sequence gets, and the engine runs exactly
+    that (the reference's engine recomputes the portion and may exceed the
+    budget: internal/engine/serving.go:353-362);
+  * free pages are consulted.  A new request is admitted only if its first
+    portion fits beside one more page for every running sequence, and the head
+    of the queue blocks those behind it (strict arrival order);
+  * when pages run out for the running sequences, the one admitted last is
+    preempted: its pages are given back, it returns to the front of the queue
+    and is later recomputed over prompt and generated tokens as one prompt, so
+    the tokens it goes on to generate are the same.  (The reference preempts the
+    sequence with most blocks at 95 % utilisation and, on re-admission, does not
+    rebuild the keys and values of generated tokens: internal/engine/serving.go:717-798,
+    364-373.)
+  * a request that could never fit (prompt + max_tokens beyond the pool or the
+    longest sequence allowed) is refused when it is added.
+"""
+from __future__ import annotations
+
+from collections import deque
+from dataclasses import dataclass, field
+from typing import Deque, Dict, List, Optional
+
+from ..config import EngineConfig
+from .sequence import SeqState, Sequence
+
+
+class QueueFull(RuntimeError):
+    pass
+
+
+class RequestTooLong(ValueError):
+    pass
+
+
+@dataclass
+class Scheduled:
+    seq: Sequence
+    num_tokens: int
+
+    @property
+    def samples(self) -> bool:
+        """True if this portion reaches the sequence's last known token, so that
+        its last logits give the next token."""
+        return self.seq.num_computed + self.num_tokens == self.seq.total_len
+
+
+@dataclass
+class SchedulerOutput:
+    scheduled: List[Scheduled] = field(default_factory=list)
+    preempted: List[Sequence] = field(default_factory=list)
+    decode_tokens: int = 0
+    prefill_tokens: int = 0
+
+
+class Scheduler:
+    def __init__(self, cfg: EngineConfig, cache, max_model_len: int):
+        self.cfg = cfg
+        self.cache = cache
+        self.max_model_len = max_model_len
+        self.waiting: Deque[Sequence] = deque()
+        self.running: Dict[int, Sequence] = {}        # admitted: prefilling or decoding
+        self.admit_order: List[int] = []              # ids in the order of (re-)admission
+        self.num_preemptions = 0
+
+    # ------------------------------------------------------------------ queue
+    def pool_tokens(self) -> int:
+        return self.cache.num_pages * self.cache.page_size
+
+    def add(self, seq: Sequence) -> None:
+        if self.cfg.max_queue_depth > 0 and len(self.waiting) >= self.cfg.max_queue_depth:
+            raise QueueFull(f"queue is full: depth {len(self.waiting)}")
+        need = len(seq.prompt) + seq.params.max_tokens
+        limit = min(self.max_model_len, self.pool_tokens())
+        if not seq.prompt:
+            raise RequestTooLong("a request needs at least one prompt token")
+        if need > limit:
+            raise RequestTooLong(f"request needs {need} tokens (prompt {len(seq.prompt)} + "
+                                 f"max_tokens {seq.params.max_tokens}); at most {limit} fit")
+        self.waiting.append(seq)
+
+    def has_work(self) -> bool:
+        return bool(self.waiting or self.running)
+
+    # ------------------------------------------------------------------ pages
+    def _pages_for(self, seq: Sequence, n: int) -> int:
+        """Pages the next n tokens of an admitted sequence take beyond what it holds
+        (the largest need over the cache groups)."""
+        ps = self.cache.page_size
+        held = -(-seq.num_computed // ps)
+        return -(-(seq.num_computed + n) // ps) - held
+
+    def _preempt(self, seq: Sequence, out: SchedulerOutput) -> None:
+        seq.transition(SeqState.PREEMPTED)
+        seq.num_computed = 0
+        seq.preemptions += 1
+        self.num_preemptions += 1
+        del self.running[seq.id]
+        self.admit_order.remove(seq.id)
+        if seq.id in self.cache.requests:
+            self.cache.free(seq.id)
+        seq.transition(SeqState.WAITING)
+        self.waiting.appendleft(seq)
+        out.preempted.append(seq)
+
+    # ------------------------------------------------------------------ one step's plan
+    def schedule(self) -> SchedulerOutput:
+        out = SchedulerOutput()
+        cfg = self.cfg
+        budget = cfg.max_token_budget
+        chunk_cap = cfg.prefill_chunk_size or (1 << 30)
+        free = self.cache.min_free_pages()
+        planned: List[Scheduled] = []
+
+        def fits_or_preempt(seq: Sequence, n: int) -> bool:
+            """Make room for n tokens of seq by preempting later-admitted sequences
+            (never an earlier one).  False if seq itself had to go."""
+            nonlocal free
+            while self._pages_for(seq, n) > free:
+                victim_id = self.admit_order[-1]
+                victim = self.running[victim_id]
+                # a victim already planned in this step loses its plan
+                for i, s in enumerate(planned):
+                    if s.seq is victim:
+                        free += self._pages_for(victim, s.num_tokens)
+                        planned.pop(i)
+                        break
+                held = -(-victim.num_computed // self.cache.page_size)
+                self._preempt(victim, out)
+                free += held
+                if victim is seq:
+                    return False
+            free -= self._pages_for(seq, n)
+            return True
+
+        # 1. decoding sequences, oldest first, one token each
+        for sid in sorted(self.running):
+            seq = self.running.get(sid)
+            if seq is None or seq.state is not SeqState.DECODING:
+                continue
+            if len(planned) >= cfg.max_batch_size or budget <= 0:
+                break
+            if fits_or_preempt(seq, 1):
+                planned.append(Scheduled(seq, 1))
+                budget -= 1
+        # 2. sequences in the middle of their prompt
+        for sid in sorted(self.running):
+            seq = self.running.get(sid)
+            if seq is None or seq.state is not SeqState.PREFILLING:
+                continue
+            if len(planned) >= cfg.max_batch_size or budget <= 0:
+                break
+            n = min(seq.remaining, chunk_cap, budget)
+            if n > 0 and fits_or_preempt(seq, n):
+                planned.append(Scheduled(seq, n))
+                budget -= n
+        # 3. new requests, strictly in arrival order
+        while self.waiting and len(planned) < cfg.max_batch_size and budget > 0:
+            seq = self.waiting[0]
+            if any(seq is p for p in out.preempted):
+                break                                   # just preempted: not in the same step
+            n = min(seq.remaining, chunk_cap, budget)
+            need = -(-n // self.cache.page_size)
+            reserve = len(self.running)                 # one more page for everyone who is running
+            if need + reserve > free or self.cache.slots.num_free == 0:
+                break
+            self.waiting.popleft()
+            seq.transition(SeqState.PREFILLING)
+            self.running[seq.id] = seq
+            self.admit_order.append(seq.id)
+            free -= need
+            planned.append(Scheduled(seq, n))
+            budget -= n
+        for s in planned:
+            if s.seq.state is SeqState.DECODING:
+                out.decode_tokens += s.num_tokens
+            else:
+                out.prefill_tokens += s.num_tokens
+        out.scheduled = planned
+        return out
+
+    # ------------------------------------------------------------------ after the step
+    def advance(self, s: Scheduled) -> None:
+        """The step ran: s.num_tokens more tokens of the sequence are cached."""
+        seq = s.seq
+        seq.num_computed += s.num_tokens
+        if seq.state is SeqState.PREFILLING and seq.num_computed < seq.total_len:
+            seq.transition(SeqState.PREFILLING)
+
+    def token_sampled(self, seq: Sequence) -> None:
+        if seq.state is SeqState.PREFILLING:
+            seq.transition(SeqState.DECODING)
+
+    def finish(self, seq: Sequence, reason: str) -> None:
+        seq.finish_reason = reason
+        seq.transition(SeqState.FINISHED)
+        self.running.pop(seq.id, None)
+        if seq.id in self.admit_order:
+            self.admit_order.remove(seq.id)
+        if seq.id in self.cache.requests:
+            self.cache.free(seq.id)

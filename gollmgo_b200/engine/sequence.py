@@ -1,0 +1,75 @@
+"""A request on its way through the scheduler.
+
+States and transitions are the reference's (internal/scheduler/sequence.go:13-45):
+WAITING -> PREFILLING (-> itself for every further portion) -> DECODING ->
+FINISHED, and DECODING -> PREEMPTED -> WAITING; here a sequence can also be
+preempted while it is still prefilling.
+"""
+from __future__ import annotations
+
+import enum
+import time
+from typing import List, Optional
+
+from ..sampling.params import SamplingParams
+
+
+class SeqState(enum.Enum):
+    WAITING = "WAITING"
+    PREFILLING = "PREFILLING"
+    DECODING = "DECODING"
+    FINISHED = "FINISHED"
+    PREEMPTED = "PREEMPTED"
+
+
+_VALID = {
+    SeqState.WAITING: {SeqState.PREFILLING},
+    SeqState.PREFILLING: {SeqState.PREFILLING, SeqState.DECODING, SeqState.PREEMPTED, SeqState.FINISHED},
+    SeqState.DECODING: {SeqState.FINISHED, SeqState.PREEMPTED},
+    SeqState.PREEMPTED: {SeqState.WAITING},
+    SeqState.FINISHED: set(),
+}
+
+
+class InvalidTransition(RuntimeError):
+    pass
+
+
+class Sequence:
+    def __init__(self, seq_id: int, request_id: str, prompt: List[int], params: SamplingParams):
+        self.id = seq_id
+        self.request_id = request_id
+        self.prompt = list(prompt)
+        self.output: List[int] = []
+        self.params = params
+        self.state = SeqState.WAITING
+        self.num_computed = 0              # tokens whose keys and values are in the cache
+        self.preemptions = 0
+        self.finish_reason: Optional[str] = None
+        self.created_at = time.perf_counter()
+        self.first_token_at: Optional[float] = None
+        self.last_token_at: Optional[float] = None
+        self.token_times: List[float] = []
+
+    @property
+    def tokens(self) -> List[int]:
+        return self.prompt + self.output
+
+    @property
+    def total_len(self) -> int:
+        return len(self.prompt) + len(self.output)
+
+    @property
+    def remaining(self) -> int:
+        """Tokens not yet in the cache.  After a preemption this is prompt and
+        generated tokens together: they are recomputed as one prompt."""
+        return self.total_len - self.num_computed
+
+    def transition(self, to: SeqState) -> None:
+        if to not in _VALID[self.state]:
+            raise InvalidTransition(f"{self.state.value} -> {to.value}")
+        self.state = to
+
+    @property
+    def finished(self) -> bool:
+        return self.state is SeqState.FINISHED
