@@ -1,0 +1,325 @@
+"""Each CUDA kernel alone against a plain float32 PyTorch reference of the same op,
+at sizes other than the engine's: widths and vocabularies that are no power of
+two, head sizes in steps of 16, ragged batches, permuted pages, contexts that
+straddle page, tile and slice edges, and inputs made so that one far key decides
+the result."""
+import math
+import random
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+DTYPES = [torch.float32, torch.bfloat16]
+
+
+def tol(dtype):
+    return dict(rtol=2e-5, atol=2e-5) if dtype == torch.float32 else dict(rtol=2e-2, atol=2e-2)
+
+
+@pytest.fixture(scope="module")
+def ops(cuda_device):
+    from gollmgo_b200.csrc import ops as o
+    assert o.device_capability() >= 100
+    return o
+
+
+# ---------------------------------------------------------------- embedding
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("V,H", [(301, 120), (1000, 4100)])
+def test_embed_gather(ops, cuda_device, dtype, V, H):
+    g = torch.Generator(device="cuda").manual_seed(0)
+    table = torch.randn(V, H, device="cuda", generator=g).to(dtype)
+    ids = torch.tensor([0, V - 1, 5, 5, 17, V // 2], dtype=torch.int32, device="cuda")
+    out = torch.full((ids.numel(), H), 7.0, device="cuda")
+    bad = torch.zeros(1, dtype=torch.int32, device="cuda")
+    ops.embed_gather(ids, table, out, bad)
+    assert torch.equal(out, table[ids.long()].float()) and int(bad) == 0
+
+
+# ---------------------------------------------------------------- add + rmsnorm
+def ref_rmsnorm(x, w, eps):
+    return x * torch.rsqrt((x * x).mean(-1, keepdim=True) + eps) * w
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("H,eps", [(100, 1e-5), (4096, 1e-6), (5120 + 16, 3e-6)])
+def test_add_rmsnorm(ops, cuda_device, dtype, H, eps):
+    g = torch.Generator(device="cuda").manual_seed(1)
+    n = 7
+    resid = torch.randn(n, H, device="cuda", generator=g) * 3
+    delta = torch.randn(n, H, device="cuda", generator=g).to(dtype)
+    w = 1 + 0.1 * torch.randn(H, device="cuda", generator=g)
+    r0 = resid.clone()
+    out = torch.empty(n, H, device="cuda", dtype=dtype)
+    ops.add_rmsnorm(resid, delta, w, out, eps)
+    x = r0 + delta.float()
+    assert torch.equal(resid, x)                                       # the residual sum is float32, exact
+    torch.testing.assert_close(out.float(), ref_rmsnorm(x, w, eps).to(dtype).float(), **tol(dtype))
+    # no delta: the residual is left alone
+    r1 = resid.clone()
+    ops.add_rmsnorm(resid, None, w, out, eps)
+    assert torch.equal(resid, r1)
+    torch.testing.assert_close(out.float(), ref_rmsnorm(r1, w, eps).to(dtype).float(), **tol(dtype))
+    # chosen rows, nothing written back
+    rows = torch.tensor([6, 0, 3], dtype=torch.int32, device="cuda")
+    out3 = torch.empty(3, H, device="cuda", dtype=dtype)
+    ops.add_rmsnorm(resid, delta, w, out3, eps, rows=rows, write_back=False)
+    assert torch.equal(resid, r1)
+    torch.testing.assert_close(out3.float(), ref_rmsnorm(r1 + delta.float(), w, eps)[rows.long()].to(dtype).float(), **tol(dtype))
+
+
+# ---------------------------------------------------------------- silu * up
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("T,I", [(1, 352), (5, 13), (33, 14336)])
+def test_silu_mul(ops, cuda_device, dtype, T, I):
+    g = torch.Generator(device="cuda").manual_seed(2)
+    gu = (torch.randn(T, 2 * I, device="cuda", generator=g) * 3).to(dtype)
+    out = torch.empty(T, I, device="cuda", dtype=dtype)
+    ops.silu_mul(gu, out)
+    gf, uf = gu[:, :I].float(), gu[:, I:].float()
+    ref = (gf / (1 + torch.exp(-gf)) * uf).to(dtype)
+    torch.testing.assert_close(out.float(), ref.float(), **tol(dtype))
+
+
+# ---------------------------------------------------------------- rope + cache write
+def ref_rope(x, pos, inv_freq, interleaved):
+    """x [T, h, d] float64; rotates the first 2*len(inv_freq) elements of each head."""
+    rot = 2 * inv_freq.numel()
+    ang = pos.double()[:, None] * inv_freq[None, :]
+    c, s = torch.cos(ang)[:, None, :], torch.sin(ang)[:, None, :]
+    out = x.clone()
+    if interleaved:
+        a, b = x[..., 0:rot:2], x[..., 1:rot:2]
+        out[..., 0:rot:2], out[..., 1:rot:2] = a * c - b * s, a * s + b * c
+    else:
+        a, b = x[..., :rot // 2], x[..., rot // 2:rot]
+        out[..., :rot // 2], out[..., rot // 2:rot] = a * c - b * s, a * s + b * c
+    return out
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("nh,nkv,d,rot,interleaved,page", [
+    (4, 2, 16, 16, False, 16), (5, 5, 48, 48, True, 8), (8, 1, 80, 32, False, 32), (3, 3, 128, 0, False, 16)])
+def test_rope_kv_write(ops, cuda_device, dtype, nh, nkv, d, rot, interleaved, page):
+    g = torch.Generator(device="cuda").manual_seed(3)
+    T, pages = 11, 9
+    qkv = torch.randn(T, (nh + 2 * nkv) * d, device="cuda", generator=g).to(dtype)
+    pos = torch.tensor([0, 1, 2, 70, 71, 500, 3, 9000, 4, 5, 6], dtype=torch.int32, device="cuda")
+    slots = random.Random(0).sample(range(pages * page), T)
+    slots[4] = -1                                                      # a token that is not to be written
+    slot_t = torch.tensor(slots, dtype=torch.int32, device="cuda")
+    inv = (1.0 / (10000.0 ** (torch.arange(0, rot, 2, dtype=torch.float64) / max(rot, 1)))).cuda() if rot else None
+    kc = torch.full((pages, nkv, page, d), 9.0, device="cuda", dtype=dtype)
+    vc = torch.full((pages, nkv, page, d), 9.0, device="cuda", dtype=dtype)
+    x = qkv.clone()
+    ops.rope_kv_write(x, pos, slot_t, inv, kc, vc, nh, nkv, d, page, interleaved, True)
+    src = qkv.double().view(T, nh + 2 * nkv, d)
+    qk = ref_rope(src[:, :nh + nkv], pos, inv, interleaved) if rot else src[:, :nh + nkv]
+    got = x.double().view(T, nh + 2 * nkv, d)
+    t = dict(rtol=1e-6, atol=1e-6) if dtype == torch.float32 else dict(rtol=1e-2, atol=1e-2)
+    torch.testing.assert_close(got[:, :nh + nkv], qk.to(dtype).double(), **t)
+    assert torch.equal(got[:, nh + nkv:], src[:, nh + nkv:])           # v is untouched in place
+    for i, s in enumerate(slots):
+        if s < 0:
+            continue
+        p, o = divmod(s, page)
+        assert torch.equal(kc[p, :, o], x.view(T, nh + 2 * nkv, d)[i, nh:nh + nkv])    # the rotated k
+        assert torch.equal(vc[p, :, o], qkv.view(T, nh + 2 * nkv, d)[i, nh + nkv:])
+    written = torch.zeros(pages * page, dtype=torch.bool)
+    written[[s for s in slots if s >= 0]] = True
+    flat = kc.permute(0, 2, 1, 3).reshape(pages * page, nkv, d)
+    assert (flat[~written.cuda()] == 9.0).all()                        # nothing else was written
+
+
+# ---------------------------------------------------------------- attention over the paged cache
+def paged(seqs_kv, page, pages, nkv, d, dtype, seed):
+    """Put each sequence's keys and values into randomly chosen pages.  Returns caches
+    and block tables."""
+    rng = random.Random(seed)
+    free = list(range(pages))
+    rng.shuffle(free)
+    kc = torch.randn(pages, nkv, page, d, device="cuda").to(dtype) * 50    # stale data everywhere else
+    vc = torch.randn(pages, nkv, page, d, device="cuda").to(dtype) * 50
+    stride = max(-(-k.shape[0] // page) for k, _ in seqs_kv) + 2
+    bt = torch.full((len(seqs_kv), stride), -1, dtype=torch.int32)
+    for b, (k, v) in enumerate(seqs_kv):
+        for lp in range(-(-k.shape[0] // page)):
+            pg = free.pop()
+            bt[b, lp] = pg
+            n = min(page, k.shape[0] - lp * page)
+            kc[pg, :, :n] = k[lp * page:lp * page + n].transpose(0, 1)
+            vc[pg, :, :n] = v[lp * page:lp * page + n].transpose(0, 1)
+    return kc, vc, bt.cuda(), stride
+
+
+def ref_attention(q, k, v, q_start, window):
+    """q [n, nh, d] at positions q_start.., k/v [ctx, nkv, d] -> [n, nh, d] in float64."""
+    n, nh, d = q.shape
+    ctx, nkv, _ = k.shape
+    qi = torch.arange(q_start, q_start + n, device=q.device)[:, None]
+    kj = torch.arange(ctx, device=q.device)[None, :]
+    ok = kj <= qi
+    if window:
+        ok &= kj > qi - window
+    out = torch.empty(n, nh, d, dtype=torch.float64, device=q.device)
+    for h in range(nh):
+        s = q[:, h].double() @ k[:, h // (nh // nkv)].double().T / math.sqrt(d)
+        p = torch.softmax(s.masked_fill(~ok, float("-inf")), dim=-1)
+        out[:, h] = p @ v[:, h // (nh // nkv)].double()
+    return out
+
+
+def spike(q, k, v, head, nkv_of_head, key_pos, strength=30.0):
+    """Make query `head` of the last token look almost only at key `key_pos`."""
+    d = q.shape[-1]
+    u = torch.randn(d, device=q.device)
+    u /= u.norm()
+    q[-1, head] = u * strength
+    k[key_pos, nkv_of_head] = u * strength
+    v[key_pos, nkv_of_head] = torch.arange(d, device=q.device).float() / d + 3.0
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("nh,nkv,d,page,window", [
+    (4, 2, 16, 16, 0), (4, 1, 32, 8, 0), (5, 5, 48, 32, 24), (32, 8, 128, 16, 0), (8, 2, 80, 16, 100),
+    (2, 1, 256, 16, 0), (24, 1, 64, 16, 0)])
+def test_attn_decode(ops, cuda_device, dtype, nh, nkv, d, page, window):
+    torch.manual_seed(4)
+    ctxs = [1, 2, page - 1, page, page + 1, 63, 64, 65, 127, 129, 300, 777]
+    B = len(ctxs)
+    seqs, qs, refs = [], [], []
+    for i, ctx in enumerate(ctxs):
+        k, v = torch.randn(ctx, nkv, d, device="cuda"), torch.randn(ctx, nkv, d, device="cuda")
+        q = torch.randn(1, nh, d, device="cuda")
+        lo = max(0, ctx - window) if window else 0
+        far = [lo, min(ctx - 1, lo + 1), ctx - 1, (lo + ctx) // 2, max(lo, ctx - 65)][i % 5]
+        spike(q, k, v, i % nh, (i % nh) // (nh // nkv), far)
+        q, k, v = q.to(dtype), k.to(dtype), v.to(dtype)
+        seqs.append((k, v)), qs.append(q)
+        refs.append(ref_attention(q.float(), k.float(), v.float(), ctx - 1, window))
+    kc, vc, bt, stride = paged(seqs, page, sum(-(-c // page) for c in ctxs) + 5, nkv, d, dtype, 1)
+    q_all = torch.cat(qs).reshape(B, nh * d).contiguous()
+    cu = torch.arange(B + 1, dtype=torch.int32, device="cuda")
+    ctx_t = torch.tensor(ctxs, dtype=torch.int32, device="cuda")
+    order = list(range(B))
+    random.Random(2).shuffle(order)
+    dec = torch.tensor(order + [-1, -1], dtype=torch.int32, device="cuda")       # two padded entries
+    for splits in (1, 3, 8):
+        n_dec = B + 2
+        part_o = torch.full((n_dec * nh * splits * d,), float("nan"), device="cuda")
+        part_ml = torch.full((n_dec * nh * splits * 2,), float("nan"), device="cuda")
+        out = torch.zeros(B, nh * d, device="cuda", dtype=dtype)
+        ops.attn_decode(q_all, nh * d, kc, vc, bt, stride, cu, ctx_t, dec, n_dec, splits, part_o, part_ml,
+                        out, nh, nkv, d, page, window, 1 / math.sqrt(d))
+        ref = torch.cat(refs).reshape(B, nh * d)
+        torch.testing.assert_close(out.double(), ref, **tol(dtype))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("nh,nkv,d,page,window", [
+    (4, 2, 16, 16, 0), (4, 1, 32, 8, 0), (5, 5, 48, 32, 24), (32, 8, 128, 16, 0), (6, 3, 96, 16, 40)])
+def test_attn_prefill(ops, cuda_device, dtype, nh, nkv, d, page, window):
+    """Portions of several sequences in one launch: (cached before, portion length)."""
+    torch.manual_seed(5)
+    shapes = [(0, 1), (0, 2), (0, 16), (0, 17), (5, 2), (13, 40), (64, 64), (100, 33), (250, 3), (0, 130)]
+    seqs, qs, refs, q_lens = [], [], [], []
+    for i, (start, n) in enumerate(shapes):
+        ctx = start + n
+        k, v = torch.randn(ctx, nkv, d, device="cuda"), torch.randn(ctx, nkv, d, device="cuda")
+        q = torch.randn(n, nh, d, device="cuda")
+        lo = max(0, ctx - window) if window else 0
+        far = [lo, start, max(lo, start - 1), ctx - 1][i % 4]
+        spike(q, k, v, i % nh, (i % nh) // (nh // nkv), min(far, ctx - 1))
+        q, k, v = q.to(dtype), k.to(dtype), v.to(dtype)
+        seqs.append((k, v)), qs.append(q), q_lens.append(n)
+        refs.append(ref_attention(q.float(), k.float(), v.float(), start, window))
+    kc, vc, bt, stride = paged(seqs, page, sum(-(-(s + n) // page) for s, n in shapes) + 3, nkv, d, dtype, 3)
+    T = sum(q_lens)
+    # q lives inside a wider row, as in the engine's qkv buffer
+    width = nh * d + 32
+    buf = torch.randn(T, width, device="cuda").to(dtype)
+    buf[:, :nh * d] = torch.cat(qs).reshape(T, nh * d)
+    cu = torch.tensor([0] + list(torch.tensor(q_lens).cumsum(0)), dtype=torch.int32, device="cuda")
+    ctx_t = torch.tensor([s + n for s, n in shapes], dtype=torch.int32, device="cuda")
+    tiles = [(b, q0) for b, n in enumerate(q_lens) for q0 in range(0, n, 16)]
+    random.Random(6).shuffle(tiles)
+    tile_seq = torch.tensor([t[0] for t in tiles], dtype=torch.int32, device="cuda")
+    tile_q0 = torch.tensor([t[1] for t in tiles], dtype=torch.int32, device="cuda")
+    out = torch.zeros(T, nh * d, device="cuda", dtype=dtype)
+    ops.attn_prefill(buf, width, kc, vc, bt, stride, cu, ctx_t, tile_seq, tile_q0, len(tiles), out,
+                     nh, nkv, d, page, window, 1 / math.sqrt(d))
+    torch.testing.assert_close(out.double(), torch.cat(refs).reshape(T, nh * d), **tol(dtype))
+
+
+def test_attention_refuses_what_it_cannot_do(ops, cuda_device):
+    z = torch.zeros(4, device="cuda")
+    zi = torch.zeros(4, dtype=torch.int32, device="cuda")
+    with pytest.raises(ops.KernelError, match="head size"):
+        ops.attn_prefill(z, 1, z, z, zi, 1, zi, zi, zi, zi, 1, z, 2, 1, 272, 16, 0, 1.0)
+    with pytest.raises(ops.KernelError, match="multiple"):
+        ops.attn_prefill(z, 1, z, z, zi, 1, zi, zi, zi, zi, 1, z, 5, 2, 16, 16, 0, 1.0)
+
+
+# ---------------------------------------------------------------- sampling
+def test_argmax_first_maximum_wins(ops, cuda_device):
+    V = 128256 + 3
+    logits = torch.randn(5, V, device="cuda")
+    logits[0, 77] = logits[0, 90000] = 50.0
+    logits[1, V - 1] = 60.0
+    logits[2, 0] = 60.0
+    logits[3] = -1.0
+    out = torch.empty(5, dtype=torch.int32, device="cuda")
+    ops.argmax(logits, out)
+    assert out.tolist() == [77, V - 1, 0, 0, int(logits[4].argmax())]
+
+
+def test_sample_matches_the_plain_sampler(ops, cuda_device):
+    import plain_llama as P
+    torch.manual_seed(7)
+    V, R = 1013, 24
+    logits = (torch.randn(R, V) * 2.5).cuda()
+    temps = [0.0, 0.8, 1.0, 1.3, 0.5, 2.0] * 4
+    top_k = [0, 0, 50, 0, 7, 1] * 4
+    top_p = [0.0, 0.0, 0.0, 0.9, 0.7, 0.0] * 4
+    seeds = list(range(100, 100 + R))
+    draws = [i % 5 for i in range(R)]
+    out = torch.empty(R, dtype=torch.int32, device="cuda")
+    dev = lambda x, dt: torch.tensor(x, dtype=dt, device="cuda")
+    ops.sample(logits, dev(temps, torch.float32), dev(top_k, torch.int32), dev(top_p, torch.float32),
+               dev(seeds, torch.int64), dev(draws, torch.int64), out)
+    host = logits.cpu()
+    agree = 0
+    for r in range(R):
+        want = P.sample(host[r], temps[r], seeds[r], draws[r], top_k[r], top_p[r])
+        got = int(out[r])
+        if got == want:
+            agree += 1
+            continue
+        # a draw that falls within rounding of a boundary may land on the neighbour
+        p = P.probabilities(host[r], temps[r], top_k[r], top_p[r])
+        u = P.uniform_draw(seeds[r], draws[r])
+        cum = torch.cumsum(p, 0)
+        assert p[got] > 0 and abs(float(cum[got]) - u) < 1e-4 or abs(float(cum[got] - p[got]) - u) < 1e-4, \
+            f"row {r}: kernel chose {got}, plain {want}"
+    assert agree >= R - 2
+
+
+def test_sample_statistics_and_seeds(ops, cuda_device):
+    V, R = 50, 4000
+    row = torch.linspace(-2, 2, V)
+    logits = row.repeat(R, 1).cuda()
+    dev = lambda x, dt: torch.tensor(x, dtype=dt, device="cuda")
+    out = torch.empty(R, dtype=torch.int32, device="cuda")
+    args = (dev([0.7] * R, torch.float32), None, None)
+    ops.sample(logits, *args, dev([5] * R, torch.int64), dev(list(range(R)), torch.int64), out)
+    freq = torch.bincount(out.long().cpu(), minlength=V).double() / R
+    p = torch.softmax(row.double() / 0.7, 0)
+    assert float((freq - p).abs().max()) < 0.02
+    again = torch.empty_like(out)
+    ops.sample(logits, *args, dev([5] * R, torch.int64), dev(list(range(R)), torch.int64), again)
+    assert torch.equal(out, again)                                     # same seed and draw: same token
+    other = torch.empty_like(out)
+    ops.sample(logits, *args, dev([6] * R, torch.int64), dev(list(range(R)), torch.int64), other)
+    assert not torch.equal(out, other)
