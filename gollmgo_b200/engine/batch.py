@@ -49,6 +49,7 @@ class StepBatch:
     request_ids: List[object]
     q_lens: List[int]
     q_starts: List[int]
+    state_slot_list: List[int]
 
 
 def _align(n: int) -> int:
@@ -212,5 +213,6 @@ class BatchBuilder:
         sb.slot_mapping = [v(o, Tp) for o in lay.slot_mapping]
         sb.block_tables = [v(o, Bp * stride) for o in lay.block_tables]
         sb.request_ids, sb.q_lens, sb.q_starts = ids, q_lens, q_starts
+        sb.state_slot_list = [cache.state_slot(e.request_id) for e in entries]
         sb.layout = lay
         return sb

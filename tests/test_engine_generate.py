@@ -1,0 +1,176 @@
+"""Generation through the Python entry point against the plain implementation:
+greedy and seeded temperature sampling, the first tokens of a sequence, long
+decoding over many pages, a pool so small that requests are preempted and
+recomputed, and the command line."""
+import json
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+import plain_llama as P
+import tiny_configs
+import trace_tools as tt
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def models(tmp_path_factory, cuda_device):
+    tmp = str(tmp_path_factory.mktemp("models"))
+    out = {}
+    for name in ("tiny_a", "tiny_b"):
+        cfg, page, std, jitter = tiny_configs.get(name)
+        d = tt.model_folder(tmp, name, cfg, seed=21, std=std, jitter=jitter, dtype="float32")
+        out[name] = (d, cfg, page, tt.load_weights(d))
+    return out
+
+
+def near_best(weights, cfg, prompt, tokens, slack):
+    """Every token is (nearly) the plain implementation's best given the same history."""
+    logits = P.forward(weights, cfg, prompt + tokens)
+    for i, tok in enumerate(tokens):
+        row = logits[len(prompt) - 1 + i]
+        assert float(row.max() - row[tok]) <= slack * float(row.abs().max()), f"token {i} = {tok}"
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_greedy_workload_of_tiny_a(models, dtype):
+    """Three requests with prompts of 7, 13 and 1 tokens, 8 greedy tokens each."""
+    from gollmgo_b200 import Engine, SamplingParams
+    d, cfg, page, w = models["tiny_a"]
+    reqs = tt.random_requests(cfg["vocab_size"], [7, 13, 1], seed=1)
+    eng = Engine(d, dtype=dtype, block_size=page, num_blocks=16, max_batch_size=4, max_token_budget=64)
+    outs = eng.generate(list(reqs.values()), SamplingParams(max_tokens=8, ignore_eos=True))
+    for prompt, o in zip(reqs.values(), outs):
+        assert len(o.token_ids) == 8 and o.finish_reason == "length"
+        if dtype == "float32":
+            assert o.token_ids == P.generate(w, cfg, prompt, 8, cast=torch.float32)
+        else:
+            near_best(w, cfg, prompt, o.token_ids, 0.05)
+    eng.runner.cache.audit()
+    assert eng.runner.cache.free_pages() == 16
+
+
+def test_temperature_workload_of_tiny_b_is_seeded_and_batch_independent(models):
+    """Four requests (1, 5, 37, 70 tokens), prompts cut into portions of 16, 12 tokens each
+    at temperature 0.8 with a seed: equal to the plain sampler, alone or in a batch."""
+    from gollmgo_b200 import Engine, SamplingParams
+    d, cfg, page, w = models["tiny_b"]
+    reqs = list(tt.random_requests(cfg["vocab_size"], [1, 5, 37, 70], seed=2).values())
+    params = [SamplingParams(temperature=0.8, seed=1000 + i, max_tokens=12, ignore_eos=True) for i in range(4)]
+    eng = Engine(d, dtype="float32", block_size=page, num_blocks=64, max_batch_size=4,
+                 max_token_budget=48, prefill_chunk_size=16)
+    together = [o.token_ids for o in eng.generate(reqs, params)]
+    alone = [eng.generate([r], [p])[0].token_ids for r, p in zip(reqs, params)]
+    assert together == alone
+    for prompt, p, got in zip(reqs, params, together):
+        want = P.generate(w, cfg, prompt, 12, temperature=0.8, seed=p.seed, cast=torch.float32)
+        assert got == want
+    greedy = eng.generate(reqs, SamplingParams(max_tokens=12, ignore_eos=True))
+    for prompt, o in zip(reqs, greedy):
+        assert o.token_ids == P.generate(w, cfg, prompt, 12, cast=torch.float32)
+    assert eng.runner.cache.free_pages() == 64
+
+
+def test_eos_stops_and_is_delivered(models):
+    from gollmgo_b200 import Engine, SamplingParams
+    d, cfg, page, w = models["tiny_b"]
+    prompt = [9, 8, 7]
+    free_run = P.generate(w, cfg, prompt, 10, cast=torch.float32)
+    cfg2 = dict(cfg, eos_token_id=[free_run[3]])
+    d2 = os.path.join(os.path.dirname(d), "tiny_b_eos")
+    os.makedirs(d2, exist_ok=True)
+    os.link(os.path.join(d, "model.safetensors"), os.path.join(d2, "model.safetensors")) \
+        if not os.path.exists(os.path.join(d2, "model.safetensors")) else None
+    with open(os.path.join(d2, "config.json"), "w") as f:
+        json.dump(cfg2, f)
+    eng = Engine(d2, dtype="float32", block_size=page, num_blocks=16, max_batch_size=2, max_token_budget=32)
+    o = eng.generate([prompt], SamplingParams(max_tokens=10))[0]
+    stop = free_run.index(free_run[3])
+    assert o.token_ids == free_run[:stop + 1] and o.finish_reason == "stop"
+    o2 = eng.generate([prompt], SamplingParams(max_tokens=10, ignore_eos=True))[0]
+    assert o2.token_ids == free_run and o2.finish_reason == "length"
+
+
+@pytest.mark.parametrize("dtype,tol", [("float32", 1e-4), ("bfloat16", 6e-2)])
+def test_first_tokens_and_long_decoding(models, dtype, tol):
+    """Prompts of 1, 2 and 3 tokens, then 230 tokens decoded one by one through the
+    runner (captured steps included), every logit row against the whole sequence."""
+    from gollmgo_b200.config import EngineConfig
+    from gollmgo_b200.engine.batch import StepEntry
+    from gollmgo_b200.engine.runner import load_runner
+    d, cfg, page, w = models["tiny_b"]
+    runner = load_runner(d, EngineConfig(dtype=dtype, block_size=page, num_blocks=96, max_batch_size=4,
+                                         max_token_budget=64, max_model_len=256))
+    seqs = tt.random_requests(cfg["vocab_size"], [233, 234, 235], seed=3)
+    refs = tt.plain_logits(w, cfg, seqs)
+    names = list(seqs)
+    first = {n: i + 1 for i, n in enumerate(names)}
+    got = {n: [] for n in names}
+    out = runner.step([StepEntry(n, seqs[n][:first[n]], range(first[n])) for n in names]).cpu().double()
+    i = 0
+    for n in names:
+        got[n].append(out[i:i + first[n]])
+        i += first[n]
+    for t in range(1, 233):
+        step = [n for n in names if first[n] + t - 1 < len(seqs[n])]
+        out = runner.step([StepEntry(n, [seqs[n][first[n] + t - 1]], [0]) for n in step]).cpu().double()
+        for j, n in enumerate(step):
+            got[n].append(out[j:j + 1])
+    for n in names:
+        rows = torch.cat(got[n])
+        ref = refs[n][:rows.shape[0]]
+        err = ((rows - ref).abs().amax(dim=1) / ref.abs().amax(dim=1)).max()
+        assert float(err) <= tol, f"{n}: worst relative error {float(err):.2e}"
+        assert rows.shape[0] >= 230
+
+
+def test_small_pool_preempts_and_results_do_not_change(models):
+    from gollmgo_b200 import Engine, SamplingParams
+    d, cfg, page, w = models["tiny_a"]
+    reqs = list(tt.random_requests(cfg["vocab_size"], [30, 12, 25, 7, 18], seed=4).values())
+    params = SamplingParams(max_tokens=40, ignore_eos=True)
+    roomy = Engine(d, dtype="float32", block_size=page, num_blocks=64, max_batch_size=8, max_token_budget=64)
+    want = [o.token_ids for o in roomy.generate(reqs, params)]
+    assert roomy.stats.preemptions == 0
+    tight = Engine(d, dtype="float32", block_size=page, num_blocks=9, max_batch_size=8,
+                   max_token_budget=40, prefill_chunk_size=16)
+    outs = tight.generate(reqs, params)
+    assert [o.token_ids for o in outs] == want
+    assert tight.stats.preemptions > 0 and sum(o.preemptions for o in outs) == tight.stats.preemptions
+    tight.runner.cache.audit()
+    assert tight.runner.cache.free_pages() == 9
+    assert want[0] == P.generate(w, cfg, reqs[0], 40, cast=torch.float32)
+
+
+def test_requests_that_cannot_fit_are_refused(models):
+    from gollmgo_b200 import Engine, SamplingParams
+    from gollmgo_b200.engine import RequestTooLong
+    d, cfg, page, w = models["tiny_a"]
+    eng = Engine(d, dtype="float32", block_size=page, num_blocks=4, max_batch_size=2, max_token_budget=64)
+    with pytest.raises(RequestTooLong):
+        eng.enqueue(list(range(60)), SamplingParams(max_tokens=10))
+    with pytest.raises(ValueError, match="outside"):
+        eng.enqueue([1, 2, 9999], SamplingParams(max_tokens=2))
+
+
+def test_command_line_generate_and_bench(models):
+    d, cfg, page, w = models["tiny_a"]
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    base = [sys.executable, "-m", "gollmgo_b200"]
+    common = ["--model", d, "--dtype", "float32", "--block-size", str(page), "--num-blocks", "32",
+              "--max-batch-size", "4", "--max-token-budget", "64", "--log-level", "error"]
+    p = subprocess.run(base + ["generate", *common, "--prompt-ids", "5,6,7", "--prompt-ids", "9",
+                               "--max-tokens", "5", "--ignore-eos"], capture_output=True, text=True, cwd=root)
+    assert p.returncode == 0, p.stderr
+    lines = [json.loads(l) for l in p.stdout.strip().splitlines()]
+    assert lines[0]["token_ids"] == P.generate(w, cfg, [5, 6, 7], 5, cast=torch.float32)
+    assert lines[1]["token_ids"] == P.generate(w, cfg, [9], 5, cast=torch.float32)
+    p = subprocess.run(base + ["bench", *common, "--mode", "offline", "--num-prompts", "6", "--prompt-len", "10",
+                               "--output-len", "4"], capture_output=True, text=True, cwd=root)
+    assert p.returncode == 0, p.stderr
+    res = json.loads(p.stdout)
+    assert res["num_prompts"] == 6 and res["tokens_per_second"] > 0 and res["error_count"] == 0
