@@ -15,33 +15,11 @@
 // The reference's prompt kernel (kernels/gollmgo_ops.cu:377-446) reads only the
 // current call's keys and masks by position alone; this one does not share those
 // two properties.
-#include "common.cuh"
+#include "attention_common.cuh"
 
 #define ATT_BQ 16
 #define ATT_BK 64
 #define ATT_THREADS 128
-
-struct AttnArgs {
-  const void* q;            // [T, q_stride]: head h of token t at q + t*q_stride + h*d
-  long long q_stride;
-  const void* kcache;       // [num_pages, nkv, page_size, d]
-  const void* vcache;
-  const int* block_tables;  // [B, bt_stride]; -1 = page given back (behind the window)
-  int bt_stride;
-  const int* cu_q_lens;     // [B+1]
-  const int* context_lens;  // [B] tokens in the cache after this step's write
-  void* out;                // [T, nh*d]
-  int nh, nkv, d, page_size, window;
-  float scale;
-  // prompt portions
-  const int* tile_seq;      // [num_tiles]
-  const int* tile_q0;       // [num_tiles] offset of the tile in the sequence's portion
-  // decoded tokens
-  const int* dec_seqs;      // [n_dec] sequence indices with exactly one query token
-  int num_splits;
-  float* part_o;            // [n_dec, nh, num_splits, d]
-  float* part_ml;           // [n_dec, nh, num_splits, 2]
-};
 
 template <typename TA, int DMAX>
 __device__ __forceinline__ void attn_tile(const AttnArgs& a, int nrows, const TA* const* qptr_s,
@@ -300,25 +278,53 @@ template <typename K> static int set_smem(K kernel, size_t bytes, const char* wh
     }                                                                                          \
   } while (0)
 
+int attn_prefill_general(const AttnArgs& a, int dtype, int num_tiles, cudaStream_t stream) {
+  GG_REQUIRE(num_tiles >= 0 && a.nh <= 65535, "attn_prefill: bad grid %d x %d", num_tiles, a.nh);
+  if (num_tiles == 0) return GG_OK;
+  dim3 grid(num_tiles, a.nh);
+  ATT_DISPATCH(attn_prefill_kernel, grid, "attn_prefill");
+  return gg_check_launch("attn_prefill");
+}
+
+int attn_decode_general(const AttnArgs& a, int dtype, int n_dec, cudaStream_t stream) {
+  const int G = a.nh / a.nkv, gchunks = (G + ATT_BQ - 1) / ATT_BQ;
+  GG_REQUIRE(a.nkv * gchunks <= 65535 && a.nh <= 65535, "attn_decode: too many heads");
+  dim3 grid(n_dec, a.nkv * gchunks, a.num_splits);
+  ATT_DISPATCH(attn_decode_kernel, grid, "attn_decode");
+  return gg_check_launch("attn_decode");
+}
+
+int attn_merge_launch(const AttnArgs& a, int dtype, int n_dec, cudaStream_t stream) {
+  dim3 mgrid(n_dec, a.nh);
+  const int mthreads = a.d >= 128 ? 128 : (a.d >= 64 ? 64 : 32);
+  if (dtype == GG_F32) attn_merge_kernel<float><<<mgrid, mthreads, 0, stream>>>(a);
+  else attn_merge_kernel<__nv_bfloat16><<<mgrid, mthreads, 0, stream>>>(a);
+  return gg_check_launch("attn_merge");
+}
+
+// tile_seq/tile_q0 describe tiles of 16 queries (the general kernel) and
+// tile64_seq/tile64_q0 tiles of 64 queries (the tensor-core kernel); the launcher
+// picks the kernel from dtype and head size.
 extern "C" int gg_attn_prefill(const void* q, long long q_stride, const void* kcache,
                                const void* vcache, int dtype, const int* block_tables,
                                int bt_stride, const int* cu_q_lens, const int* context_lens,
-                               const int* tile_seq, const int* tile_q0, int num_tiles, void* out,
-                               int nh, int nkv, int d, int page_size, int window, float scale,
-                               cudaStream_t stream) {
+                               const int* tile_seq, const int* tile_q0, int num_tiles,
+                               const int* tile64_seq, const int* tile64_q0, int num_tiles64,
+                               void* out, int nh, int nkv, int d, int page_size, int window,
+                               float scale, int allow_mma, cudaStream_t stream) {
   AttnArgs a = {};
   a.q = q; a.q_stride = q_stride; a.kcache = kcache; a.vcache = vcache;
   a.block_tables = block_tables; a.bt_stride = bt_stride; a.cu_q_lens = cu_q_lens;
   a.context_lens = context_lens; a.out = out; a.nh = nh; a.nkv = nkv; a.d = d;
   a.page_size = page_size; a.window = window; a.scale = scale;
-  a.tile_seq = tile_seq; a.tile_q0 = tile_q0;
   int rc = check_common(a, "attn_prefill");
   if (rc) return rc;
-  GG_REQUIRE(num_tiles >= 0 && nh <= 65535, "attn_prefill: bad grid %d x %d", num_tiles, nh);
-  if (num_tiles == 0) return GG_OK;
-  dim3 grid(num_tiles, nh);
-  ATT_DISPATCH(attn_prefill_kernel, grid, "attn_prefill");
-  return gg_check_launch("attn_prefill");
+  if (allow_mma && tile64_seq && attn_mma_supported(dtype, d) && q_stride % 8 == 0) {
+    a.tile_seq = tile64_seq; a.tile_q0 = tile64_q0;
+    return attn_prefill_mma(a, num_tiles64, stream);
+  }
+  a.tile_seq = tile_seq; a.tile_q0 = tile_q0;
+  return attn_prefill_general(a, dtype, num_tiles, stream);
 }
 
 // Scratch the caller provides: part_o float[n_dec * nh * num_splits * d],
@@ -328,7 +334,7 @@ extern "C" int gg_attn_decode(const void* q, long long q_stride, const void* kca
                               int bt_stride, const int* cu_q_lens, const int* context_lens,
                               const int* dec_seqs, int n_dec, int num_splits, float* part_o,
                               float* part_ml, void* out, int nh, int nkv, int d, int page_size,
-                              int window, float scale, cudaStream_t stream) {
+                              int window, float scale, int allow_mma, cudaStream_t stream) {
   AttnArgs a = {};
   a.q = q; a.q_stride = q_stride; a.kcache = kcache; a.vcache = vcache;
   a.block_tables = block_tables; a.bt_stride = bt_stride; a.cu_q_lens = cu_q_lens;
@@ -340,15 +346,10 @@ extern "C" int gg_attn_decode(const void* q, long long q_stride, const void* kca
   GG_REQUIRE(n_dec >= 0 && num_splits >= 1 && num_splits <= 65535, "attn_decode: bad n_dec %d or splits %d", n_dec, num_splits);
   GG_REQUIRE(part_o && part_ml, "attn_decode: no scratch given");
   if (n_dec == 0) return GG_OK;
-  const int G = nh / nkv, gchunks = (G + ATT_BQ - 1) / ATT_BQ;
-  GG_REQUIRE(nkv * gchunks <= 65535 && nh <= 65535, "attn_decode: too many heads");
-  dim3 grid(n_dec, nkv * gchunks, num_splits);
-  ATT_DISPATCH(attn_decode_kernel, grid, "attn_decode");
-  rc = gg_check_launch("attn_decode");
+  if (allow_mma && attn_mma_supported(dtype, d) && q_stride % 2 == 0)
+    rc = attn_decode_mma(a, n_dec, stream);
+  else
+    rc = attn_decode_general(a, dtype, n_dec, stream);
   if (rc) return rc;
-  dim3 mgrid(n_dec, nh);
-  const int mthreads = d >= 128 ? 128 : (d >= 64 ? 64 : 32);
-  if (dtype == GG_F32) attn_merge_kernel<float><<<mgrid, mthreads, 0, stream>>>(a);
-  else attn_merge_kernel<__nv_bfloat16><<<mgrid, mthreads, 0, stream>>>(a);
-  return gg_check_launch("attn_merge");
+  return attn_merge_launch(a, dtype, n_dec, stream);
 }

@@ -1,0 +1,69 @@
+// Argument block shared by the attention kernels, and the tensor-core helpers of
+// the bfloat16 fast path (mma.sync m16n8k16, ldmatrix, cp.async, shared-memory swizzle).
+#pragma once
+#include "common.cuh"
+
+struct AttnArgs {
+  const void* q;            // [T, q_stride]: head h of token t at q + t*q_stride + h*d
+  long long q_stride;
+  const void* kcache;       // [num_pages, nkv, page_size, d]
+  const void* vcache;
+  const int* block_tables;  // [B, bt_stride]; -1 = page given back (behind the window)
+  int bt_stride;
+  const int* cu_q_lens;     // [B+1]
+  const int* context_lens;  // [B] tokens in the cache after this step's write
+  void* out;                // [T, nh*d]
+  int nh, nkv, d, page_size, window;
+  float scale;
+  // prompt portions
+  const int* tile_seq;      // [num_tiles]
+  const int* tile_q0;       // [num_tiles] offset of the tile in the sequence's portion
+  // decoded tokens
+  const int* dec_seqs;      // [n_dec] sequence indices with exactly one query token; -1 = padding
+  int num_splits;
+  float* part_o;            // [n_dec, nh, num_splits, d]
+  float* part_ml;           // [n_dec, nh, num_splits, 2]
+};
+
+// General kernels (attention.cu)
+int attn_prefill_general(const AttnArgs& a, int dtype, int num_tiles, cudaStream_t stream);
+int attn_decode_general(const AttnArgs& a, int dtype, int n_dec, cudaStream_t stream);
+int attn_merge_launch(const AttnArgs& a, int dtype, int n_dec, cudaStream_t stream);
+// bfloat16 tensor-core kernels for head sizes 64 and 128 (attention_mma.cu)
+bool attn_mma_supported(int dtype, int d);
+int attn_prefill_mma(const AttnArgs& a, int num_tiles, cudaStream_t stream);   // tiles of 64 queries
+int attn_decode_mma(const AttnArgs& a, int n_dec, cudaStream_t stream);
+
+__device__ __forceinline__ unsigned smem_u32(const void* p) {
+  return (unsigned)__cvta_generic_to_shared(p);
+}
+__device__ __forceinline__ void cp_async16(unsigned dst, const void* src, int src_bytes) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(dst), "l"(src), "r"(src_bytes));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N> __device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;\n" ::"n"(N));
+}
+__device__ __forceinline__ void ldmatrix_x4(unsigned& r0, unsigned& r1, unsigned& r2, unsigned& r3, unsigned addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(unsigned& r0, unsigned& r1, unsigned& r2, unsigned& r3, unsigned addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+// D(16x8, f32) += A(16x16, bf16, row) * B(16x8, bf16, col)
+__device__ __forceinline__ void mma_bf16(float* c, const unsigned* a, unsigned b0, unsigned b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm volatile("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<unsigned*>(&v);
+}

@@ -1,0 +1,409 @@
+// Attention over the paged cache on the tensor cores, bfloat16, head sizes 64 and 128.
+//
+// Same contract as the general kernels in attention.cu (same formulas: kv head =
+// head / (nh/nkv), scale 1/sqrt(d), causal by absolute position, optional window,
+// keys only from the cache through the block table), different machinery:
+//   * keys and values of 64 tokens at a time are brought to shared memory with
+//     16-byte cp.async copies (zero-filled past the end or where a page was given
+//     back), three stages deep for decode and two for prompts, in a layout whose
+//     16-byte columns are XOR-swizzled by the row so ldmatrix has no bank conflicts;
+//   * scores S = Q K^T and outputs O += P V are mma.sync m16n8k16 (bf16 in, f32
+//     accumulate); P goes from the score accumulators straight into the A operand;
+//   * softmax is online in float32 with base-2 exponentials (scores are scaled by
+//     scale * log2(e)).
+// Decode: one CTA per (token, kv head [x 16 heads of its group], slice of the
+// context); the 16 rows of the A operand are the query heads that share the kv
+// head, so every key and value is read once per group; the four warps take 16
+// keys each of every 64 and are combined through shared memory at the end.
+// Prompt portions: one CTA per (64 queries of a sequence, head); a warp owns 16
+// query rows.
+#include "attention_common.cuh"
+
+#define MMA_THREADS 128
+#define MMA_BK 64
+#define LOG2E 1.4426950408889634f
+
+bool attn_mma_supported(int dtype, int d) { return dtype == GG_BF16 && (d == 64 || d == 128); }
+
+// Shared-memory tile [64 rows][D] bf16; the 16-byte chunk c of row r sits at chunk c ^ (r & 7).
+template <int D> __device__ __forceinline__ unsigned tile_off(int row, int chunk) {
+  return (unsigned)(row * D * 2 + ((chunk ^ (row & 7)) << 4));
+}
+
+// Bring keys and values of tokens [k0, k0+64) of one sequence and kv head to a stage.
+// Tokens outside [lo, hi) and pages that were given back are zero-filled.
+template <int D>
+__device__ __forceinline__ void load_kv_tile(const AttnArgs& a, const int* bt, int kvh, int k0, int lo,
+                                             int hi, unsigned ks, unsigned vs) {
+  constexpr int CPR = D / 8;                       // 16-byte chunks per row
+  constexpr int ROWS_PER_PASS = MMA_THREADS / CPR;
+  const __nv_bfloat16* kc = (const __nv_bfloat16*)a.kcache;
+  const __nv_bfloat16* vc = (const __nv_bfloat16*)a.vcache;
+  const int ch = threadIdx.x % CPR, r0 = threadIdx.x / CPR;
+  const int ps = a.page_size;
+#pragma unroll
+  for (int i = 0; i < MMA_BK / ROWS_PER_PASS; ++i) {
+    const int row = r0 + i * ROWS_PER_PASS;
+    const int tok = k0 + row;
+    int page = -1;
+    if (tok >= lo && tok < hi) page = __ldg(bt + tok / ps);
+    const size_t src = page >= 0 ? (((size_t)page * a.nkv + kvh) * ps + (tok % ps)) * D + ch * 8 : 0;
+    const int bytes = page >= 0 ? 16 : 0;
+    const unsigned off = tile_off<D>(row, ch);
+    cp_async16(ks + off, kc + src, bytes);
+    cp_async16(vs + off, vc + src, bytes);
+  }
+}
+
+// Scores of 16 query rows against NT*8 keys (rows key0.. of the staged tile).
+template <int D, int NT>
+__device__ __forceinline__ void qk_mma(const unsigned (*qf)[4], unsigned ks, int key0, float (*s)[4]) {
+  const int lane = threadIdx.x & 31;
+#pragma unroll
+  for (int j = 0; j < NT; ++j) { s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f; }
+#pragma unroll
+  for (int kk = 0; kk < D / 16; ++kk) {
+#pragma unroll
+    for (int j = 0; j < NT; j += 2) {
+      // four 8x8 matrices: (keys j*8.., d chunk 2kk), (same keys, chunk 2kk+1), (keys (j+1)*8.., 2kk), (.., 2kk+1)
+      const int mi = lane >> 3;
+      const int row = key0 + (j + (mi >> 1)) * 8 + (lane & 7);
+      unsigned b0, b1, b2, b3;
+      ldmatrix_x4(b0, b1, b2, b3, ks + tile_off<D>(row, 2 * kk + (mi & 1)));
+      mma_bf16(s[j], qf[kk], b0, b1);
+      mma_bf16(s[j + 1], qf[kk], b2, b3);
+    }
+  }
+}
+
+// O(16 x D) += P(16 x NT*8) V(NT*8 x D); p holds NT/2 A-operand fragments.
+template <int D, int NT>
+__device__ __forceinline__ void pv_mma(const unsigned (*p)[4], unsigned vs, int key0, float (*o)[4]) {
+  const int lane = threadIdx.x & 31;
+#pragma unroll
+  for (int kk = 0; kk < NT / 2; ++kk) {
+#pragma unroll
+    for (int nt = 0; nt < D / 8; nt += 2) {
+      // (keys kk*16.. +8, d chunk nt), (keys +8.. +16, chunk nt), (keys ..+8, chunk nt+1), (keys +8.., chunk nt+1)
+      const int mi = lane >> 3;
+      const int row = key0 + kk * 16 + (mi & 1) * 8 + (lane & 7);
+      unsigned b0, b1, b2, b3;
+      ldmatrix_x4_trans(b0, b1, b2, b3, vs + tile_off<D>(row, nt + (mi >> 1)));
+      mma_bf16(o[nt], p[kk], b0, b1);
+      mma_bf16(o[nt + 1], p[kk], b2, b3);
+    }
+  }
+}
+
+// One online-softmax update of a warp's 16 rows with NT*8 new scores (already scaled
+// to base 2 and masked with -inf).  Thread holds rows g = lane/4 (regs 0,1) and g+8 (2,3).
+template <int D, int NT>
+__device__ __forceinline__ void softmax_update(float (*s)[4], float* m, float* l, float (*o)[4],
+                                               unsigned (*p)[4]) {
+  float mx0 = -INFINITY, mx1 = -INFINITY;
+#pragma unroll
+  for (int j = 0; j < NT; ++j) {
+    mx0 = fmaxf(mx0, fmaxf(s[j][0], s[j][1]));
+    mx1 = fmaxf(mx1, fmaxf(s[j][2], s[j][3]));
+  }
+  mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
+  mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
+  mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
+  mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+  const float mn0 = fmaxf(m[0], mx0), mn1 = fmaxf(m[1], mx1);
+  const float ref0 = mn0 == -INFINITY ? 0.f : mn0, ref1 = mn1 == -INFINITY ? 0.f : mn1;
+  const float al0 = fast_exp2(m[0] - ref0), al1 = fast_exp2(m[1] - ref1);
+  m[0] = mn0;
+  m[1] = mn1;
+  float sum0 = 0.f, sum1 = 0.f;
+#pragma unroll
+  for (int j = 0; j < NT; ++j) {
+    s[j][0] = fast_exp2(s[j][0] - ref0);
+    s[j][1] = fast_exp2(s[j][1] - ref0);
+    s[j][2] = fast_exp2(s[j][2] - ref1);
+    s[j][3] = fast_exp2(s[j][3] - ref1);
+    sum0 += s[j][0] + s[j][1];
+    sum1 += s[j][2] + s[j][3];
+  }
+  l[0] = l[0] * al0 + sum0;          // per-thread partial sums; the quad is reduced at the end
+  l[1] = l[1] * al1 + sum1;
+#pragma unroll
+  for (int nt = 0; nt < D / 8; ++nt) {
+    o[nt][0] *= al0; o[nt][1] *= al0; o[nt][2] *= al1; o[nt][3] *= al1;
+  }
+#pragma unroll
+  for (int kk = 0; kk < NT / 2; ++kk) {
+    p[kk][0] = pack_bf16(s[2 * kk][0], s[2 * kk][1]);
+    p[kk][1] = pack_bf16(s[2 * kk][2], s[2 * kk][3]);
+    p[kk][2] = pack_bf16(s[2 * kk + 1][0], s[2 * kk + 1][1]);
+    p[kk][3] = pack_bf16(s[2 * kk + 1][2], s[2 * kk + 1][3]);
+  }
+}
+
+// A-operand fragments of 16 query rows: row r of the tile is at qrow(r) (null = zero row).
+template <int D, typename F>
+__device__ __forceinline__ void load_q_frags(unsigned (*qf)[4], F qrow) {
+  const int lane = threadIdx.x & 31, g = lane >> 2, c = (lane & 3) * 2;
+  const __nv_bfloat16* r0 = qrow(g);
+  const __nv_bfloat16* r1 = qrow(g + 8);
+#pragma unroll
+  for (int kk = 0; kk < D / 16; ++kk) {
+    qf[kk][0] = r0 ? *reinterpret_cast<const unsigned*>(r0 + kk * 16 + c) : 0u;
+    qf[kk][1] = r1 ? *reinterpret_cast<const unsigned*>(r1 + kk * 16 + c) : 0u;
+    qf[kk][2] = r0 ? *reinterpret_cast<const unsigned*>(r0 + kk * 16 + c + 8) : 0u;
+    qf[kk][3] = r1 ? *reinterpret_cast<const unsigned*>(r1 + kk * 16 + c + 8) : 0u;
+  }
+}
+
+// ---------------------------------------------------------------- decoded tokens
+template <int D, int STAGES>
+__global__ void __launch_bounds__(MMA_THREADS) attn_decode_mma_kernel(AttnArgs a) {
+  extern __shared__ __align__(128) unsigned char smem_raw[];
+  constexpr int TILE_BYTES = MMA_BK * D * 2;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, c2 = (lane & 3) * 2;
+  const int G = a.nh / a.nkv, gchunks = (G + 15) / 16;
+  const int b = a.dec_seqs[blockIdx.x];
+  const int kvh = blockIdx.y / gchunks, g0 = (blockIdx.y % gchunks) * 16;
+  const int split = blockIdx.z, S = a.num_splits;
+  const int nrows = min(16, G - g0);
+  const int ctx = b >= 0 ? a.context_lens[b] : 0;
+  const int t = b >= 0 ? a.cu_q_lens[b] : 0;
+  const int lo0 = a.window > 0 ? max(0, ctx - a.window) : 0;
+  const int n = ctx - lo0;
+  int chunk = (n + S - 1) / S;
+  chunk = ((chunk + MMA_BK - 1) / MMA_BK) * MMA_BK;
+  const int lo = lo0 + split * chunk, hi = min(ctx, lo + chunk);
+  const int head0 = kvh * G + g0;
+
+  float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+  float o[D / 8][4];
+#pragma unroll
+  for (int nt = 0; nt < D / 8; ++nt) { o[nt][0] = o[nt][1] = o[nt][2] = o[nt][3] = 0.f; }
+
+  if (lo < hi) {
+    const int* bt = a.block_tables + (size_t)b * a.bt_stride;
+    const unsigned base = smem_u32(smem_raw);
+    const int ntiles = (hi - lo + MMA_BK - 1) / MMA_BK;
+#pragma unroll
+    for (int s = 0; s < STAGES - 1; ++s) {
+      if (s < ntiles) load_kv_tile<D>(a, bt, kvh, lo + s * MMA_BK, lo, hi, base + s * 2 * TILE_BYTES, base + s * 2 * TILE_BYTES + TILE_BYTES);
+      cp_async_commit();
+    }
+    unsigned qf[D / 16][4];
+    const __nv_bfloat16* qbase = (const __nv_bfloat16*)a.q + (size_t)t * a.q_stride + (size_t)head0 * D;
+    load_q_frags<D>(qf, [&](int r) { return r < nrows ? qbase + (size_t)r * D : nullptr; });
+    const float sc = a.scale * LOG2E;
+    for (int it = 0; it < ntiles; ++it) {
+      const int nx = it + STAGES - 1;
+      if (nx < ntiles) {
+        const int st = nx % STAGES;
+        load_kv_tile<D>(a, bt, kvh, lo + nx * MMA_BK, lo, hi, base + st * 2 * TILE_BYTES, base + st * 2 * TILE_BYTES + TILE_BYTES);
+      }
+      cp_async_commit();
+      cp_async_wait<STAGES - 1>();
+      __syncthreads();
+      const int st = it % STAGES;
+      const unsigned ks = base + st * 2 * TILE_BYTES, vs = ks + TILE_BYTES;
+      const int key0 = warp * 16;                        // this warp's 16 keys of the tile
+      const int tok0 = lo + it * MMA_BK + key0;
+      if (tok0 < hi) {
+        float s[2][4];
+        qk_mma<D, 2>(qf, ks, key0, s);
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+          const int tk = tok0 + j * 8 + c2;
+          s[j][0] = tk < hi ? s[j][0] * sc : -INFINITY;
+          s[j][2] = tk < hi ? s[j][2] * sc : -INFINITY;
+          s[j][1] = tk + 1 < hi ? s[j][1] * sc : -INFINITY;
+          s[j][3] = tk + 1 < hi ? s[j][3] * sc : -INFINITY;
+        }
+        unsigned p[1][4];
+        softmax_update<D, 2>(s, m, l, o, p);
+        pv_mma<D, 2>(p, vs, key0, o);
+      }
+      __syncthreads();
+    }
+    cp_async_wait<0>();
+  }
+  // ---- combine the four warps: (m, l, o) of each through shared memory
+  l[0] += __shfl_xor_sync(0xffffffffu, l[0], 1);
+  l[0] += __shfl_xor_sync(0xffffffffu, l[0], 2);
+  l[1] += __shfl_xor_sync(0xffffffffu, l[1], 1);
+  l[1] += __shfl_xor_sync(0xffffffffu, l[1], 2);
+  float* cm = reinterpret_cast<float*>(smem_raw);          // [4][16]
+  float* cl = cm + 64;                                     // [4][16]
+  float* co = cl + 64;                                     // [4][16][D]
+  __syncthreads();
+  if ((lane & 3) == 0) {
+    cm[warp * 16 + g] = m[0]; cm[warp * 16 + g + 8] = m[1];
+    cl[warp * 16 + g] = l[0]; cl[warp * 16 + g + 8] = l[1];
+  }
+#pragma unroll
+  for (int nt = 0; nt < D / 8; ++nt) {
+    float* r0 = co + ((size_t)warp * 16 + g) * D + nt * 8 + c2;
+    float* r1 = co + ((size_t)warp * 16 + g + 8) * D + nt * 8 + c2;
+    r0[0] = o[nt][0]; r0[1] = o[nt][1];
+    r1[0] = o[nt][2]; r1[1] = o[nt][3];
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e < nrows * D; e += MMA_THREADS) {
+    const int r = e / D, col = e - r * D;
+    float M = fmaxf(fmaxf(cm[r], cm[16 + r]), fmaxf(cm[32 + r], cm[48 + r]));
+    float L = 0.f, acc = 0.f;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) {
+      const float mw = cm[w * 16 + r];
+      if (mw != -INFINITY) {
+        const float f = fast_exp2(mw - M);
+        L += f * cl[w * 16 + r];
+        acc += f * co[((size_t)w * 16 + r) * D + col];
+      }
+    }
+    const size_t row = ((size_t)blockIdx.x * a.nh + head0 + r) * S + split;
+    a.part_o[row * D + col] = acc;
+    if (col == 0) {
+      // the merge kernel works with natural exponentials: hand it m in that base
+      a.part_ml[row * 2] = M == -INFINITY ? -INFINITY : M * (1.0f / LOG2E);
+      a.part_ml[row * 2 + 1] = L;
+    }
+  }
+}
+
+// ---------------------------------------------------------------- prompt portions
+template <int D>
+__global__ void __launch_bounds__(MMA_THREADS) attn_prefill_mma_kernel(AttnArgs a) {
+  extern __shared__ __align__(128) unsigned char smem_raw[];
+  constexpr int TILE_BYTES = MMA_BK * D * 2;
+  constexpr int STAGES = 2;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, c2 = (lane & 3) * 2;
+  const int b = a.tile_seq[blockIdx.x], q0 = a.tile_q0[blockIdx.x];
+  const int h = blockIdx.y, kvh = h / (a.nh / a.nkv);
+  const int t0 = a.cu_q_lens[b], qlen = a.cu_q_lens[b + 1] - t0;
+  const int ctx = a.context_lens[b];
+  const int qstart = ctx - qlen;
+  const int nrows = min(64, qlen - q0);
+  const int first = qstart + q0;                     // position of the tile's first query
+  const int hi = first + nrows;
+  const int lo = a.window > 0 ? max(0, first - a.window + 1) : 0;
+  const int kstart = (lo / MMA_BK) * MMA_BK;
+  const int ntiles = (hi - kstart + MMA_BK - 1) / MMA_BK;
+  const int* bt = a.block_tables + (size_t)b * a.bt_stride;
+  const unsigned base = smem_u32(smem_raw);
+
+  load_kv_tile<D>(a, bt, kvh, kstart, lo, hi, base, base + TILE_BYTES);
+  cp_async_commit();
+
+  const int wrow0 = warp * 16;                       // this warp's rows of the tile
+  const int pos0 = first + wrow0 + g, pos1 = pos0 + 8;   // positions of the thread's two rows
+  unsigned qf[D / 16][4];
+  const __nv_bfloat16* qbase = (const __nv_bfloat16*)a.q + (size_t)(t0 + q0 + wrow0) * a.q_stride + (size_t)h * D;
+  load_q_frags<D>(qf, [&](int r) { return wrow0 + r < nrows ? qbase + (size_t)r * a.q_stride : nullptr; });
+  const bool row0_ok = wrow0 + g < nrows, row1_ok = wrow0 + g + 8 < nrows;
+  const int wlast = first + min(wrow0 + 15, nrows - 1);  // last position this warp needs
+
+  float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+  float o[D / 8][4];
+#pragma unroll
+  for (int nt = 0; nt < D / 8; ++nt) { o[nt][0] = o[nt][1] = o[nt][2] = o[nt][3] = 0.f; }
+  const float sc = a.scale * LOG2E;
+
+  for (int it = 0; it < ntiles; ++it) {
+    if (it + 1 < ntiles) {
+      const int st = (it + 1) % STAGES;
+      load_kv_tile<D>(a, bt, kvh, kstart + (it + 1) * MMA_BK, lo, hi, base + st * 2 * TILE_BYTES, base + st * 2 * TILE_BYTES + TILE_BYTES);
+    }
+    cp_async_commit();
+    cp_async_wait<STAGES - 1>();
+    __syncthreads();
+    const int st = it % STAGES;
+    const unsigned ks = base + st * 2 * TILE_BYTES, vs = ks + TILE_BYTES;
+    const int kb = kstart + it * MMA_BK;
+    if (wrow0 < nrows && kb <= wlast) {
+      float s[8][4];
+      qk_mma<D, 8>(qf, ks, 0, s);
+      const bool interior = kb >= lo && kb + MMA_BK - 1 <= first + wrow0 &&
+                            (a.window <= 0 || kb > wlast - a.window);
+      if (interior) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) { s[j][0] *= sc; s[j][1] *= sc; s[j][2] *= sc; s[j][3] *= sc; }
+      } else {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const int tk = kb + j * 8 + c2 + (e & 1);
+            const int pos = (e & 2) ? pos1 : pos0;
+            const bool ok = ((e & 2) ? row1_ok : row0_ok) && tk >= lo && tk <= pos &&
+                            (a.window <= 0 || tk > pos - a.window);
+            s[j][e] = ok ? s[j][e] * sc : -INFINITY;
+          }
+        }
+      }
+      unsigned p[4][4];
+      softmax_update<D, 8>(s, m, l, o, p);
+      pv_mma<D, 8>(p, vs, 0, o);
+    }
+    __syncthreads();
+  }
+  cp_async_wait<0>();
+  l[0] += __shfl_xor_sync(0xffffffffu, l[0], 1);
+  l[0] += __shfl_xor_sync(0xffffffffu, l[0], 2);
+  l[1] += __shfl_xor_sync(0xffffffffu, l[1], 1);
+  l[1] += __shfl_xor_sync(0xffffffffu, l[1], 2);
+  const float inv0 = l[0] > 0.f ? 1.f / l[0] : 0.f, inv1 = l[1] > 0.f ? 1.f / l[1] : 0.f;
+  __nv_bfloat16* out = (__nv_bfloat16*)a.out;
+  const size_t ostride = (size_t)a.nh * D;
+#pragma unroll
+  for (int nt = 0; nt < D / 8; ++nt) {
+    const int col = nt * 8 + c2;
+    if (row0_ok)
+      *reinterpret_cast<unsigned*>(out + (size_t)(t0 + q0 + wrow0 + g) * ostride + (size_t)h * D + col) =
+          pack_bf16(o[nt][0] * inv0, o[nt][1] * inv0);
+    if (row1_ok)
+      *reinterpret_cast<unsigned*>(out + (size_t)(t0 + q0 + wrow0 + g + 8) * ostride + (size_t)h * D + col) =
+          pack_bf16(o[nt][2] * inv1, o[nt][3] * inv1);
+  }
+}
+
+// ---------------------------------------------------------------- launchers
+template <typename K> static int opt_in_smem(K kernel, size_t bytes, const char* who) {
+  if (bytes > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+    if (e != cudaSuccess) return gg_fail(GG_ERR_CUDA, "%s: %s", who, cudaGetErrorString(e));
+  }
+  return GG_OK;
+}
+
+int attn_decode_mma(const AttnArgs& a, int n_dec, cudaStream_t stream) {
+  const int G = a.nh / a.nkv, gchunks = (G + 15) / 16;
+  GG_REQUIRE(a.nkv * gchunks <= 65535, "attn_decode: too many heads");
+  dim3 grid(n_dec, a.nkv * gchunks, a.num_splits);
+  constexpr int STAGES = 3;
+  int rc;
+  if (a.d == 128) {
+    const size_t smem = (size_t)STAGES * 2 * MMA_BK * 128 * 2;       // 96 KB; the combine needs 33 KB of it
+    if ((rc = opt_in_smem(attn_decode_mma_kernel<128, STAGES>, smem, "attn_decode"))) return rc;
+    attn_decode_mma_kernel<128, STAGES><<<grid, MMA_THREADS, smem, stream>>>(a);
+  } else {
+    const size_t smem = (size_t)STAGES * 2 * MMA_BK * 64 * 2;        // 48 KB; the combine needs 17 KB
+    if ((rc = opt_in_smem(attn_decode_mma_kernel<64, STAGES>, smem, "attn_decode"))) return rc;
+    attn_decode_mma_kernel<64, STAGES><<<grid, MMA_THREADS, smem, stream>>>(a);
+  }
+  return gg_check_launch("attn_decode_mma");
+}
+
+int attn_prefill_mma(const AttnArgs& a, int num_tiles, cudaStream_t stream) {
+  GG_REQUIRE(num_tiles >= 0 && a.nh <= 65535, "attn_prefill: bad grid %d x %d", num_tiles, a.nh);
+  if (num_tiles == 0) return GG_OK;
+  dim3 grid(num_tiles, a.nh);
+  int rc;
+  if (a.d == 128) {
+    const size_t smem = (size_t)2 * 2 * MMA_BK * 128 * 2;            // 64 KB
+    if ((rc = opt_in_smem(attn_prefill_mma_kernel<128>, smem, "attn_prefill"))) return rc;
+    attn_prefill_mma_kernel<128><<<grid, MMA_THREADS, smem, stream>>>(a);
+  } else {
+    const size_t smem = (size_t)2 * 2 * MMA_BK * 64 * 2;             // 32 KB
+    attn_prefill_mma_kernel<64><<<grid, MMA_THREADS, smem, stream>>>(a);
+  }
+  return gg_check_launch("attn_prefill_mma");
+}

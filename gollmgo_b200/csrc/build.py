@@ -122,6 +122,12 @@ def ensure_built(verbose: bool = True) -> str:
     if p.returncode != 0:
         raise BuildError(f"link failed:\n{p.stdout}\n{p.stderr}")
     os.replace(tmp_so, so)
+    for old in glob.glob(os.path.join(build_dir, "libgollmgo_b200_*.so")):
+        if old != so:                      # builds of older sources
+            try:
+                os.remove(old)
+            except OSError:
+                pass
     shutil.rmtree(obj_dir, ignore_errors=True)
     _log(f"built {os.path.basename(so)} in {time.time() - t0:.0f} s", verbose)
     return so

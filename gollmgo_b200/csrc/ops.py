@@ -137,20 +137,25 @@ def attn_prefill(q: torch.Tensor, q_stride: int, kcache: torch.Tensor, vcache: t
                  block_tables: torch.Tensor, bt_stride: int, cu_q_lens: torch.Tensor,
                  context_lens: torch.Tensor, tile_seq: torch.Tensor, tile_q0: torch.Tensor,
                  num_tiles: int, out: torch.Tensor, nh: int, nkv: int, d: int, page_size: int,
-                 window: int, scale: float) -> None:
-    """Causal attention of prompt portions over the paged cache (general kernel)."""
+                 window: int, scale: float, tile64_seq: Optional[torch.Tensor] = None,
+                 tile64_q0: Optional[torch.Tensor] = None, num_tiles64: int = 0,
+                 allow_mma: bool = True) -> None:
+    """Causal attention of prompt portions over the paged cache.  ``tile_*`` list tiles
+    of 16 queries (general kernel), ``tile64_*`` tiles of 64 (tensor-core kernel, used
+    for bfloat16 with head size 64 or 128 when the lists are given)."""
     _check(lib().gg_attn_prefill(_p(q), ctypes.c_longlong(q_stride), _p(kcache), _p(vcache),
                                  dtype_code(kcache.dtype), _p(block_tables), bt_stride,
                                  _p(cu_q_lens), _p(context_lens), _p(tile_seq), _p(tile_q0),
-                                 num_tiles, _p(out), nh, nkv, d, page_size, window,
-                                 ctypes.c_float(scale), _stream()))
+                                 num_tiles, _p(tile64_seq), _p(tile64_q0), num_tiles64, _p(out),
+                                 nh, nkv, d, page_size, window, ctypes.c_float(scale),
+                                 int(allow_mma), _stream()))
 
 
 def attn_decode(q: torch.Tensor, q_stride: int, kcache: torch.Tensor, vcache: torch.Tensor,
                 block_tables: torch.Tensor, bt_stride: int, cu_q_lens: torch.Tensor,
                 context_lens: torch.Tensor, dec_seqs: torch.Tensor, n_dec: int, num_splits: int,
                 part_o: torch.Tensor, part_ml: torch.Tensor, out: torch.Tensor, nh: int, nkv: int,
-                d: int, page_size: int, window: int, scale: float) -> None:
+                d: int, page_size: int, window: int, scale: float, allow_mma: bool = True) -> None:
     """Attention of single decoded tokens, split over the context and merged."""
     if part_o.numel() < n_dec * nh * num_splits * d or part_ml.numel() < n_dec * nh * num_splits * 2:
         raise KernelError("attn_decode: scratch too small")
@@ -158,7 +163,7 @@ def attn_decode(q: torch.Tensor, q_stride: int, kcache: torch.Tensor, vcache: to
                                 dtype_code(kcache.dtype), _p(block_tables), bt_stride,
                                 _p(cu_q_lens), _p(context_lens), _p(dec_seqs), n_dec, num_splits,
                                 _p(part_o), _p(part_ml), _p(out), nh, nkv, d, page_size, window,
-                                ctypes.c_float(scale), _stream()), 2)
+                                ctypes.c_float(scale), int(allow_mma), _stream()), 2)
 
 
 def argmax(logits: torch.Tensor, out: torch.Tensor) -> None:

@@ -15,7 +15,8 @@ from typing import List, Optional, Sequence
 import numpy as np
 import torch
 
-ATTN_TILE_ROWS = 16        # query rows of one attention tile (csrc/attention.cu: ATT_BQ)
+ATTN_TILE_ROWS = 16        # query rows of one tile of the general attention kernel (ATT_BQ)
+ATTN_TILE_ROWS_MMA = 64    # ... and of the tensor-core kernel (csrc/attention_mma.cu)
 
 
 @dataclass
@@ -42,6 +43,9 @@ class StepBatch:
     logit_rows: torch.Tensor
     tile_seq: torch.Tensor
     tile_q0: torch.Tensor
+    tile64_seq: torch.Tensor
+    tile64_q0: torch.Tensor
+    num_tiles64: int
     dec_seqs: torch.Tensor
     slot_mapping: List[torch.Tensor]
     block_tables: List[torch.Tensor]
@@ -59,8 +63,9 @@ def _align(n: int) -> int:
 class BatchLayout:
     """Offsets of every array in the packed int32 buffer, for given capacities."""
 
-    def __init__(self, T: int, B: int, R: int, NT: int, ND: int, G: int, stride: int):
+    def __init__(self, T: int, B: int, R: int, NT: int, ND: int, G: int, stride: int, NT64: int = 0):
         self.T, self.B, self.R, self.NT, self.ND, self.G, self.stride = T, B, R, NT, ND, G, stride
+        self.NT64 = NT64
         off = 0
 
         def take(n):
@@ -77,6 +82,8 @@ class BatchLayout:
         self.logit_rows = take(R)
         self.tile_seq = take(NT)
         self.tile_q0 = take(NT)
+        self.tile64_seq = take(NT64)
+        self.tile64_q0 = take(NT64)
         self.dec_seqs = take(ND)
         self.block_tables = [take(B * stride) for _ in range(G)]
         self.size = off
@@ -138,6 +145,8 @@ class BatchBuilder:
         q_starts = [a.start for a in appended]
         T = sum(q_lens)
         tiles = [(b, q0) for b in range(B) if q_lens[b] > 1 for q0 in range(0, q_lens[b], ATTN_TILE_ROWS)]
+        tiles64 = [(b, q0) for b in range(B) if q_lens[b] > 1
+                   for q0 in range(0, q_lens[b], ATTN_TILE_ROWS_MMA)]
         dec = [b for b in range(B) if q_lens[b] == 1]
         max_pages = max(len(cache.block_table(e.request_id, g)) for e in entries for g in range(G)) if G else 1
         Bp = fixed_seqs if fixed_seqs is not None else B
@@ -153,7 +162,7 @@ class BatchBuilder:
             base += n
         rows.extend(range(T, Tp))    # ... whose logits are computed and ignored
         R = len(rows)
-        lay = BatchLayout(Tp, Bp, R, len(tiles), len(dec) + (Bp - B), G, stride)
+        lay = BatchLayout(Tp, Bp, R, len(tiles), len(dec) + (Bp - B), G, stride, len(tiles64))
         if static_dev is None:
             self._ensure(lay.size)
             if self._copied is not None:
@@ -181,6 +190,8 @@ class BatchBuilder:
         if tiles:
             h[lay.tile_seq:lay.tile_seq + len(tiles)] = [t[0] for t in tiles]
             h[lay.tile_q0:lay.tile_q0 + len(tiles)] = [t[1] for t in tiles]
+            h[lay.tile64_seq:lay.tile64_seq + len(tiles64)] = [t[0] for t in tiles64]
+            h[lay.tile64_q0:lay.tile64_q0 + len(tiles64)] = [t[1] for t in tiles64]
         nd = len(dec) + (Bp - B)
         h[lay.dec_seqs:lay.dec_seqs + len(dec)] = dec
         h[lay.dec_seqs + len(dec):lay.dec_seqs + nd] = -1
@@ -209,6 +220,8 @@ class BatchBuilder:
         sb.cu_q_lens, sb.context_lens = v(lay.cu_q_lens, Bp + 1), v(lay.context_lens, Bp)
         sb.state_slots, sb.logit_rows = v(lay.state_slots, Bp), v(lay.logit_rows, R)[:R]
         sb.tile_seq, sb.tile_q0 = v(lay.tile_seq, len(tiles)), v(lay.tile_q0, len(tiles))
+        sb.tile64_seq, sb.tile64_q0 = v(lay.tile64_seq, len(tiles64)), v(lay.tile64_q0, len(tiles64))
+        sb.num_tiles64 = len(tiles64)
         sb.dec_seqs = v(lay.dec_seqs, nd)
         sb.slot_mapping = [v(o, Tp) for o in lay.slot_mapping]
         sb.block_tables = [v(o, Bp * stride) for o in lay.block_tables]

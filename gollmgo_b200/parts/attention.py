@@ -93,7 +93,8 @@ class Attention:
         if batch.num_tiles:
             ops.attn_prefill(qkv, self.qkv_width, kc, vc, bt, batch.bt_stride, batch.cu_q_lens,
                              batch.context_lens, batch.tile_seq, batch.tile_q0, batch.num_tiles,
-                             out, self.nh, self.nkv, self.d, self.ctx.page_size, window, self.scale)
+                             out, self.nh, self.nkv, self.d, self.ctx.page_size, window, self.scale,
+                             batch.tile64_seq, batch.tile64_q0, batch.num_tiles64)
         if batch.num_decode:
             splits = decode_splits(batch.num_decode, self._ctas_per_split, self.num_sms)
             ops.attn_decode(qkv, self.qkv_width, kc, vc, bt, batch.bt_stride, batch.cu_q_lens,

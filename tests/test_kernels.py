@@ -181,11 +181,14 @@ def spike(q, k, v, head, nkv_of_head, key_pos, strength=30.0):
     v[key_pos, nkv_of_head] = torch.arange(d, device=q.device).float() / d + 3.0
 
 
+@pytest.mark.parametrize("allow_mma", [False, True])
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("nh,nkv,d,page,window", [
     (4, 2, 16, 16, 0), (4, 1, 32, 8, 0), (5, 5, 48, 32, 24), (32, 8, 128, 16, 0), (8, 2, 80, 16, 100),
-    (2, 1, 256, 16, 0), (24, 1, 64, 16, 0)])
-def test_attn_decode(ops, cuda_device, dtype, nh, nkv, d, page, window):
+    (2, 1, 256, 16, 0), (24, 1, 64, 16, 0), (6, 2, 64, 8, 70), (40, 2, 128, 32, 0), (3, 3, 128, 16, 33)])
+def test_attn_decode(ops, cuda_device, dtype, nh, nkv, d, page, window, allow_mma):
+    if allow_mma and not (dtype == torch.bfloat16 and d in (64, 128)):
+        pytest.skip("the tensor-core kernel takes bfloat16 with head size 64 or 128")
     torch.manual_seed(4)
     ctxs = [1, 2, page - 1, page, page + 1, 63, 64, 65, 127, 129, 300, 777]
     B = len(ctxs)
@@ -212,18 +215,23 @@ def test_attn_decode(ops, cuda_device, dtype, nh, nkv, d, page, window):
         part_ml = torch.full((n_dec * nh * splits * 2,), float("nan"), device="cuda")
         out = torch.zeros(B, nh * d, device="cuda", dtype=dtype)
         ops.attn_decode(q_all, nh * d, kc, vc, bt, stride, cu, ctx_t, dec, n_dec, splits, part_o, part_ml,
-                        out, nh, nkv, d, page, window, 1 / math.sqrt(d))
+                        out, nh, nkv, d, page, window, 1 / math.sqrt(d), allow_mma=allow_mma)
         ref = torch.cat(refs).reshape(B, nh * d)
         torch.testing.assert_close(out.double(), ref, **tol(dtype))
 
 
+@pytest.mark.parametrize("allow_mma", [False, True])
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("nh,nkv,d,page,window", [
-    (4, 2, 16, 16, 0), (4, 1, 32, 8, 0), (5, 5, 48, 32, 24), (32, 8, 128, 16, 0), (6, 3, 96, 16, 40)])
-def test_attn_prefill(ops, cuda_device, dtype, nh, nkv, d, page, window):
+    (4, 2, 16, 16, 0), (4, 1, 32, 8, 0), (5, 5, 48, 32, 24), (32, 8, 128, 16, 0), (6, 3, 96, 16, 40),
+    (6, 2, 64, 8, 0), (3, 1, 64, 32, 50), (5, 5, 128, 16, 70)])
+def test_attn_prefill(ops, cuda_device, dtype, nh, nkv, d, page, window, allow_mma):
     """Portions of several sequences in one launch: (cached before, portion length)."""
+    if allow_mma and not (dtype == torch.bfloat16 and d in (64, 128)):
+        pytest.skip("the tensor-core kernel takes bfloat16 with head size 64 or 128")
     torch.manual_seed(5)
-    shapes = [(0, 1), (0, 2), (0, 16), (0, 17), (5, 2), (13, 40), (64, 64), (100, 33), (250, 3), (0, 130)]
+    shapes = [(0, 1), (0, 2), (0, 16), (0, 17), (5, 2), (13, 40), (64, 64), (100, 33), (250, 3), (0, 130),
+              (1, 63), (63, 65), (0, 64), (7, 200)]
     seqs, qs, refs, q_lens = [], [], [], []
     for i, (start, n) in enumerate(shapes):
         ctx = start + n
@@ -247,9 +255,14 @@ def test_attn_prefill(ops, cuda_device, dtype, nh, nkv, d, page, window):
     random.Random(6).shuffle(tiles)
     tile_seq = torch.tensor([t[0] for t in tiles], dtype=torch.int32, device="cuda")
     tile_q0 = torch.tensor([t[1] for t in tiles], dtype=torch.int32, device="cuda")
+    tiles64 = [(b, q0) for b, n in enumerate(q_lens) for q0 in range(0, n, 64)]
+    random.Random(7).shuffle(tiles64)
+    t64_seq = torch.tensor([t[0] for t in tiles64], dtype=torch.int32, device="cuda")
+    t64_q0 = torch.tensor([t[1] for t in tiles64], dtype=torch.int32, device="cuda")
     out = torch.zeros(T, nh * d, device="cuda", dtype=dtype)
     ops.attn_prefill(buf, width, kc, vc, bt, stride, cu, ctx_t, tile_seq, tile_q0, len(tiles), out,
-                     nh, nkv, d, page, window, 1 / math.sqrt(d))
+                     nh, nkv, d, page, window, 1 / math.sqrt(d), t64_seq, t64_q0, len(tiles64),
+                     allow_mma=allow_mma)
     torch.testing.assert_close(out.double(), torch.cat(refs).reshape(T, nh * d), **tol(dtype))
 
 
