@@ -136,6 +136,7 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_prefill_kernel(AttnArgs a) {
   extern __shared__ float smem[];
   __shared__ const TA* qptr_s[ATT_BQ];
   __shared__ int pos_s[ATT_BQ];
+  pdl_wait();
   const int b = a.tile_seq[blockIdx.x], q0 = a.tile_q0[blockIdx.x];
   const int h = blockIdx.y, kvh = h / (a.nh / a.nkv);
   const int t0 = a.cu_q_lens[b], qlen = a.cu_q_lens[b + 1] - t0;
@@ -152,6 +153,7 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_prefill_kernel(AttnArgs a) {
   const int lo = a.window > 0 ? max(0, first - a.window + 1) : 0;
   float acc[NACC];
   attn_tile<TA, DMAX>(a, nrows, qptr_s, pos_s, kvh, a.block_tables + (size_t)b * a.bt_stride, lo, last + 1, smem, acc);
+  pdl_trigger();
   const float* l_s = smem + ATT_BQ * a.d + ATT_BK * (a.d + 1) + ATT_BK * a.d + ATT_BQ * ATT_BK + ATT_BQ;
   TA* out = (TA*)a.out;
 #pragma unroll
@@ -174,6 +176,7 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_decode_kernel(AttnArgs a) {
   extern __shared__ float smem[];
   __shared__ const TA* qptr_s[ATT_BQ];
   __shared__ int pos_s[ATT_BQ];
+  pdl_wait();
   const int G = a.nh / a.nkv, gchunks = (G + ATT_BQ - 1) / ATT_BQ;
   const int b = a.dec_seqs[blockIdx.x];
   const int kvh = blockIdx.y / gchunks, g0 = (blockIdx.y % gchunks) * ATT_BQ;
@@ -199,6 +202,7 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_decode_kernel(AttnArgs a) {
 #pragma unroll
     for (int i = 0; i < NACC; ++i) acc[i] = 0.f;
   }
+  pdl_trigger();
   const float* m_s = smem + ATT_BQ * a.d + ATT_BK * (a.d + 1) + ATT_BK * a.d + ATT_BQ * ATT_BK;
   const float* l_s = m_s + ATT_BQ;
 #pragma unroll
@@ -222,6 +226,8 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_decode_kernel(AttnArgs a) {
 // (kernels/gollmgo_paged_attn.cu:331-384).  grid (n_dec, nh), one thread per column.
 template <typename TA>
 __global__ void attn_merge_kernel(AttnArgs a) {
+  pdl_trigger();
+  pdl_wait();
   const int b = a.dec_seqs[blockIdx.x];
   if (b < 0) return;
   const int h = blockIdx.y, S = a.num_splits, d = a.d;
@@ -266,13 +272,13 @@ template <typename K> static int set_smem(K kernel, size_t bytes, const char* wh
     const size_t smem = (size_t)attn_smem_floats<0>(a.d) * sizeof(float);                      \
     int rc = GG_OK;                                                                            \
     if (dtype == GG_F32) {                                                                     \
-      if (a.d <= 64) { rc = set_smem(KERNEL<float, 64>, smem, who); if (rc) return rc; KERNEL<float, 64><<<grid, ATT_THREADS, smem, stream>>>(a); } \
-      else if (a.d <= 128) { rc = set_smem(KERNEL<float, 128>, smem, who); if (rc) return rc; KERNEL<float, 128><<<grid, ATT_THREADS, smem, stream>>>(a); } \
-      else { rc = set_smem(KERNEL<float, 256>, smem, who); if (rc) return rc; KERNEL<float, 256><<<grid, ATT_THREADS, smem, stream>>>(a); } \
+      if (a.d <= 64) { rc = set_smem(KERNEL<float, 64>, smem, who); if (rc) return rc; gg_launch(KERNEL<float, 64>, dim3(grid), dim3(ATT_THREADS), smem, stream, a); } \
+      else if (a.d <= 128) { rc = set_smem(KERNEL<float, 128>, smem, who); if (rc) return rc; gg_launch(KERNEL<float, 128>, dim3(grid), dim3(ATT_THREADS), smem, stream, a); } \
+      else { rc = set_smem(KERNEL<float, 256>, smem, who); if (rc) return rc; gg_launch(KERNEL<float, 256>, dim3(grid), dim3(ATT_THREADS), smem, stream, a); } \
     } else if (dtype == GG_BF16) {                                                             \
-      if (a.d <= 64) { rc = set_smem(KERNEL<__nv_bfloat16, 64>, smem, who); if (rc) return rc; KERNEL<__nv_bfloat16, 64><<<grid, ATT_THREADS, smem, stream>>>(a); } \
-      else if (a.d <= 128) { rc = set_smem(KERNEL<__nv_bfloat16, 128>, smem, who); if (rc) return rc; KERNEL<__nv_bfloat16, 128><<<grid, ATT_THREADS, smem, stream>>>(a); } \
-      else { rc = set_smem(KERNEL<__nv_bfloat16, 256>, smem, who); if (rc) return rc; KERNEL<__nv_bfloat16, 256><<<grid, ATT_THREADS, smem, stream>>>(a); } \
+      if (a.d <= 64) { rc = set_smem(KERNEL<__nv_bfloat16, 64>, smem, who); if (rc) return rc; gg_launch(KERNEL<__nv_bfloat16, 64>, dim3(grid), dim3(ATT_THREADS), smem, stream, a); } \
+      else if (a.d <= 128) { rc = set_smem(KERNEL<__nv_bfloat16, 128>, smem, who); if (rc) return rc; gg_launch(KERNEL<__nv_bfloat16, 128>, dim3(grid), dim3(ATT_THREADS), smem, stream, a); } \
+      else { rc = set_smem(KERNEL<__nv_bfloat16, 256>, smem, who); if (rc) return rc; gg_launch(KERNEL<__nv_bfloat16, 256>, dim3(grid), dim3(ATT_THREADS), smem, stream, a); } \
     } else {                                                                                   \
       return gg_fail(GG_ERR_INVALID, "%s: unknown dtype %d", who, dtype);                      \
     }                                                                                          \
@@ -297,8 +303,8 @@ int attn_decode_general(const AttnArgs& a, int dtype, int n_dec, cudaStream_t st
 int attn_merge_launch(const AttnArgs& a, int dtype, int n_dec, cudaStream_t stream) {
   dim3 mgrid(n_dec, a.nh);
   const int mthreads = a.d >= 128 ? 128 : (a.d >= 64 ? 64 : 32);
-  if (dtype == GG_F32) attn_merge_kernel<float><<<mgrid, mthreads, 0, stream>>>(a);
-  else attn_merge_kernel<__nv_bfloat16><<<mgrid, mthreads, 0, stream>>>(a);
+  if (dtype == GG_F32) gg_launch(attn_merge_kernel<float>, dim3(mgrid), dim3(mthreads), 0, stream, a);
+  else gg_launch(attn_merge_kernel<__nv_bfloat16>, dim3(mgrid), dim3(mthreads), 0, stream, a);
   return gg_check_launch("attn_merge");
 }
 

@@ -161,6 +161,7 @@ __global__ void __launch_bounds__(MMA_THREADS) attn_decode_mma_kernel(AttnArgs a
   extern __shared__ __align__(128) unsigned char smem_raw[];
   constexpr int TILE_BYTES = MMA_BK * D * 2;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, c2 = (lane & 3) * 2;
+  pdl_wait();
   const int G = a.nh / a.nkv, gchunks = (G + 15) / 16;
   const int b = a.dec_seqs[blockIdx.x];
   const int kvh = blockIdx.y / gchunks, g0 = (blockIdx.y % gchunks) * 16;
@@ -225,6 +226,7 @@ __global__ void __launch_bounds__(MMA_THREADS) attn_decode_mma_kernel(AttnArgs a
     }
     cp_async_wait<0>();
   }
+  pdl_trigger();
   // ---- combine the four warps: (m, l, o) of each through shared memory
   l[0] += __shfl_xor_sync(0xffffffffu, l[0], 1);
   l[0] += __shfl_xor_sync(0xffffffffu, l[0], 2);
@@ -276,6 +278,7 @@ __global__ void __launch_bounds__(MMA_THREADS) attn_prefill_mma_kernel(AttnArgs 
   constexpr int TILE_BYTES = MMA_BK * D * 2;
   constexpr int STAGES = 2;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, c2 = (lane & 3) * 2;
+  pdl_wait();
   const int b = a.tile_seq[blockIdx.x], q0 = a.tile_q0[blockIdx.x];
   const int h = blockIdx.y, kvh = h / (a.nh / a.nkv);
   const int t0 = a.cu_q_lens[b], qlen = a.cu_q_lens[b + 1] - t0;
@@ -346,6 +349,7 @@ __global__ void __launch_bounds__(MMA_THREADS) attn_prefill_mma_kernel(AttnArgs 
     __syncthreads();
   }
   cp_async_wait<0>();
+  pdl_trigger();
   l[0] += __shfl_xor_sync(0xffffffffu, l[0], 1);
   l[0] += __shfl_xor_sync(0xffffffffu, l[0], 2);
   l[1] += __shfl_xor_sync(0xffffffffu, l[1], 1);
@@ -383,11 +387,11 @@ int attn_decode_mma(const AttnArgs& a, int n_dec, cudaStream_t stream) {
   if (a.d == 128) {
     const size_t smem = (size_t)STAGES * 2 * MMA_BK * 128 * 2;       // 96 KB; the combine needs 33 KB of it
     if ((rc = opt_in_smem(attn_decode_mma_kernel<128, STAGES>, smem, "attn_decode"))) return rc;
-    attn_decode_mma_kernel<128, STAGES><<<grid, MMA_THREADS, smem, stream>>>(a);
+    gg_launch(attn_decode_mma_kernel<128, STAGES>, dim3(grid), dim3(MMA_THREADS), smem, stream, a);
   } else {
     const size_t smem = (size_t)STAGES * 2 * MMA_BK * 64 * 2;        // 48 KB; the combine needs 17 KB
     if ((rc = opt_in_smem(attn_decode_mma_kernel<64, STAGES>, smem, "attn_decode"))) return rc;
-    attn_decode_mma_kernel<64, STAGES><<<grid, MMA_THREADS, smem, stream>>>(a);
+    gg_launch(attn_decode_mma_kernel<64, STAGES>, dim3(grid), dim3(MMA_THREADS), smem, stream, a);
   }
   return gg_check_launch("attn_decode_mma");
 }
@@ -400,10 +404,10 @@ int attn_prefill_mma(const AttnArgs& a, int num_tiles, cudaStream_t stream) {
   if (a.d == 128) {
     const size_t smem = (size_t)2 * 2 * MMA_BK * 128 * 2;            // 64 KB
     if ((rc = opt_in_smem(attn_prefill_mma_kernel<128>, smem, "attn_prefill"))) return rc;
-    attn_prefill_mma_kernel<128><<<grid, MMA_THREADS, smem, stream>>>(a);
+    gg_launch(attn_prefill_mma_kernel<128>, dim3(grid), dim3(MMA_THREADS), smem, stream, a);
   } else {
     const size_t smem = (size_t)2 * 2 * MMA_BK * 64 * 2;             // 32 KB
-    attn_prefill_mma_kernel<64><<<grid, MMA_THREADS, smem, stream>>>(a);
+    gg_launch(attn_prefill_mma_kernel<64>, dim3(grid), dim3(MMA_THREADS), smem, stream, a);
   }
   return gg_check_launch("attn_prefill_mma");
 }

@@ -22,6 +22,35 @@ int gg_check_launch(const char* what);
     if (!(cond)) return gg_fail(GG_ERR_INVALID, __VA_ARGS__);   \
   } while (0)
 
+// Programmatic dependent launch.  Every kernel of this library is launched so that it
+// may start while its predecessor in the stream is still draining: its blocks are
+// scheduled (and may read data no kernel writes, such as weights) and then block in
+// pdl_wait() until the predecessor has completed and its writes are visible.  A
+// kernel calls pdl_wait() before it reads anything another kernel produced and
+// before its first write, and pdl_trigger() once the grid that follows may be
+// scheduled.  Without a predecessor launched this way both are no-ops.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+// True unless GOLLMGO_B200_NO_PDL is set in the environment.
+bool gg_pdl_enabled();
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t gg_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                             cudaStream_t stream, Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = gg_pdl_enabled() ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
 __device__ __forceinline__ float to_f32(float x) { return x; }
 __device__ __forceinline__ float to_f32(__nv_bfloat16 x) { return __bfloat162float(x); }
 template <typename T> __device__ __forceinline__ T from_f32(float x);

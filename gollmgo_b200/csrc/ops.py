@@ -166,6 +166,36 @@ def attn_decode(q: torch.Tensor, q_stride: int, kcache: torch.Tensor, vcache: to
                                 ctypes.c_float(scale), int(allow_mma), _stream()), 2)
 
 
+SMALL_M = 16          # most tokens gemm_small_m takes
+
+
+def small_m_ok(x: torch.Tensor, w: torch.Tensor) -> bool:
+    """Whether out = x @ w^T can go through gemm_small_m."""
+    return (x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.is_cuda
+            and 0 < x.shape[0] <= SMALL_M and x.shape[1] % 8 == 0 and x.stride(1) == 1
+            and x.stride(0) % 8 == 0 and w.is_contiguous())
+
+
+def gemm_small_m(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, gated: bool = False) -> None:
+    """out[M, N] = x[M, K] @ w[N, K]^T for M <= 16 (bfloat16 in, float32 accumulate); out is
+    bfloat16 or float32.  ``gated``: w is [2N, K] (gate rows, then up rows) and
+    out = silu(x Wg^T) * (x Wu^T) in bfloat16."""
+    M, K = x.shape
+    N = out.shape[1]
+    if w.shape != ((2 * N, K) if gated else (N, K)) or out.shape[0] != M or not out.is_contiguous():
+        raise KernelError("gemm_small_m: shapes do not fit")
+    if gated:
+        if out.dtype != torch.bfloat16:
+            raise KernelError("gemm_small_m: the gated product writes bfloat16")
+        mode = 2
+    else:
+        mode = 1 if out.dtype == torch.float32 else 0
+        if out.dtype not in (torch.float32, torch.bfloat16):
+            raise KernelError("gemm_small_m: out must be bfloat16 or float32")
+    _check(lib().gg_gemm_small_m(_p(x), ctypes.c_longlong(x.stride(0)), _p(w), _p(out), M, N, K, mode,
+                                 _stream()))
+
+
 def argmax(logits: torch.Tensor, out: torch.Tensor) -> None:
     """out[r] = first index of the maximum of logits[r, :] (float32 [R, V])."""
     _cuda(logits, out)

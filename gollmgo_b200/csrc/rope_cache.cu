@@ -23,6 +23,8 @@ __global__ void rope_kv_write_kernel(TA* __restrict__ qkv, const int* __restrict
                                      TA* __restrict__ vcache, int nh, int nkv, int d, int rot,
                                      int page_size, int interleaved, int write_cache) {
   extern __shared__ float cs[];        // cos[rot/2], sin[rot/2]
+  pdl_trigger();
+  pdl_wait();
   const int t = blockIdx.x;
   const int half = rot >> 1;
   if (inv_freq) {
@@ -91,9 +93,9 @@ extern "C" int gg_rope_kv_write(void* qkv, int act_dtype, const int* positions,
   GG_REQUIRE(smem <= 48 * 1024, "rope_kv_write: rotary width %d too large", rot);
   const int threads = 256;
   if (act_dtype == GG_F32)
-    rope_kv_write_kernel<float><<<T, threads, smem, stream>>>((float*)qkv, positions, slot_mapping, inv_freq, (float*)kcache, (float*)vcache, nh, nkv, d, rot, page_size, interleaved, write_cache);
+    gg_launch(rope_kv_write_kernel<float>, dim3(T), dim3(threads), smem, stream, (float*)qkv, positions, slot_mapping, inv_freq, (float*)kcache, (float*)vcache, nh, nkv, d, rot, page_size, interleaved, write_cache);
   else if (act_dtype == GG_BF16)
-    rope_kv_write_kernel<__nv_bfloat16><<<T, threads, smem, stream>>>((__nv_bfloat16*)qkv, positions, slot_mapping, inv_freq, (__nv_bfloat16*)kcache, (__nv_bfloat16*)vcache, nh, nkv, d, rot, page_size, interleaved, write_cache);
+    gg_launch(rope_kv_write_kernel<__nv_bfloat16>, dim3(T), dim3(threads), smem, stream, (__nv_bfloat16*)qkv, positions, slot_mapping, inv_freq, (__nv_bfloat16*)kcache, (__nv_bfloat16*)vcache, nh, nkv, d, rot, page_size, interleaved, write_cache);
   else
     return gg_fail(GG_ERR_INVALID, "rope_kv_write: unknown dtype %d", act_dtype);
   return gg_check_launch("rope_kv_write");

@@ -63,6 +63,8 @@ __device__ int block_argmax(const float* row, int V, float* red_f, int* red_i, f
 __global__ void argmax_kernel(const float* __restrict__ logits, int V, int* __restrict__ out) {
   __shared__ float red_f[33];
   __shared__ int red_i[33];
+  pdl_trigger();
+  pdl_wait();
   const int r = blockIdx.x;
   const int idx = block_argmax(logits + (size_t)r * V, V, red_f, red_i, nullptr);
   if (threadIdx.x == 0) out[r] = idx;
@@ -117,6 +119,8 @@ sample_kernel(const float* __restrict__ logits, int V, const float* __restrict__
   __shared__ float hist[258];
   __shared__ float scan[SAMPLE_THREADS / 32 + 1];
   __shared__ int found;
+  pdl_trigger();
+  pdl_wait();
   const int r = blockIdx.x;
   const float* row = logits + (size_t)r * V;
   const float T = temperature[r];
@@ -189,7 +193,7 @@ sample_kernel(const float* __restrict__ logits, int V, const float* __restrict__
 extern "C" int gg_argmax(const float* logits, int R, int V, int* out, cudaStream_t stream) {
   GG_REQUIRE(R >= 0 && V > 0, "argmax: bad sizes R=%d V=%d", R, V);
   if (R == 0) return GG_OK;
-  argmax_kernel<<<R, SAMPLE_THREADS, 0, stream>>>(logits, V, out);
+  gg_launch(argmax_kernel, dim3(R), dim3(SAMPLE_THREADS), 0, stream, logits, V, out);
   return gg_check_launch("argmax");
 }
 
@@ -199,6 +203,6 @@ extern "C" int gg_sample(const float* logits, int R, int V, const float* tempera
   GG_REQUIRE(R >= 0 && V > 0, "sample: bad sizes R=%d V=%d", R, V);
   GG_REQUIRE(temperature != nullptr, "sample: no temperatures given");
   if (R == 0) return GG_OK;
-  sample_kernel<<<R, SAMPLE_THREADS, 0, stream>>>(logits, V, temperature, top_k, top_p, seeds, draw_index, out);
+  gg_launch(sample_kernel, dim3(R), dim3(SAMPLE_THREADS), 0, stream, logits, V, temperature, top_k, top_p, seeds, draw_index, out);
   return gg_check_launch("sample");
 }

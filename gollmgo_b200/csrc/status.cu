@@ -1,6 +1,7 @@
 // Error reporting shared by all launchers, and the library's version probe.
 #include <stdarg.h>
 #include <stdio.h>
+#include <stdlib.h>
 
 #include "common.cuh"
 
@@ -18,6 +19,15 @@ int gg_check_launch(const char* what) {
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return gg_fail(GG_ERR_CUDA, "%s: %s", what, cudaGetErrorString(e));
   return GG_OK;
+}
+
+bool gg_pdl_enabled() {
+  static int on = -1;
+  if (on < 0) {
+    const char* v = getenv("GOLLMGO_B200_NO_PDL");
+    on = (v && v[0] && v[0] != '0') ? 0 : 1;
+  }
+  return on == 1;
 }
 
 extern "C" const char* gg_last_error() { return g_err; }

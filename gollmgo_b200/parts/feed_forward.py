@@ -43,10 +43,13 @@ class GatedMLP:
     def forward(self, x, batch):
         T = x.shape[0]
         ws = self.ctx.workspace
-        gu = ws.get("gate_up", T, 2 * self.inter)
-        linear(x, self.w_gate_up, gu)
         a = ws.get("ffn_act", T, self.inter)
-        ops.silu_mul(gu, a)
+        if ops.small_m_ok(x, self.w_gate_up):
+            ops.gemm_small_m(x, self.w_gate_up, a, gated=True)       # product and activation in one
+        else:
+            gu = ws.get("gate_up", T, 2 * self.inter)
+            linear(x, self.w_gate_up, gu)
+            ops.silu_mul(gu, a)
         y = ws.get("ffn_out", T, self.hidden)
         linear(a, self.w_down, y)
         return y

@@ -1,5 +1,7 @@
-"""Matrix products of the model: out = x @ w^T through the vendor library, as in
-the reference (cublasGemmEx with float32 accumulation: kernels/gollmgo_model.cu:143-169).
+"""Matrix products of the model: out = x @ w^T.  Steps of up to 16 tokens in
+bfloat16 go through this package's weight-streaming kernel (csrc/gemm_small_m.cu);
+everything else through the vendor library, as in the reference (cublasGemmEx with
+float32 accumulation: kernels/gollmgo_model.cu:143-169).
 
 In the float32 mode the product is a true float32 one: the TF32 matrix mode and
 reduced-precision accumulation are switched off for the process by
@@ -10,6 +12,8 @@ from __future__ import annotations
 from typing import Optional
 
 import torch
+
+from ..csrc import ops
 
 
 def set_matmul_precision() -> None:
@@ -24,7 +28,9 @@ def set_matmul_precision() -> None:
 def linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
     """out[T, N] = x[T, K] @ w[N, K]^T, rounded to out's dtype.  A weight stored in
     float32 is multiplied in float32 even when the activations are bfloat16."""
-    if w.dtype == x.dtype and out.dtype == x.dtype:
+    if ops.small_m_ok(x, w) and out.is_contiguous():
+        ops.gemm_small_m(x, w, out)          # a few tokens: the weight-streaming kernel
+    elif w.dtype == x.dtype and out.dtype == x.dtype:
         torch.mm(x, w.t(), out=out)
     elif w.dtype == x.dtype and out.dtype == torch.float32:
         out.copy_(torch.mm(x, w.t(), out_dtype=torch.float32))

@@ -336,3 +336,49 @@ def test_sample_statistics_and_seeds(ops, cuda_device):
     other = torch.empty_like(out)
     ops.sample(logits, *args, dev([6] * R, torch.int64), dev(list(range(R)), torch.int64), other)
     assert not torch.equal(out, other)
+
+
+# ---------------------------------------------------------------- products for a few tokens
+@pytest.mark.parametrize("M", [1, 3, 8, 9, 16])
+@pytest.mark.parametrize("N,K", [(48, 64), (100, 120), (4096, 4096), (1000, 14336 + 8)])
+def test_gemm_small_m(ops, cuda_device, M, N, K):
+    g = torch.Generator(device="cuda").manual_seed(M * 1000 + N)
+    x_wide = (torch.randn(M, K + 16, device="cuda", generator=g)).to(torch.bfloat16)
+    x = x_wide[:, :K]                                                   # rows with a stride wider than K
+    w = (torch.randn(N, K, device="cuda", generator=g) / math.sqrt(K)).to(torch.bfloat16)
+    ref = x.float() @ w.float().T
+    out32 = torch.empty(M, N, device="cuda")
+    ops.gemm_small_m(x, w, out32)
+    torch.testing.assert_close(out32, ref, rtol=1e-4, atol=1e-4)       # float32 accumulate of bf16 inputs
+    out16 = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+    ops.gemm_small_m(x, w, out16)
+    assert torch.equal(out16, out32.to(torch.bfloat16))
+    # a spike in one far column of K must arrive in exactly one output
+    x2, w2 = x.clone(), w.clone()
+    x2[M - 1, K - 3] = 64.0
+    w2[N - 1, K - 3] = 8.0
+    ops.gemm_small_m(x2, w2, out32)
+    torch.testing.assert_close(out32, x2.float() @ w2.float().T, rtol=1e-4, atol=1e-3)
+
+
+@pytest.mark.parametrize("M", [1, 8, 13])
+@pytest.mark.parametrize("I,K", [(44, 64), (352, 128), (14336, 4096)])
+def test_gemm_small_m_gated(ops, cuda_device, M, I, K):
+    g = torch.Generator(device="cuda").manual_seed(M + I)
+    x = torch.randn(M, K, device="cuda", generator=g).to(torch.bfloat16)
+    w = (torch.randn(2 * I, K, device="cuda", generator=g) * (2.0 / math.sqrt(K))).to(torch.bfloat16)
+    out = torch.empty(M, I, device="cuda", dtype=torch.bfloat16)
+    ops.gemm_small_m(x, w, out, gated=True)
+    gu = x.float() @ w.float().T
+    gate, up = gu[:, :I], gu[:, I:]
+    ref = gate / (1 + torch.exp(-gate)) * up
+    torch.testing.assert_close(out.float(), ref.to(torch.bfloat16).float(), rtol=1e-2, atol=1e-2)
+
+
+def test_gemm_small_m_refuses_what_it_cannot_do(ops, cuda_device):
+    x = torch.zeros(17, 64, device="cuda", dtype=torch.bfloat16)
+    w = torch.zeros(32, 64, device="cuda", dtype=torch.bfloat16)
+    assert not ops.small_m_ok(x, w)
+    with pytest.raises(ops.KernelError, match="at most 16"):
+        ops.gemm_small_m(x, w, torch.empty(17, 32, device="cuda", dtype=torch.bfloat16))
+    assert not ops.small_m_ok(x[:4, :60], w[:, :60].contiguous())       # K not a multiple of 8
