@@ -24,6 +24,7 @@
 #define LOG2E 1.4426950408889634f
 
 bool attn_mma_supported(int dtype, int d) { return dtype == GG_BF16 && (d == 64 || d == 128); }
+static bool power_of_two(int x) { return x > 0 && (x & (x - 1)) == 0; }
 
 // Shared-memory tile [64 rows][D] bf16; the 16-byte chunk c of row r sits at chunk c ^ (r & 7).
 template <int D> __device__ __forceinline__ unsigned tile_off(int row, int chunk) {
@@ -31,23 +32,26 @@ template <int D> __device__ __forceinline__ unsigned tile_off(int row, int chunk
 }
 
 // Bring keys and values of tokens [k0, k0+64) of one sequence and kv head to a stage.
-// Tokens outside [lo, hi) and pages that were given back are zero-filled.
+// Tokens outside [lo, hi) and pages that were given back are zero-filled.  The page size
+// is a power of two (ps_log2), so the page of a token is a shift away.
 template <int D>
 __device__ __forceinline__ void load_kv_tile(const AttnArgs& a, const int* bt, int kvh, int k0, int lo,
-                                             int hi, unsigned ks, unsigned vs) {
+                                             int hi, unsigned ks, unsigned vs, int ps_log2) {
   constexpr int CPR = D / 8;                       // 16-byte chunks per row
   constexpr int ROWS_PER_PASS = MMA_THREADS / CPR;
   const __nv_bfloat16* kc = (const __nv_bfloat16*)a.kcache;
   const __nv_bfloat16* vc = (const __nv_bfloat16*)a.vcache;
   const int ch = threadIdx.x % CPR, r0 = threadIdx.x / CPR;
-  const int ps = a.page_size;
+  const int ps_mask = (1 << ps_log2) - 1;
+  const size_t page_elems = (size_t)a.nkv << ps_log2;          // rows of D elements per page
+  const unsigned in_head = ((unsigned)kvh << ps_log2);
 #pragma unroll
   for (int i = 0; i < MMA_BK / ROWS_PER_PASS; ++i) {
     const int row = r0 + i * ROWS_PER_PASS;
     const int tok = k0 + row;
     int page = -1;
-    if (tok >= lo && tok < hi) page = __ldg(bt + tok / ps);
-    const size_t src = page >= 0 ? (((size_t)page * a.nkv + kvh) * ps + (tok % ps)) * D + ch * 8 : 0;
+    if (tok >= lo && tok < hi) page = __ldg(bt + (tok >> ps_log2));
+    const size_t src = page >= 0 ? ((size_t)page * page_elems + in_head + (unsigned)(tok & ps_mask)) * D + ch * 8 : 0;
     const int bytes = page >= 0 ? 16 : 0;
     const unsigned off = tile_off<D>(row, ch);
     cp_async16(ks + off, kc + src, bytes);
@@ -157,11 +161,12 @@ __device__ __forceinline__ void load_q_frags(unsigned (*qf)[4], F qrow) {
 
 // ---------------------------------------------------------------- decoded tokens
 template <int D, int STAGES>
-__global__ void __launch_bounds__(MMA_THREADS) attn_decode_mma_kernel(AttnArgs a) {
+__global__ void __launch_bounds__(MMA_THREADS, D == 128 ? 3 : 4) attn_decode_mma_kernel(AttnArgs a) {
   extern __shared__ __align__(128) unsigned char smem_raw[];
   constexpr int TILE_BYTES = MMA_BK * D * 2;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, c2 = (lane & 3) * 2;
   pdl_wait();
+  const int ps_log2 = 31 - __clz(a.page_size);
   const int G = a.nh / a.nkv, gchunks = (G + 15) / 16;
   const int b = a.dec_seqs[blockIdx.x];
   const int kvh = blockIdx.y / gchunks, g0 = (blockIdx.y % gchunks) * 16;
@@ -187,7 +192,7 @@ __global__ void __launch_bounds__(MMA_THREADS) attn_decode_mma_kernel(AttnArgs a
     const int ntiles = (hi - lo + MMA_BK - 1) / MMA_BK;
 #pragma unroll
     for (int s = 0; s < STAGES - 1; ++s) {
-      if (s < ntiles) load_kv_tile<D>(a, bt, kvh, lo + s * MMA_BK, lo, hi, base + s * 2 * TILE_BYTES, base + s * 2 * TILE_BYTES + TILE_BYTES);
+      if (s < ntiles) load_kv_tile<D>(a, bt, kvh, lo + s * MMA_BK, lo, hi, base + s * 2 * TILE_BYTES, base + s * 2 * TILE_BYTES + TILE_BYTES, ps_log2);
       cp_async_commit();
     }
     unsigned qf[D / 16][4];
@@ -198,7 +203,7 @@ __global__ void __launch_bounds__(MMA_THREADS) attn_decode_mma_kernel(AttnArgs a
       const int nx = it + STAGES - 1;
       if (nx < ntiles) {
         const int st = nx % STAGES;
-        load_kv_tile<D>(a, bt, kvh, lo + nx * MMA_BK, lo, hi, base + st * 2 * TILE_BYTES, base + st * 2 * TILE_BYTES + TILE_BYTES);
+        load_kv_tile<D>(a, bt, kvh, lo + nx * MMA_BK, lo, hi, base + st * 2 * TILE_BYTES, base + st * 2 * TILE_BYTES + TILE_BYTES, ps_log2);
       }
       cp_async_commit();
       cp_async_wait<STAGES - 1>();
@@ -279,6 +284,7 @@ __global__ void __launch_bounds__(MMA_THREADS) attn_prefill_mma_kernel(AttnArgs 
   constexpr int STAGES = 2;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, c2 = (lane & 3) * 2;
   pdl_wait();
+  const int ps_log2 = 31 - __clz(a.page_size);
   const int b = a.tile_seq[blockIdx.x], q0 = a.tile_q0[blockIdx.x];
   const int h = blockIdx.y, kvh = h / (a.nh / a.nkv);
   const int t0 = a.cu_q_lens[b], qlen = a.cu_q_lens[b + 1] - t0;
@@ -293,7 +299,7 @@ __global__ void __launch_bounds__(MMA_THREADS) attn_prefill_mma_kernel(AttnArgs 
   const int* bt = a.block_tables + (size_t)b * a.bt_stride;
   const unsigned base = smem_u32(smem_raw);
 
-  load_kv_tile<D>(a, bt, kvh, kstart, lo, hi, base, base + TILE_BYTES);
+  load_kv_tile<D>(a, bt, kvh, kstart, lo, hi, base, base + TILE_BYTES, ps_log2);
   cp_async_commit();
 
   const int wrow0 = warp * 16;                       // this warp's rows of the tile
@@ -313,7 +319,7 @@ __global__ void __launch_bounds__(MMA_THREADS) attn_prefill_mma_kernel(AttnArgs 
   for (int it = 0; it < ntiles; ++it) {
     if (it + 1 < ntiles) {
       const int st = (it + 1) % STAGES;
-      load_kv_tile<D>(a, bt, kvh, kstart + (it + 1) * MMA_BK, lo, hi, base + st * 2 * TILE_BYTES, base + st * 2 * TILE_BYTES + TILE_BYTES);
+      load_kv_tile<D>(a, bt, kvh, kstart + (it + 1) * MMA_BK, lo, hi, base + st * 2 * TILE_BYTES, base + st * 2 * TILE_BYTES + TILE_BYTES, ps_log2);
     }
     cp_async_commit();
     cp_async_wait<STAGES - 1>();
@@ -379,17 +385,18 @@ template <typename K> static int opt_in_smem(K kernel, size_t bytes, const char*
 }
 
 int attn_decode_mma(const AttnArgs& a, int n_dec, cudaStream_t stream) {
+  GG_REQUIRE(power_of_two(a.page_size), "attn_decode: page size %d is not a power of two", a.page_size);
   const int G = a.nh / a.nkv, gchunks = (G + 15) / 16;
   GG_REQUIRE(a.nkv * gchunks <= 65535, "attn_decode: too many heads");
   dim3 grid(n_dec, a.nkv * gchunks, a.num_splits);
-  constexpr int STAGES = 3;
+  constexpr int STAGES = 2;
   int rc;
   if (a.d == 128) {
-    const size_t smem = (size_t)STAGES * 2 * MMA_BK * 128 * 2;       // 96 KB; the combine needs 33 KB of it
+    const size_t smem = (size_t)STAGES * 2 * MMA_BK * 128 * 2;       // 64 KB (3 CTAs per SM); the combine needs 33 KB of it
     if ((rc = opt_in_smem(attn_decode_mma_kernel<128, STAGES>, smem, "attn_decode"))) return rc;
     gg_launch(attn_decode_mma_kernel<128, STAGES>, dim3(grid), dim3(MMA_THREADS), smem, stream, a);
   } else {
-    const size_t smem = (size_t)STAGES * 2 * MMA_BK * 64 * 2;        // 48 KB; the combine needs 17 KB
+    const size_t smem = (size_t)STAGES * 2 * MMA_BK * 64 * 2;        // 32 KB; the combine needs 17 KB
     if ((rc = opt_in_smem(attn_decode_mma_kernel<64, STAGES>, smem, "attn_decode"))) return rc;
     gg_launch(attn_decode_mma_kernel<64, STAGES>, dim3(grid), dim3(MMA_THREADS), smem, stream, a);
   }
@@ -397,6 +404,7 @@ int attn_decode_mma(const AttnArgs& a, int n_dec, cudaStream_t stream) {
 }
 
 int attn_prefill_mma(const AttnArgs& a, int num_tiles, cudaStream_t stream) {
+  GG_REQUIRE(power_of_two(a.page_size), "attn_prefill: page size %d is not a power of two", a.page_size);
   GG_REQUIRE(num_tiles >= 0 && a.nh <= 65535, "attn_prefill: bad grid %d x %d", num_tiles, a.nh);
   if (num_tiles == 0) return GG_OK;
   dim3 grid(num_tiles, a.nh);

@@ -1,0 +1,130 @@
+"""Kernel micro-benchmarks: one kernel at the sizes of a model, timed with CUDA events
+on inputs larger than L2 (a ring of weight copies, or a cache of many sequences).
+
+    python -m gollmgo_b200.microbench gemm_small_m [--tokens 8] [--reps 40]
+    python -m gollmgo_b200.microbench attn_decode  [--batch 64] [--context 2048]
+    python -m gollmgo_b200.microbench attn_prefill [--tokens 2048]
+
+Sizes default to the Llama-3.1-8B shape.  With ``--reps 2`` a run is short enough to
+sit under a profiler.
+"""
+from __future__ import annotations
+
+import argparse
+import math
+import sys
+
+import torch
+
+from .csrc import ops
+from .parts.attention import decode_splits
+
+L2_BYTES = 126e6
+
+
+def _time(fn, reps: int) -> float:
+    """Mean microseconds of fn(i) over reps calls, after 3 warm-up calls."""
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    for i in range(3):
+        fn(i)
+    torch.cuda.synchronize()
+    a.record()
+    for i in range(reps):
+        fn(i)
+    b.record()
+    torch.cuda.synchronize()
+    return a.elapsed_time(b) / reps * 1e3
+
+
+def gemm_small_m(args) -> None:
+    H, I, V = args.hidden, args.intermediate, args.vocab
+    qkv = (args.heads + 2 * args.kv_heads) * args.head_dim
+    shapes = [("qkv", qkv, H, False), ("o", H, args.heads * args.head_dim, False),
+              ("gate_up+silu", I, H, True), ("down", H, I, False), ("head", V, H, False)]
+    M = args.tokens
+    for name, N, K, gated in shapes:
+        rows = 2 * N if gated else N
+        nbytes = rows * K * 2
+        copies = max(2, int(3 * L2_BYTES // nbytes) + 1)          # walk through > 3 x L2 of weights
+        ws = [torch.randn(rows, K, device="cuda", dtype=torch.bfloat16) * 0.02 for _ in range(copies)]
+        x = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
+        out = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+        lib_out = torch.empty(M, rows, device="cuda", dtype=torch.bfloat16)
+        own = _time(lambda i: ops.gemm_small_m(x, ws[i % copies], out, gated=gated), args.reps)
+        lib = _time(lambda i: torch.mm(x, ws[i % copies].t(), out=lib_out), args.reps)
+        print(f"gemm_small_m {name:13s} M={M:2d} N={N:6d} K={K:5d}: {own:7.1f} us {nbytes / own / 1e6:5.2f} TB/s"
+              f"   (vendor library: {lib:7.1f} us {nbytes / lib / 1e6:5.2f} TB/s)", flush=True)
+        del ws
+
+
+def _cache(args, n_seqs: int, ctx: int):
+    page, nkv, d = args.page_size, args.kv_heads, args.head_dim
+    per_seq = -(-ctx // page)
+    pages = n_seqs * per_seq
+    kc = torch.randn(pages, nkv, page, d, device="cuda", dtype=torch.bfloat16)
+    vc = torch.randn(pages, nkv, page, d, device="cuda", dtype=torch.bfloat16)
+    tables = torch.randperm(pages, dtype=torch.int32).view(n_seqs, per_seq).cuda()
+    return kc, vc, tables, per_seq
+
+
+def attn_decode(args) -> None:
+    nh, nkv, d, page, B, ctx = args.heads, args.kv_heads, args.head_dim, args.page_size, args.batch, args.context
+    seq_bytes = ctx * nkv * d * 2 * 2
+    n_seqs = max(B, int(3 * L2_BYTES // seq_bytes) // B * B + B)    # rotate through > 3 x L2 of cache
+    kc, vc, tables, stride = _cache(args, n_seqs, ctx)
+    q = torch.randn(B, (nh + 2 * nkv) * d, device="cuda", dtype=torch.bfloat16)
+    cu = torch.arange(B + 1, dtype=torch.int32, device="cuda")
+    ctxs = torch.full((B,), ctx, dtype=torch.int32, device="cuda")
+    dec = torch.arange(B, dtype=torch.int32, device="cuda")
+    out = torch.empty(B, nh * d, device="cuda", dtype=torch.bfloat16)
+    bts = [tables[i:i + B].contiguous() for i in range(0, n_seqs, B)]
+    sms = torch.cuda.get_device_properties(0).multi_processor_count
+    splits = args.splits or decode_splits(B, nkv * -(-(nh // nkv) // 16), sms)
+    po = torch.empty(B * nh * splits * d, device="cuda")
+    pm = torch.empty(B * nh * splits * 2, device="cuda")
+    t = _time(lambda i: ops.attn_decode(q, q.shape[1], kc, vc, bts[i % len(bts)], stride, cu, ctxs, dec, B,
+                                        splits, po, pm, out, nh, nkv, d, page, 0, 1 / math.sqrt(d)), args.reps)
+    print(f"attn_decode+merge B={B} context={ctx} heads={nh}/{nkv} d={d} splits={splits}: {t:7.1f} us "
+          f"{B * seq_bytes / t / 1e6:5.2f} TB/s of cache", flush=True)
+
+
+def attn_prefill(args) -> None:
+    nh, nkv, d, page, T = args.heads, args.kv_heads, args.head_dim, args.page_size, args.tokens
+    kc, vc, tables, stride = _cache(args, 4, T)
+    q = torch.randn(T, (nh + 2 * nkv) * d, device="cuda", dtype=torch.bfloat16)
+    cu = torch.tensor([0, T], dtype=torch.int32, device="cuda")
+    ctxs = torch.tensor([T], dtype=torch.int32, device="cuda")
+    t16 = torch.arange(0, T, 16, dtype=torch.int32, device="cuda")
+    t64 = torch.arange(0, T, 64, dtype=torch.int32, device="cuda")
+    out = torch.empty(T, nh * d, device="cuda", dtype=torch.bfloat16)
+    t = _time(lambda i: ops.attn_prefill(q, q.shape[1], kc, vc, tables[i % 4:i % 4 + 1].contiguous(), stride, cu,
+                                         ctxs, torch.zeros_like(t16), t16, len(t16), out, nh, nkv, d, page, 0,
+                                         1 / math.sqrt(d), torch.zeros_like(t64), t64, len(t64)), args.reps)
+    flops = 2.0 * 2.0 * nh * d * T * T / 2
+    print(f"attn_prefill T={T} heads={nh}/{nkv} d={d}: {t:7.1f} us {flops / t / 1e6:6.1f} TFLOP/s (causal)", flush=True)
+
+
+def main(argv=None) -> int:
+    ap = argparse.ArgumentParser(prog="python -m gollmgo_b200.microbench")
+    ap.add_argument("kernel", choices=["gemm_small_m", "attn_decode", "attn_prefill"])
+    ap.add_argument("--tokens", type=int, default=None)
+    ap.add_argument("--batch", type=int, default=64)
+    ap.add_argument("--context", type=int, default=2048)
+    ap.add_argument("--splits", type=int, default=0)
+    ap.add_argument("--reps", type=int, default=40)
+    ap.add_argument("--hidden", type=int, default=4096)
+    ap.add_argument("--intermediate", type=int, default=14336)
+    ap.add_argument("--vocab", type=int, default=128256)
+    ap.add_argument("--heads", type=int, default=32)
+    ap.add_argument("--kv-heads", type=int, default=8)
+    ap.add_argument("--head-dim", type=int, default=128)
+    ap.add_argument("--page-size", type=int, default=16)
+    args = ap.parse_args(argv)
+    if args.tokens is None:
+        args.tokens = 8 if args.kernel == "gemm_small_m" else 2048
+    {"gemm_small_m": gemm_small_m, "attn_decode": attn_decode, "attn_prefill": attn_prefill}[args.kernel](args)
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -19,15 +19,26 @@ from ..weights import WeightSpec
 from .linear import linear
 from .registry import build_position, register_mixer
 
-MAX_SPLITS = 64
+MAX_SPLITS = 16
+CTAS_PER_SM = 3            # decode attention CTAs resident on one SM (csrc/attention_mma.cu)
+ASSUMED_TILES = 32         # context the choice is tuned for: 32 tiles of 64 keys
+SPLIT_OVERHEAD = 4         # fixed cost of one slice (prologue, combine, merge), in tiles
 
 
 def decode_splits(n_dec: int, ctas_per_split: int, num_sms: int) -> int:
-    """Slices of the context per decoded token: enough that the grid fills the
-    machine about twice.  Depends only on the batch, never on context lengths,
-    so a captured step stays valid as contexts grow."""
-    per = max(1, n_dec * ctas_per_split)
-    return max(1, min(MAX_SPLITS, -(-2 * num_sms // per)))
+    """Slices of the context per decoded token.  Picks the count that minimises
+    waves x (tiles per slice + fixed cost per slice) for a typical context.  It depends
+    only on the batch, never on the actual context lengths, so a captured step stays
+    valid as contexts grow."""
+    slots = CTAS_PER_SM * num_sms
+    ctas = max(1, n_dec * ctas_per_split)
+    best, best_cost = 1, None
+    for s in range(1, MAX_SPLITS + 1):
+        waves = -(-ctas * s // slots)
+        cost = waves * (ASSUMED_TILES / s + SPLIT_OVERHEAD)
+        if best_cost is None or cost < best_cost - 1e-9:
+            best, best_cost = s, cost
+    return best
 
 
 class Attention:
