@@ -1,0 +1,318 @@
+// Matrix products for many tokens (prompt portions) on the fifth-generation tensor
+// cores: out[M, N] = x[M, K] W[N, K]^T, bfloat16 in, float32 accumulation in tensor
+// memory.  Both operands are K-major, as the activations and the checkpoint's weights
+// already are, so no transposed copies exist anywhere.
+//
+// One CTA computes one 128 x BN tile (BN = 256, or 128 gate + 128 up rows for the
+// gated product) with six warps in three roles:
+//   warp 0  one lane issues the TMA loads (cp.async.bulk.tensor, 128-byte swizzle)
+//           of a 128 x 64 tile of x and a BN x 64 tile of W per stage, four stages
+//           deep, each landing on an mbarrier with a byte count;
+//   warp 1  allocates BN columns of tensor memory; one lane issues tcgen05.mma
+//           (M = 128, N = BN, K = 16; four per stage) from shared-memory descriptors
+//           and releases each stage with tcgen05.commit;
+//   warps 2-5  wait for the last commit, read the accumulator with tcgen05.ld (each
+//           warp its own 32 lanes = 32 rows of the tile), apply the epilogue and
+//           store.
+// Epilogues: bfloat16; float32; SiLU-gated: columns [0,128) of the accumulator come
+// from the gate rows of W and [128,256) from the up rows of the same features, and
+// the tile written is silu(gate) * up (formula: kernels/gollmgo_ops.cu:361-374).
+// Rows of x beyond M, rows of W beyond N and columns beyond K are zero-filled by TMA;
+// the epilogue only stores what lies inside the output.
+//
+// Every wait on an mbarrier is bounded.  A wait that runs out records a code in
+// *status, and the CTA stops issuing work, gives up its tensor memory and returns; the
+// host treats a non-zero status as an error.  No TMA load uses cluster multicast.
+#include <cuda.h>
+
+#include "common.cuh"
+
+#define TC_BM 128
+#define TC_BK 64
+#define TC_STAGES 4
+#define TC_THREADS 192
+#define TC_SPIN_LIMIT (1u << 22)
+
+enum { TC_OUT_BF16 = 0, TC_OUT_F32 = 1, TC_OUT_SILU = 2 };
+enum { TC_ERR_EMPTY_WAIT = 1, TC_ERR_FULL_WAIT = 2, TC_ERR_ACC_WAIT = 3, TC_ERR_DRAIN = 4 };
+
+__device__ __forceinline__ unsigned tc_smem(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(unsigned bar, unsigned count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(unsigned bar, unsigned bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+// Bounded wait for the phase with the given parity.  False if it ran out.
+__device__ __forceinline__ bool mbar_wait(unsigned bar, unsigned parity) {
+  for (unsigned spin = 0; spin < TC_SPIN_LIMIT; ++spin) {
+    unsigned done;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+        "selp.b32 %0, 1, 0, p;\n\t}"
+        : "=r"(done) : "r"(bar), "r"(parity), "r"(1000u) : "memory");
+    if (done) return true;
+  }
+  return false;
+}
+__device__ __forceinline__ void tma_load_2d(unsigned dst, const CUtensorMap* map, int c0, int c1, unsigned bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(unsigned bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+// D[tmem] (+)= A[smem desc] * B[smem desc]; one instruction is 128 x N x 16.
+__device__ __forceinline__ void tc_mma(unsigned d_tmem, unsigned long long a_desc, unsigned long long b_desc,
+                                       unsigned idesc, unsigned accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %6, %7, %8}, p;\n\t}"
+      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(0u), "r"(0u), "r"(0u), "r"(0u)
+      : "memory");
+}
+// 32 lanes x 32 consecutive 32-bit columns of tensor memory: thread = lane (row), v[j] = column j.
+__device__ __forceinline__ void tc_load32(unsigned taddr, unsigned* v) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
+        "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]),
+        "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]),
+        "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+      : "r"(taddr));
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// Shared-memory matrix descriptor of a K-major tile with 128-byte rows and 128-byte
+// swizzle: start address / 16, leading offset 1 (unused with a swizzle), 1024 bytes
+// between groups of eight rows, descriptor version 1, layout type 2 (128-byte swizzle).
+__device__ __forceinline__ unsigned long long tc_smem_desc(unsigned addr) {
+  return (unsigned long long)((addr & 0x3FFFFu) >> 4) | (1ull << 16) | (64ull << 32) | (1ull << 46) | (2ull << 61);
+}
+
+// BN = 256 columns of the accumulator.  MODE as the enum above.
+template <int MODE>
+__global__ void __launch_bounds__(TC_THREADS)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
+               void* __restrict__ out, int M, int N, int K, int* __restrict__ status) {
+  constexpr int BN = 256;
+  constexpr unsigned A_BYTES = TC_BM * TC_BK * 2, B_BYTES = BN * TC_BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
+  extern __shared__ unsigned char tc_smem_raw[];
+  __shared__ __align__(8) unsigned long long bars[2 * TC_STAGES + 1];
+  __shared__ unsigned tmem_base_s;
+  __shared__ int abort_s;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const unsigned tiles = (tc_smem(tc_smem_raw) + 1023u) & ~1023u;        // 1024-byte aligned stages
+  const unsigned full0 = tc_smem(&bars[0]), empty0 = tc_smem(&bars[TC_STAGES]), acc_bar = tc_smem(&bars[2 * TC_STAGES]);
+  // output tile: in the gated mode N counts gated features and a tile has 128 of them
+  const int n_out_tile = MODE == TC_OUT_SILU ? 128 : BN;
+  const int m0 = blockIdx.y * TC_BM, n0 = blockIdx.x * n_out_tile;
+  const int num_kb = (K + TC_BK - 1) / TC_BK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < TC_STAGES; ++s) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, 1); }
+    mbar_init(acc_bar, 1);
+    abort_s = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tc_smem(&tmem_base_s)), "r"((unsigned)BN) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const unsigned tmem_base = tmem_base_s;
+  pdl_trigger();
+  pdl_wait();                                   // x is the previous kernel's output
+
+  if (warp == 0 && lane == 0) {
+    // ---------------- TMA producer
+    int issued = 0;
+    for (int kb = 0; kb < num_kb; ++kb) {
+      const int s = kb % TC_STAGES;
+      const unsigned phase = (kb / TC_STAGES) & 1;
+      if (!mbar_wait(empty0 + 8 * s, phase ^ 1)) { atomicExch(status, TC_ERR_EMPTY_WAIT); atomicExch(&abort_s, 1); break; }
+      if (*(volatile int*)&abort_s) break;
+      const unsigned a_dst = tiles + s * STAGE_BYTES, b_dst = a_dst + A_BYTES;
+      mbar_expect_tx(full0 + 8 * s, STAGE_BYTES);
+      tma_load_2d(a_dst, &map_x, kb * TC_BK, m0, full0 + 8 * s);
+      if (MODE == TC_OUT_SILU) {
+        tma_load_2d(b_dst, &map_w, kb * TC_BK, n0, full0 + 8 * s);                      // 128 gate rows
+        tma_load_2d(b_dst + B_BYTES / 2, &map_w, kb * TC_BK, N + n0, full0 + 8 * s);    // 128 up rows
+      } else {
+        tma_load_2d(b_dst, &map_w, kb * TC_BK, n0, full0 + 8 * s);
+      }
+      issued = kb + 1;
+    }
+    // on an abort: let the copies that were issued land before shared memory is given up
+    if (*(volatile int*)&abort_s) {
+      for (int kb = max(0, issued - TC_STAGES); kb < issued; ++kb)
+        if (!mbar_wait(full0 + 8 * (kb % TC_STAGES), (kb / TC_STAGES) & 1)) { atomicExch(status, TC_ERR_DRAIN); break; }
+    }
+  } else if (warp == 1 && lane == 0) {
+    // ---------------- MMA issuer
+    // instruction descriptor: f32 accumulate, bf16 x bf16, both K-major, N = BN, M = 128
+    const unsigned idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((unsigned)(BN >> 3) << 17) | ((unsigned)(TC_BM >> 4) << 24);
+    bool ok = true;
+    for (int kb = 0; kb < num_kb && ok; ++kb) {
+      const int s = kb % TC_STAGES;
+      const unsigned phase = (kb / TC_STAGES) & 1;
+      if (*(volatile int*)&abort_s) { ok = false; break; }
+      if (!mbar_wait(full0 + 8 * s, phase)) { atomicExch(status, TC_ERR_FULL_WAIT); atomicExch(&abort_s, 1); ok = false; break; }
+      tc_fence_after();
+      const unsigned long long a_desc = tc_smem_desc(tiles + s * STAGE_BYTES);
+      const unsigned long long b_desc = tc_smem_desc(tiles + s * STAGE_BYTES + A_BYTES);
+#pragma unroll
+      for (int k = 0; k < TC_BK / 16; ++k)          // 16 values of k = 32 bytes = 2 units of 16 bytes
+        tc_mma(tmem_base, a_desc + 2 * k, b_desc + 2 * k, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+      tc_commit(empty0 + 8 * s);                    // the stage is free once these MMAs have read it
+    }
+    tc_commit(acc_bar);                             // the accumulator is complete (also reached on abort)
+  } else if (warp >= 2) {
+    // ---------------- epilogue: warp w reads tensor-memory lanes 32*(w%4) .. +32
+    const int quarter = warp & 3;
+    const int row = m0 + quarter * 32 + lane;
+    bool ok = mbar_wait(acc_bar, 0);
+    if (!ok) { atomicExch(status, TC_ERR_ACC_WAIT); atomicExch(&abort_s, 1); }
+    tc_fence_after();
+    if (ok && !*(volatile int*)&abort_s) {
+      const unsigned tlane = tmem_base + ((unsigned)(quarter * 32) << 16);
+      if (MODE == TC_OUT_SILU) {
+        __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(out) + (size_t)row * N + n0;
+#pragma unroll 1
+        for (int c = 0; c < 128; c += 32) {
+          unsigned g[32], u[32];
+          tc_load32(tlane + c, g);
+          tc_load32(tlane + 128 + c, u);
+          if (row < M) {
+#pragma unroll
+            for (int j = 0; j < 32; j += 2) {
+              if (n0 + c + j + 1 < N) {
+                const float g0 = __uint_as_float(g[j]), g1 = __uint_as_float(g[j + 1]);
+                const float v0 = g0 / (1.f + expf(-g0)) * __uint_as_float(u[j]);
+                const float v1 = g1 / (1.f + expf(-g1)) * __uint_as_float(u[j + 1]);
+                *reinterpret_cast<__nv_bfloat162*>(o + c + j) = __floats2bfloat162_rn(v0, v1);
+              } else if (n0 + c + j < N) {
+                const float g0 = __uint_as_float(g[j]);
+                o[c + j] = __float2bfloat16_rn(g0 / (1.f + expf(-g0)) * __uint_as_float(u[j]));
+              }
+            }
+          }
+        }
+      } else {
+#pragma unroll 1
+        for (int c = 0; c < BN; c += 32) {
+          unsigned v[32];
+          tc_load32(tlane + c, v);
+          if (row < M) {
+            if (MODE == TC_OUT_F32) {
+              float* o = reinterpret_cast<float*>(out) + (size_t)row * N + n0 + c;
+#pragma unroll
+              for (int j = 0; j < 32; ++j)
+                if (n0 + c + j < N) o[j] = __uint_as_float(v[j]);
+            } else {
+              __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(out) + (size_t)row * N + n0 + c;
+#pragma unroll
+              for (int j = 0; j < 32; j += 2) {
+                if (n0 + c + j + 1 < N)
+                  *reinterpret_cast<__nv_bfloat162*>(o + j) = __floats2bfloat162_rn(__uint_as_float(v[j]), __uint_as_float(v[j + 1]));
+                else if (n0 + c + j < N)
+                  o[j] = __float2bfloat16_rn(__uint_as_float(v[j]));
+              }
+            }
+          }
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((unsigned)BN) : "memory");
+  }
+}
+
+// ---------------------------------------------------------------- host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = (EncodeTiledFn)p;
+  }
+  return fn;
+}
+
+// Tensor map of a row-major bf16 matrix [rows, cols] with row stride ld (elements), boxes of
+// box_rows x 64 columns, 128-byte swizzle, zero fill outside.
+static int make_map(CUtensorMap* map, const void* ptr, int rows, int cols, long long ld, int box_rows) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return gg_fail(GG_ERR_CUDA, "gemm_tc: the driver has no cuTensorMapEncodeTiled");
+  cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+  cuuint32_t box[2] = {TC_BK, (cuuint32_t)box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return gg_fail(GG_ERR_CUDA, "gemm_tc: cuTensorMapEncodeTiled failed with %d", (int)r);
+  return GG_OK;
+}
+
+// mode: 0 = bfloat16 out [M, N]; 1 = float32 out [M, N]; 2 = W is [2N, K] (gate rows then up
+// rows), out is bfloat16 [M, N] = silu(x Wg^T) * (x Wu^T).  status: one int in device memory,
+// left untouched unless a wait inside the kernel ran out (then non-zero).
+extern "C" int gg_gemm_tc(const void* x, long long ldx, const void* W, void* out, int M, int N, int K,
+                          int mode, int* status, cudaStream_t stream) {
+  GG_REQUIRE(M >= 0 && N > 0 && K > 0, "gemm_tc: bad sizes M=%d N=%d K=%d", M, N, K);
+  GG_REQUIRE(K % 8 == 0 && ldx % 8 == 0, "gemm_tc: K=%d and the row stride %lld of x must be multiples of 8", K, ldx);
+  GG_REQUIRE(((size_t)x % 16) == 0 && ((size_t)W % 16) == 0, "gemm_tc: x and W must be 16-byte aligned");
+  GG_REQUIRE(mode >= 0 && mode <= 2, "gemm_tc: unknown mode %d", mode);
+  GG_REQUIRE(mode != TC_OUT_SILU || N % 2 == 0, "gemm_tc: the gated product needs an even number of features");
+  GG_REQUIRE(N % 2 == 0 || mode == TC_OUT_F32, "gemm_tc: bfloat16 rows of odd length are not 4-byte aligned");
+  GG_REQUIRE(status != nullptr, "gemm_tc: no status word given");
+  if (M == 0) return GG_OK;
+  CUtensorMap map_x, map_w;
+  int rc = make_map(&map_x, x, M, K, ldx, TC_BM);
+  if (rc) return rc;
+  const int w_rows = mode == TC_OUT_SILU ? 2 * N : N;
+  rc = make_map(&map_w, W, w_rows, K, K, mode == TC_OUT_SILU ? 128 : 256);
+  if (rc) return rc;
+  const int n_tile = mode == TC_OUT_SILU ? 128 : 256;
+  dim3 grid((N + n_tile - 1) / n_tile, (M + TC_BM - 1) / TC_BM);
+  GG_REQUIRE(grid.y <= 65535, "gemm_tc: too many rows");
+  const size_t smem = (size_t)TC_STAGES * (TC_BM * TC_BK * 2 + 256 * TC_BK * 2) + 1024;
+  cudaError_t e;
+#define TC_LAUNCH(MODE)                                                                                   \
+  do {                                                                                                    \
+    static bool set = false;                                                                              \
+    if (!set) {                                                                                           \
+      e = cudaFuncSetAttribute(gemm_tc_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+      if (e != cudaSuccess) return gg_fail(GG_ERR_CUDA, "gemm_tc: %s", cudaGetErrorString(e));            \
+      set = true;                                                                                         \
+    }                                                                                                     \
+    e = gg_launch(gemm_tc_kernel<MODE>, grid, dim3(TC_THREADS), smem, stream, map_x, map_w, out, M, N, K, status); \
+  } while (0)
+  if (mode == TC_OUT_BF16) TC_LAUNCH(TC_OUT_BF16);
+  else if (mode == TC_OUT_F32) TC_LAUNCH(TC_OUT_F32);
+  else TC_LAUNCH(TC_OUT_SILU);
+#undef TC_LAUNCH
+  if (e != cudaSuccess) return gg_fail(GG_ERR_CUDA, "gemm_tc: launch: %s", cudaGetErrorString(e));
+  return gg_check_launch("gemm_tc");
+}

@@ -196,6 +196,50 @@ def gemm_small_m(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, gated: boo
                                  _stream()))
 
 
+_TC_STATUS = {}
+
+
+def tc_status(device) -> torch.Tensor:
+    """The status word gemm_tc writes when one of its bounded waits runs out (0 = fine)."""
+    key = torch.device(device).index or 0
+    if key not in _TC_STATUS:
+        _TC_STATUS[key] = torch.zeros(1, dtype=torch.int32, device=device)
+    return _TC_STATUS[key]
+
+
+def check_tc_status(device) -> None:
+    """Raise if a tensor-core product gave up on a wait since the last check (synchronises)."""
+    st = tc_status(device)
+    code = int(st.item())
+    if code:
+        st.zero_()
+        raise KernelError(f"gemm_tc gave up waiting on a barrier (code {code}); its output is not valid")
+
+
+def tc_ok(x: torch.Tensor, w: torch.Tensor, out_cols: int) -> bool:
+    """Whether out = x @ w^T can go through gemm_tc."""
+    return (x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.is_cuda and x.shape[0] > 0
+            and x.shape[1] % 8 == 0 and x.stride(1) == 1 and x.stride(0) % 8 == 0 and w.is_contiguous()
+            and out_cols % 2 == 0)
+
+
+def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, gated: bool = False) -> None:
+    """out[M, N] = x[M, K] @ w[N, K]^T on tcgen05 (bfloat16 in, float32 accumulate in tensor
+    memory); out bfloat16 or float32.  ``gated``: w is [2N, K] (gate rows, then up rows) and
+    out = silu(x Wg^T) * (x Wu^T) in bfloat16."""
+    M, K = x.shape
+    N = out.shape[1]
+    if w.shape != ((2 * N, K) if gated else (N, K)) or out.shape[0] != M or not out.is_contiguous():
+        raise KernelError("gemm_tc: shapes do not fit")
+    if gated and out.dtype != torch.bfloat16:
+        raise KernelError("gemm_tc: the gated product writes bfloat16")
+    if out.dtype not in (torch.float32, torch.bfloat16):
+        raise KernelError("gemm_tc: out must be bfloat16 or float32")
+    mode = 2 if gated else (1 if out.dtype == torch.float32 else 0)
+    _check(lib().gg_gemm_tc(_p(x), ctypes.c_longlong(x.stride(0)), _p(w), _p(out), M, N, K, mode,
+                            _p(tc_status(x.device)), _stream()))
+
+
 def argmax(logits: torch.Tensor, out: torch.Tensor) -> None:
     """out[r] = first index of the maximum of logits[r, :] (float32 [R, V])."""
     _cuda(logits, out)
