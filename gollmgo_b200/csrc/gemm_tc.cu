@@ -3,12 +3,13 @@
 // memory.  Both operands are K-major, as the activations and the checkpoint's weights
 // already are, so no transposed copies exist anywhere.
 //
-// One CTA computes one 128 x BN tile (BN = 256, or 128 gate + 128 up rows for the
-// gated product) with six warps in three roles:
+// A persistent CTA (one per SM) computes 128 x BN tiles (BN = 256, or 128 gate + 128 up
+// rows for the gated product), one after the other, with six warps in three roles:
 //   warp 0  one lane issues the TMA loads (cp.async.bulk.tensor, 128-byte swizzle)
 //           of a 128 x 64 tile of x and a BN x 64 tile of W per stage, four stages
 //           deep, each landing on an mbarrier with a byte count;
-//   warp 1  allocates BN columns of tensor memory; one lane issues tcgen05.mma
+//   warp 1  allocates 2 x BN columns of tensor memory (two accumulators, so that one
+//           tile's epilogue overlaps the next tile's products); one lane issues tcgen05.mma
 //           (M = 128, N = BN, K = 16; four per stage) from shared-memory descriptors
 //           and releases each stage with tcgen05.commit;
 //   warps 2-5  wait for the last commit, read the accumulator with tcgen05.ld (each
@@ -98,33 +99,62 @@ __device__ __forceinline__ unsigned long long tc_smem_desc(unsigned addr) {
   return (unsigned long long)((addr & 0x3FFFFu) >> 4) | (1ull << 16) | (64ull << 32) | (1ull << 46) | (2ull << 61);
 }
 
-// BN = 256 columns of the accumulator.  MODE as the enum above.
+// Stores 32 consecutive outputs of one row; `valid` of them lie inside the matrix.
+__device__ __forceinline__ void store_row32(__nv_bfloat16* o, const float* v, int valid) {
+  if (valid >= 32 && ((size_t)o % 16) == 0) {
+#pragma unroll
+    for (int j = 0; j < 32; j += 8) {
+      uint4 pk;
+      __nv_bfloat162 t0 = __floats2bfloat162_rn(v[j], v[j + 1]), t1 = __floats2bfloat162_rn(v[j + 2], v[j + 3]);
+      __nv_bfloat162 t2 = __floats2bfloat162_rn(v[j + 4], v[j + 5]), t3 = __floats2bfloat162_rn(v[j + 6], v[j + 7]);
+      pk.x = *reinterpret_cast<unsigned*>(&t0); pk.y = *reinterpret_cast<unsigned*>(&t1);
+      pk.z = *reinterpret_cast<unsigned*>(&t2); pk.w = *reinterpret_cast<unsigned*>(&t3);
+      *reinterpret_cast<uint4*>(o + j) = pk;
+    }
+  } else {
+    for (int j = 0; j < 32 && j < valid; ++j) o[j] = __float2bfloat16_rn(v[j]);
+  }
+}
+__device__ __forceinline__ void store_row32(float* o, const float* v, int valid) {
+  if (valid >= 32 && ((size_t)o % 16) == 0) {
+#pragma unroll
+    for (int j = 0; j < 32; j += 4) *reinterpret_cast<float4*>(o + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+  } else {
+    for (int j = 0; j < 32 && j < valid; ++j) o[j] = v[j];
+  }
+}
+
+// A persistent CTA walks over output tiles blockIdx.x, blockIdx.x + gridDim.x, ...; tile t is
+// (row block t % tiles_m, column block t / tiles_m), so CTAs that run together share a block of
+// W.  The accumulator is double-buffered in tensor memory (2 x 256 columns): while the
+// epilogue warps drain one buffer the MMA warp fills the other.
 template <int MODE>
 __global__ void __launch_bounds__(TC_THREADS)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
-               void* __restrict__ out, int M, int N, int K, int* __restrict__ status) {
+               void* __restrict__ out, int M, int N, int K, int tiles_m, int num_tiles,
+               int* __restrict__ status) {
   constexpr int BN = 256;
   constexpr unsigned A_BYTES = TC_BM * TC_BK * 2, B_BYTES = BN * TC_BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
   extern __shared__ unsigned char tc_smem_raw[];
-  __shared__ __align__(8) unsigned long long bars[2 * TC_STAGES + 1];
+  __shared__ __align__(8) unsigned long long bars[2 * TC_STAGES + 4];
   __shared__ unsigned tmem_base_s;
   __shared__ int abort_s;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const unsigned tiles = (tc_smem(tc_smem_raw) + 1023u) & ~1023u;        // 1024-byte aligned stages
-  const unsigned full0 = tc_smem(&bars[0]), empty0 = tc_smem(&bars[TC_STAGES]), acc_bar = tc_smem(&bars[2 * TC_STAGES]);
+  const unsigned full0 = tc_smem(&bars[0]), empty0 = tc_smem(&bars[TC_STAGES]);
+  const unsigned acc_full0 = tc_smem(&bars[2 * TC_STAGES]), acc_empty0 = tc_smem(&bars[2 * TC_STAGES + 2]);
   // output tile: in the gated mode N counts gated features and a tile has 128 of them
   const int n_out_tile = MODE == TC_OUT_SILU ? 128 : BN;
-  const int m0 = blockIdx.y * TC_BM, n0 = blockIdx.x * n_out_tile;
   const int num_kb = (K + TC_BK - 1) / TC_BK;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < TC_STAGES; ++s) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, 1); }
-    mbar_init(acc_bar, 1);
+    for (int b = 0; b < 2; ++b) { mbar_init(acc_full0 + 8 * b, 1); mbar_init(acc_empty0 + 8 * b, 4); }
     abort_s = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 1) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tc_smem(&tmem_base_s)), "r"((unsigned)BN) : "memory");
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tc_smem(&tmem_base_s)), "r"(2u * BN) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
   tc_fence_before();
@@ -136,56 +166,71 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
 
   if (warp == 0 && lane == 0) {
     // ---------------- TMA producer
-    int issued = 0;
-    for (int kb = 0; kb < num_kb; ++kb) {
-      const int s = kb % TC_STAGES;
-      const unsigned phase = (kb / TC_STAGES) & 1;
-      if (!mbar_wait(empty0 + 8 * s, phase ^ 1)) { atomicExch(status, TC_ERR_EMPTY_WAIT); atomicExch(&abort_s, 1); break; }
-      if (*(volatile int*)&abort_s) break;
-      const unsigned a_dst = tiles + s * STAGE_BYTES, b_dst = a_dst + A_BYTES;
-      mbar_expect_tx(full0 + 8 * s, STAGE_BYTES);
-      tma_load_2d(a_dst, &map_x, kb * TC_BK, m0, full0 + 8 * s);
-      if (MODE == TC_OUT_SILU) {
-        tma_load_2d(b_dst, &map_w, kb * TC_BK, n0, full0 + 8 * s);                      // 128 gate rows
-        tma_load_2d(b_dst + B_BYTES / 2, &map_w, kb * TC_BK, N + n0, full0 + 8 * s);    // 128 up rows
-      } else {
-        tma_load_2d(b_dst, &map_w, kb * TC_BK, n0, full0 + 8 * s);
+    int issued = 0, it = 0;
+    bool ok = true;
+    for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+      const int m0 = (t % tiles_m) * TC_BM, n0 = (t / tiles_m) * n_out_tile;
+      for (int kb = 0; kb < num_kb; ++kb, ++it) {
+        const int s = it % TC_STAGES;
+        const unsigned phase = (it / TC_STAGES) & 1;
+        if (!mbar_wait(empty0 + 8 * s, phase ^ 1)) { atomicExch(status, TC_ERR_EMPTY_WAIT); atomicExch(&abort_s, 1); ok = false; break; }
+        if (*(volatile int*)&abort_s) { ok = false; break; }
+        const unsigned a_dst = tiles + s * STAGE_BYTES, b_dst = a_dst + A_BYTES;
+        mbar_expect_tx(full0 + 8 * s, STAGE_BYTES);
+        tma_load_2d(a_dst, &map_x, kb * TC_BK, m0, full0 + 8 * s);
+        if (MODE == TC_OUT_SILU) {
+          tma_load_2d(b_dst, &map_w, kb * TC_BK, n0, full0 + 8 * s);                      // 128 gate rows
+          tma_load_2d(b_dst + B_BYTES / 2, &map_w, kb * TC_BK, N + n0, full0 + 8 * s);    // 128 up rows
+        } else {
+          tma_load_2d(b_dst, &map_w, kb * TC_BK, n0, full0 + 8 * s);
+        }
+        issued = it + 1;
       }
-      issued = kb + 1;
     }
     // on an abort: let the copies that were issued land before shared memory is given up
     if (*(volatile int*)&abort_s) {
-      for (int kb = max(0, issued - TC_STAGES); kb < issued; ++kb)
-        if (!mbar_wait(full0 + 8 * (kb % TC_STAGES), (kb / TC_STAGES) & 1)) { atomicExch(status, TC_ERR_DRAIN); break; }
+      for (int i = max(0, issued - TC_STAGES); i < issued; ++i)
+        if (!mbar_wait(full0 + 8 * (i % TC_STAGES), (i / TC_STAGES) & 1)) { atomicExch(status, TC_ERR_DRAIN); break; }
     }
   } else if (warp == 1 && lane == 0) {
     // ---------------- MMA issuer
     // instruction descriptor: f32 accumulate, bf16 x bf16, both K-major, N = BN, M = 128
     const unsigned idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((unsigned)(BN >> 3) << 17) | ((unsigned)(TC_BM >> 4) << 24);
     bool ok = true;
-    for (int kb = 0; kb < num_kb && ok; ++kb) {
-      const int s = kb % TC_STAGES;
-      const unsigned phase = (kb / TC_STAGES) & 1;
-      if (*(volatile int*)&abort_s) { ok = false; break; }
-      if (!mbar_wait(full0 + 8 * s, phase)) { atomicExch(status, TC_ERR_FULL_WAIT); atomicExch(&abort_s, 1); ok = false; break; }
+    int it = 0, local = 0;
+    for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++local) {
+      const int buf = local & 1;
+      // the epilogue must have drained this buffer (two tiles ago)
+      if (!mbar_wait(acc_empty0 + 8 * buf, ((local >> 1) & 1) ^ 1)) { atomicExch(status, TC_ERR_ACC_WAIT); atomicExch(&abort_s, 1); ok = false; break; }
       tc_fence_after();
-      const unsigned long long a_desc = tc_smem_desc(tiles + s * STAGE_BYTES);
-      const unsigned long long b_desc = tc_smem_desc(tiles + s * STAGE_BYTES + A_BYTES);
+      const unsigned d_tmem = tmem_base + buf * BN;
+      for (int kb = 0; kb < num_kb; ++kb, ++it) {
+        const int s = it % TC_STAGES;
+        const unsigned phase = (it / TC_STAGES) & 1;
+        if (*(volatile int*)&abort_s) { ok = false; break; }
+        if (!mbar_wait(full0 + 8 * s, phase)) { atomicExch(status, TC_ERR_FULL_WAIT); atomicExch(&abort_s, 1); ok = false; break; }
+        tc_fence_after();
+        const unsigned long long a_desc = tc_smem_desc(tiles + s * STAGE_BYTES);
+        const unsigned long long b_desc = tc_smem_desc(tiles + s * STAGE_BYTES + A_BYTES);
 #pragma unroll
-      for (int k = 0; k < TC_BK / 16; ++k)          // 16 values of k = 32 bytes = 2 units of 16 bytes
-        tc_mma(tmem_base, a_desc + 2 * k, b_desc + 2 * k, idesc, (kb > 0 || k > 0) ? 1u : 0u);
-      tc_commit(empty0 + 8 * s);                    // the stage is free once these MMAs have read it
+        for (int k = 0; k < TC_BK / 16; ++k)          // 16 values of k = 32 bytes = 2 units of 16 bytes
+          tc_mma(d_tmem, a_desc + 2 * k, b_desc + 2 * k, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+        tc_commit(empty0 + 8 * s);                    // the stage is free once these MMAs have read it
+      }
+      tc_commit(acc_full0 + 8 * buf);                 // this tile's accumulator is complete (also on abort)
     }
-    tc_commit(acc_bar);                             // the accumulator is complete (also reached on abort)
   } else if (warp >= 2) {
     // ---------------- epilogue: warp w reads tensor-memory lanes 32*(w%4) .. +32
     const int quarter = warp & 3;
-    const int row = m0 + quarter * 32 + lane;
-    bool ok = mbar_wait(acc_bar, 0);
-    if (!ok) { atomicExch(status, TC_ERR_ACC_WAIT); atomicExch(&abort_s, 1); }
-    tc_fence_after();
-    if (ok && !*(volatile int*)&abort_s) {
-      const unsigned tlane = tmem_base + ((unsigned)(quarter * 32) << 16);
+    int local = 0;
+    for (int t = blockIdx.x; t < num_tiles; t += gridDim.x, ++local) {
+      const int buf = local & 1;
+      const int m0 = (t % tiles_m) * TC_BM, n0 = (t / tiles_m) * n_out_tile;
+      const int row = m0 + quarter * 32 + lane;
+      if (!mbar_wait(acc_full0 + 8 * buf, (local >> 1) & 1)) { atomicExch(status, TC_ERR_ACC_WAIT); atomicExch(&abort_s, 1); break; }
+      if (*(volatile int*)&abort_s) break;
+      tc_fence_after();
+      const unsigned tlane = tmem_base + buf * BN + ((unsigned)(quarter * 32) << 16);
       if (MODE == TC_OUT_SILU) {
         __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(out) + (size_t)row * N + n0;
 #pragma unroll 1
@@ -193,52 +238,39 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
           unsigned g[32], u[32];
           tc_load32(tlane + c, g);
           tc_load32(tlane + 128 + c, u);
-          if (row < M) {
+          float v[32];
 #pragma unroll
-            for (int j = 0; j < 32; j += 2) {
-              if (n0 + c + j + 1 < N) {
-                const float g0 = __uint_as_float(g[j]), g1 = __uint_as_float(g[j + 1]);
-                const float v0 = g0 / (1.f + expf(-g0)) * __uint_as_float(u[j]);
-                const float v1 = g1 / (1.f + expf(-g1)) * __uint_as_float(u[j + 1]);
-                *reinterpret_cast<__nv_bfloat162*>(o + c + j) = __floats2bfloat162_rn(v0, v1);
-              } else if (n0 + c + j < N) {
-                const float g0 = __uint_as_float(g[j]);
-                o[c + j] = __float2bfloat16_rn(g0 / (1.f + expf(-g0)) * __uint_as_float(u[j]));
-              }
-            }
+          for (int j = 0; j < 32; ++j) {
+            const float gj = __uint_as_float(g[j]);
+            v[j] = gj / (1.f + __expf(-gj)) * __uint_as_float(u[j]);
           }
+          if (row < M) store_row32(o + c, v, N - (n0 + c));
         }
       } else {
 #pragma unroll 1
         for (int c = 0; c < BN; c += 32) {
-          unsigned v[32];
-          tc_load32(tlane + c, v);
+          unsigned r[32];
+          tc_load32(tlane + c, r);
+          float v[32];
+#pragma unroll
+          for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
           if (row < M) {
-            if (MODE == TC_OUT_F32) {
-              float* o = reinterpret_cast<float*>(out) + (size_t)row * N + n0 + c;
-#pragma unroll
-              for (int j = 0; j < 32; ++j)
-                if (n0 + c + j < N) o[j] = __uint_as_float(v[j]);
-            } else {
-              __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(out) + (size_t)row * N + n0 + c;
-#pragma unroll
-              for (int j = 0; j < 32; j += 2) {
-                if (n0 + c + j + 1 < N)
-                  *reinterpret_cast<__nv_bfloat162*>(o + j) = __floats2bfloat162_rn(__uint_as_float(v[j]), __uint_as_float(v[j + 1]));
-                else if (n0 + c + j < N)
-                  o[j] = __float2bfloat16_rn(__uint_as_float(v[j]));
-              }
-            }
+            if (MODE == TC_OUT_F32) store_row32(reinterpret_cast<float*>(out) + (size_t)row * N + n0 + c, v, N - (n0 + c));
+            else store_row32(reinterpret_cast<__nv_bfloat16*>(out) + (size_t)row * N + n0 + c, v, N - (n0 + c));
           }
         }
       }
+      // hand the buffer back to the MMA warp
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(acc_empty0 + 8 * buf) : "memory");
     }
   }
   tc_fence_before();
   __syncthreads();
   if (warp == 1) {
     tc_fence_after();
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((unsigned)BN) : "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(2u * BN) : "memory");
   }
 }
 
@@ -295,8 +327,18 @@ extern "C" int gg_gemm_tc(const void* x, long long ldx, const void* W, void* out
   rc = make_map(&map_w, W, w_rows, K, K, mode == TC_OUT_SILU ? 128 : 256);
   if (rc) return rc;
   const int n_tile = mode == TC_OUT_SILU ? 128 : 256;
-  dim3 grid((N + n_tile - 1) / n_tile, (M + TC_BM - 1) / TC_BM);
-  GG_REQUIRE(grid.y <= 65535, "gemm_tc: too many rows");
+  const int tiles_m = (M + TC_BM - 1) / TC_BM, tiles_n = (N + n_tile - 1) / n_tile;
+  const long long num_tiles_ll = (long long)tiles_m * tiles_n;
+  GG_REQUIRE(num_tiles_ll < (1ll << 30), "gemm_tc: too many tiles");
+  const int num_tiles = (int)num_tiles_ll;
+  static int num_sms = 0;
+  if (!num_sms) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess ||
+        cudaDeviceGetAttribute(&num_sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || num_sms <= 0)
+      num_sms = 148;
+  }
+  dim3 grid(num_tiles < num_sms ? num_tiles : num_sms);
   const size_t smem = (size_t)TC_STAGES * (TC_BM * TC_BK * 2 + 256 * TC_BK * 2) + 1024;
   cudaError_t e;
 #define TC_LAUNCH(MODE)                                                                                   \
@@ -307,7 +349,7 @@ extern "C" int gg_gemm_tc(const void* x, long long ldx, const void* W, void* out
       if (e != cudaSuccess) return gg_fail(GG_ERR_CUDA, "gemm_tc: %s", cudaGetErrorString(e));            \
       set = true;                                                                                         \
     }                                                                                                     \
-    e = gg_launch(gemm_tc_kernel<MODE>, grid, dim3(TC_THREADS), smem, stream, map_x, map_w, out, M, N, K, status); \
+    e = gg_launch(gemm_tc_kernel<MODE>, grid, dim3(TC_THREADS), smem, stream, map_x, map_w, out, M, N, K, tiles_m, num_tiles, status); \
   } while (0)
   if (mode == TC_OUT_BF16) TC_LAUNCH(TC_OUT_BF16);
   else if (mode == TC_OUT_F32) TC_LAUNCH(TC_OUT_F32);

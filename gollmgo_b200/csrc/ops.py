@@ -197,6 +197,7 @@ def gemm_small_m(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, gated: boo
 
 
 _TC_STATUS = {}
+tc_launched = False       # a tcgen05 product was launched since the status word was last checked
 
 
 def tc_status(device) -> torch.Tensor:
@@ -236,6 +237,8 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, gated: bool = F
     if out.dtype not in (torch.float32, torch.bfloat16):
         raise KernelError("gemm_tc: out must be bfloat16 or float32")
     mode = 2 if gated else (1 if out.dtype == torch.float32 else 0)
+    global tc_launched
+    tc_launched = True
     _check(lib().gg_gemm_tc(_p(x), ctypes.c_longlong(x.stride(0)), _p(w), _p(out), M, N, K, mode,
                             _p(tc_status(x.device)), _stream()))
 

@@ -127,6 +127,7 @@ class Engine:
         logits = self.runner.step(entries)
         tokens = self.sampler.sample(logits, [q.params for q in samplers], [len(q.output) for q in samplers]) \
             if samplers else []
+        self.runner.check_kernels()
         now = time.perf_counter()
         for s in plan.scheduled:
             self.scheduler.advance(s)

@@ -140,6 +140,13 @@ class ModelRunner:
         self.steps += 1
         return logits
 
+    def check_kernels(self) -> None:
+        """Raise if a kernel reported that it gave up on a bounded wait.  Call where the
+        host has synchronised anyway (it reads one word from the device)."""
+        if ops.tc_launched:
+            ops.tc_launched = False
+            ops.check_tc_status(self.device)
+
     # ------------------------------------------------------------------ captured decode steps
     def _graph_stride(self) -> int:
         return -(-self.max_model_len // self.cache.page_size)

@@ -88,6 +88,7 @@ def replay(runner: ModelRunner, lines: IO[str], out_dir: str, log: IO[str] = sys
                 data.astype("<f4", copy=False).tofile(os.path.join(out_dir, f"{step}.f32"))
             else:
                 torch.cuda.synchronize(runner.device)
+            runner.check_kernels()
         for rid in rec.get("end", []):
             if runner.has(rid):
                 runner.release(rid)

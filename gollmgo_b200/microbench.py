@@ -2,6 +2,7 @@
 on inputs larger than L2 (a ring of weight copies, or a cache of many sequences).
 
     python -m gollmgo_b200.microbench gemm_small_m [--tokens 8] [--reps 40]
+    python -m gollmgo_b200.microbench gemm_tc      [--tokens 2048]
     python -m gollmgo_b200.microbench attn_decode  [--batch 64] [--context 2048]
     python -m gollmgo_b200.microbench attn_prefill [--tokens 2048]
 
@@ -57,6 +58,28 @@ def gemm_small_m(args) -> None:
         del ws
 
 
+def gemm_tc(args) -> None:
+    H, I, V = args.hidden, args.intermediate, args.vocab
+    qkv = (args.heads + 2 * args.kv_heads) * args.head_dim
+    shapes = [("qkv", qkv, H, False), ("o", H, args.heads * args.head_dim, False),
+              ("gate_up+silu", I, H, True), ("down", H, I, False)]
+    M = args.tokens
+    for name, N, K, gated in shapes:
+        rows = 2 * N if gated else N
+        flops = 2.0 * M * rows * K
+        copies = max(2, int(3 * L2_BYTES // (rows * K * 2)) + 1)
+        ws = [torch.randn(rows, K, device="cuda", dtype=torch.bfloat16) * 0.02 for _ in range(copies)]
+        x = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
+        out = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+        lib_out = torch.empty(M, rows, device="cuda", dtype=torch.bfloat16)
+        own = _time(lambda i: ops.gemm_tc(x, ws[i % copies], out, gated=gated), args.reps)
+        ops.check_tc_status("cuda")
+        lib = _time(lambda i: torch.mm(x, ws[i % copies].t(), out=lib_out), args.reps)
+        print(f"gemm_tc {name:13s} M={M:4d} N={N:6d} K={K:5d}: {own:7.1f} us {flops / own / 1e6:7.1f} TFLOP/s"
+              f"   (vendor library: {lib:7.1f} us {flops / lib / 1e6:7.1f} TFLOP/s)", flush=True)
+        del ws
+
+
 def _cache(args, n_seqs: int, ctx: int):
     page, nkv, d = args.page_size, args.kv_heads, args.head_dim
     per_seq = -(-ctx // page)
@@ -106,7 +129,7 @@ def attn_prefill(args) -> None:
 
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(prog="python -m gollmgo_b200.microbench")
-    ap.add_argument("kernel", choices=["gemm_small_m", "attn_decode", "attn_prefill"])
+    ap.add_argument("kernel", choices=["gemm_small_m", "gemm_tc", "attn_decode", "attn_prefill"])
     ap.add_argument("--tokens", type=int, default=None)
     ap.add_argument("--batch", type=int, default=64)
     ap.add_argument("--context", type=int, default=2048)
@@ -122,7 +145,7 @@ def main(argv=None) -> int:
     args = ap.parse_args(argv)
     if args.tokens is None:
         args.tokens = 8 if args.kernel == "gemm_small_m" else 2048
-    {"gemm_small_m": gemm_small_m, "attn_decode": attn_decode, "attn_prefill": attn_prefill}[args.kernel](args)
+    {"gemm_small_m": gemm_small_m, "gemm_tc": gemm_tc, "attn_decode": attn_decode, "attn_prefill": attn_prefill}[args.kernel](args)
     return 0
 
 

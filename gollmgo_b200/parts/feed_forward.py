@@ -8,7 +8,7 @@ import torch
 
 from ..csrc import ops
 from ..weights import WeightSpec
-from .linear import linear
+from .linear import linear, use_tc
 from .registry import register_feed_forward
 
 
@@ -46,6 +46,8 @@ class GatedMLP:
         a = ws.get("ffn_act", T, self.inter)
         if ops.small_m_ok(x, self.w_gate_up):
             ops.gemm_small_m(x, self.w_gate_up, a, gated=True)       # product and activation in one
+        elif use_tc(x, self.w_gate_up, self.inter, True):
+            ops.gemm_tc(x, self.w_gate_up, a, gated=True)            # the same, on tcgen05
         else:
             gu = ws.get("gate_up", T, 2 * self.inter)
             linear(x, self.w_gate_up, gu)
