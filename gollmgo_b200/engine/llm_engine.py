@@ -120,7 +120,7 @@ class Engine:
         entries, samplers = [], []
         for s in plan.scheduled:
             seq = s.seq
-            toks = seq.tokens[seq.num_computed:seq.num_computed + s.num_tokens]
+            toks = seq.token_slice(seq.num_computed, seq.num_computed + s.num_tokens)
             entries.append(StepEntry(seq.id, toks, [s.num_tokens - 1] if s.samples else []))
             if s.samples:
                 samplers.append(seq)

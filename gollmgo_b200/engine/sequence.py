@@ -55,6 +55,15 @@ class Sequence:
     def tokens(self) -> List[int]:
         return self.prompt + self.output
 
+    def token_slice(self, lo: int, hi: int) -> List[int]:
+        """tokens[lo:hi] without building the whole list."""
+        n = len(self.prompt)
+        if lo >= n:
+            return self.output[lo - n:hi - n]
+        if hi <= n:
+            return self.prompt[lo:hi]
+        return self.prompt[lo:] + self.output[:hi - n]
+
     @property
     def total_len(self) -> int:
         return len(self.prompt) + len(self.output)

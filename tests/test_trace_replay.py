@@ -11,12 +11,13 @@ import trace_tools as tt
 pytestmark = pytest.mark.gpu
 
 LENGTHS = {"tiny_a": [7, 13, 1, 70, 45, 101], "tiny_b": [1, 5, 37, 70, 130, 96],
-           "tiny_c": [3, 66, 40, 150, 97, 129]}
-TOL = {"float32": 2e-4, "bfloat16": 6e-2}
+           "tiny_c": [3, 66, 40, 150, 97, 129], "tiny_d": [2, 64, 65, 130, 200, 33],
+           "tiny_e": [1, 129, 64, 190, 80, 257]}
+TOL = {"float32": 2e-5, "bfloat16": 4e-2}
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["tiny_a", "tiny_b", "tiny_c"])
+@pytest.mark.parametrize("name", ["tiny_a", "tiny_b", "tiny_c", "tiny_d", "tiny_e"])
 def test_replay_matches_plain(tmp_path, cuda_device, name, dtype):
     config, page, std, jitter = tiny_configs.get(name)
     model_dir = tt.model_folder(str(tmp_path), name, config, seed=11, std=std, jitter=jitter,

@@ -33,11 +33,32 @@ TINY_C = {
     "layer_types": ["sliding_attention", "full_attention", "sliding_attention", "full_attention"],
 }
 
+# head size 64 and 128 in turn take the tensor-core attention kernels of the bfloat16 mode;
+# widths that are multiples of 8 take the weight-streaming and tcgen05 products
+TINY_D = {
+    "architectures": ["LlamaForCausalLM"], "model_type": "llama",
+    "num_hidden_layers": 2, "hidden_size": 192, "num_attention_heads": 6,
+    "num_key_value_heads": 2, "head_dim": 64, "intermediate_size": 328, "vocab_size": 500,
+    "rope_theta": 100000.0, "rms_norm_eps": 1e-5, "tie_word_embeddings": False,
+    "max_position_embeddings": 1024, "hidden_act": "silu",
+    "rope_scaling": {"rope_type": "linear", "factor": 2.0},
+}
+TINY_E = {
+    "architectures": ["LlamaForCausalLM"], "model_type": "llama",
+    "num_hidden_layers": 2, "hidden_size": 256, "num_attention_heads": 4,
+    "num_key_value_heads": 1, "head_dim": 128, "intermediate_size": 264, "vocab_size": 384,
+    "rope_theta": 500000.0, "rms_norm_eps": 1e-5, "tie_word_embeddings": True,
+    "max_position_embeddings": 1024, "hidden_act": "silu", "sliding_window": 80,
+    "layer_types": ["full_attention", "sliding_attention"],
+}
+
 # name -> (config, page size, std of matrices, jitter of norm weights)
 TINY = {
     "tiny_a": (TINY_A, 16, 0.12, 0.0),
     "tiny_b": (TINY_B, 8, 0.09, 0.1),
     "tiny_c": (TINY_C, 32, 0.10, 0.05),
+    "tiny_d": (TINY_D, 16, 0.07, 0.05),
+    "tiny_e": (TINY_E, 16, 0.06, 0.0),
 }
 
 
