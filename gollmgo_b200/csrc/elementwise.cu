@@ -9,13 +9,20 @@
 // out[t, :] = float(table[ids[t], :])   (reference: kernels/gollmgo_ops.cu:538-552,
 // which leaves the row stale for an id out of range; here the row is zeroed and
 // *bad_id is set, and the host has already refused such ids.)
+// With token_src, token t comes from prev_tokens[token_src[t]] where token_src[t] >= 0: the
+// token sampled on the device in the step before, which the host has not read yet.
 template <typename TW>
 __global__ void embed_gather_kernel(const int* __restrict__ ids, const TW* __restrict__ table,
-                                    float* __restrict__ out, int H, int V, int* bad_id) {
+                                    float* __restrict__ out, int H, int V, int* bad_id,
+                                    const int* __restrict__ token_src, const int* __restrict__ prev_tokens) {
   pdl_trigger();
   pdl_wait();
   const int t = blockIdx.x;
-  const int id = ids[t];
+  int id = ids[t];
+  if (token_src) {
+    const int src = token_src[t];
+    if (src >= 0) id = prev_tokens[src];
+  }
   float* o = out + (size_t)t * H;
   if (id < 0 || id >= V) {
     if (threadIdx.x == 0 && bad_id) atomicExch(bad_id, 1);
@@ -27,14 +34,16 @@ __global__ void embed_gather_kernel(const int* __restrict__ ids, const TW* __res
 }
 
 extern "C" int gg_embed_gather(const int* ids, const void* table, int table_dtype, float* out,
-                               int T, int H, int V, int* bad_id, cudaStream_t stream) {
+                               int T, int H, int V, int* bad_id, const int* token_src,
+                               const int* prev_tokens, cudaStream_t stream) {
+  GG_REQUIRE(!token_src || prev_tokens, "embed_gather: token sources without the previous tokens");
   GG_REQUIRE(T >= 0 && H > 0 && V > 0, "embed_gather: bad sizes T=%d H=%d V=%d", T, H, V);
   if (T == 0) return GG_OK;
   const int threads = H >= 1024 ? 256 : 128;
   if (table_dtype == GG_F32)
-    gg_launch(embed_gather_kernel<float>, dim3(T), dim3(threads), 0, stream, ids, (const float*)table, out, H, V, bad_id);
+    gg_launch(embed_gather_kernel<float>, dim3(T), dim3(threads), 0, stream, ids, (const float*)table, out, H, V, bad_id, token_src, prev_tokens);
   else if (table_dtype == GG_BF16)
-    gg_launch(embed_gather_kernel<__nv_bfloat16>, dim3(T), dim3(threads), 0, stream, ids, (const __nv_bfloat16*)table, out, H, V, bad_id);
+    gg_launch(embed_gather_kernel<__nv_bfloat16>, dim3(T), dim3(threads), 0, stream, ids, (const __nv_bfloat16*)table, out, H, V, bad_id, token_src, prev_tokens);
   else
     return gg_fail(GG_ERR_INVALID, "embed_gather: unknown dtype %d", table_dtype);
   return gg_check_launch("embed_gather");

@@ -78,14 +78,16 @@ def device_capability() -> int:
 
 
 def embed_gather(ids: torch.Tensor, table: torch.Tensor, out: torch.Tensor,
-                 bad_id: Optional[torch.Tensor] = None) -> None:
-    """out[t, :] = float32(table[ids[t], :]); ids int32 [T], out float32 [T, H]."""
-    _cuda(ids, table, out)
+                 bad_id: Optional[torch.Tensor] = None, token_src: Optional[torch.Tensor] = None,
+                 prev_tokens: Optional[torch.Tensor] = None) -> None:
+    """out[t, :] = float32(table[id_t, :]); ids int32 [T], out float32 [T, H].  Where
+    token_src[t] >= 0 the id is prev_tokens[token_src[t]] (a token still on the device)."""
+    _cuda(ids, table, out, token_src, prev_tokens)
     T, (V, H) = ids.numel(), table.shape
     if out.dtype != torch.float32 or out.shape[-1] != H or ids.dtype != torch.int32:
         raise KernelError("embed_gather: out must be float32 [T, H], ids int32")
     _check(lib().gg_embed_gather(_p(ids), _p(table), dtype_code(table.dtype), _p(out),
-                                 T, H, V, _p(bad_id), _stream()))
+                                 T, H, V, _p(bad_id), _p(token_src), _p(prev_tokens), _stream()))
 
 
 def add_rmsnorm(resid: torch.Tensor, delta: Optional[torch.Tensor], weight: torch.Tensor,

@@ -25,6 +25,9 @@ class StepEntry:
     request_id: object
     tokens: Sequence[int]
     want: Sequence[int] = ()
+    # the entry's single token is not known on the host yet: it is row `token_src` of the
+    # tokens sampled on the device in the step before (tokens[0] is then ignored)
+    token_src: int = -1
 
 
 class StepBatch:
@@ -36,6 +39,8 @@ class StepBatch:
     num_decode: int
     bt_stride: int
     token_ids: torch.Tensor
+    token_src: Optional[torch.Tensor]      # None: every token id is given by the host
+    prev_tokens: Optional[torch.Tensor]    # the tokens sampled on the device in the step before
     positions: torch.Tensor
     cu_q_lens: torch.Tensor
     context_lens: torch.Tensor
@@ -74,6 +79,7 @@ class BatchLayout:
             off += _align(max(n, 1))
             return o
         self.token_ids = take(T)
+        self.token_src = take(T)
         self.positions = take(T)
         self.slot_mapping = [take(T) for _ in range(G)]
         self.cu_q_lens = take(B + 1)
@@ -173,6 +179,18 @@ class BatchBuilder:
         h[:lay.size] = 0
         flat_tokens = np.fromiter((t for e in entries for t in e.tokens), dtype=np.int64, count=T)
         h[lay.token_ids:lay.token_ids + T] = flat_tokens
+        h[lay.token_src:lay.token_src + Tp] = -1
+        if any(e.token_src >= 0 for e in entries):
+            base = 0
+            for e, n in zip(entries, q_lens):
+                if e.token_src >= 0:
+                    if n != 1:
+                        raise ValueError("only a single decoded token can come from the device")
+                    h[lay.token_src + base] = e.token_src
+                base += n
+            has_src = True
+        else:
+            has_src = False
         pos = np.concatenate([np.arange(s, s + n, dtype=np.int32) for s, n in zip(q_starts, q_lens)])
         h[lay.positions:lay.positions + T] = pos
         for g in range(G):
@@ -217,6 +235,7 @@ class BatchBuilder:
         sb.num_tiles, sb.num_decode, sb.bt_stride = len(tiles), nd, stride
         v = lambda off, n: dev[off:off + max(n, 1)]
         sb.token_ids, sb.positions = v(lay.token_ids, Tp), v(lay.positions, Tp)
+        sb.token_src = v(lay.token_src, Tp) if (has_src or static_dev is not None) else None
         sb.cu_q_lens, sb.context_lens = v(lay.cu_q_lens, Bp + 1), v(lay.context_lens, Bp)
         sb.state_slots, sb.logit_rows = v(lay.state_slots, Bp), v(lay.logit_rows, R)[:R]
         sb.tile_seq, sb.tile_q0 = v(lay.tile_seq, len(tiles)), v(lay.tile_q0, len(tiles))
@@ -227,5 +246,6 @@ class BatchBuilder:
         sb.block_tables = [v(o, Bp * stride) for o in lay.block_tables]
         sb.request_ids, sb.q_lens, sb.q_starts = ids, q_lens, q_starts
         sb.state_slot_list = [cache.state_slot(e.request_id) for e in entries]
+        sb.prev_tokens = None
         sb.layout = lay
         return sb

@@ -21,7 +21,7 @@ from ..sampling.params import SamplingParams
 from .batch import StepEntry
 from .runner import ModelRunner
 from .scheduler import Scheduler, SchedulerOutput
-from .sequence import SeqState, Sequence
+from .sequence import PENDING, SeqState, Sequence
 
 
 @dataclass
@@ -73,7 +73,8 @@ class Engine:
         self.ecfg = ecfg
         self.spec = self.runner.spec
         self.scheduler = Scheduler(ecfg, self.runner.cache, self.runner.max_model_len)
-        self.sampler = Sampler(self.runner.device, max(ecfg.max_batch_size, 1))
+        self.sampler = Sampler(self.runner.device, max(ecfg.max_batch_size, 1), self.runner.last_tokens)
+        self._inflight = None
         self.sequences: Dict[str, Sequence] = {}
         self.stats = EngineStats()
         self._next_id = 0
@@ -105,56 +106,97 @@ class Engine:
         self.sequences[rid] = seq
         return rid
 
-    def has_unfinished(self) -> bool:
-        return self.scheduler.has_work()
-
     # ------------------------------------------------------------------ one turn of the loop
     def step(self) -> List[TokenResult]:
+        """One turn: plan and launch the next step, then hand out the tokens of the step
+        launched one turn earlier.
+
+        The device runs one step ahead of the host.  A sequence that sampled in the step
+        still in flight gets a placeholder for its unknown token; the step launched now
+        reads that token on the device (from the sampler's buffer), so the host work of
+        this turn overlaps the device's work on the step before.  What the host cannot
+        know one step early is an end-of-sequence token: such a sequence takes part in
+        one step too many, whose token is dropped.  Finishing by length is known early.
+        """
         plan: SchedulerOutput = self.scheduler.schedule()
         self.stats.preemptions += len(plan.preempted)
-        if not plan.scheduled:
-            if self.scheduler.has_work() and not plan.preempted:
-                raise RuntimeError("scheduler made no progress: the page pool is too small for the "
-                                   "request at the head of the queue")
+        launched = None
+        if plan.scheduled:
+            entries, samplers = [], []
+            for s in plan.scheduled:
+                seq = s.seq
+                toks = seq.token_slice(seq.num_computed, seq.num_computed + s.num_tokens)
+                src = -1
+                if toks[-1] == PENDING:
+                    if s.num_tokens != 1:
+                        raise RuntimeError("a token still on the device can only be fed alone")
+                    toks, src = [0], seq.pending_row
+                if PENDING in toks:
+                    raise RuntimeError("an unknown token in the middle of a portion")
+                entries.append(StepEntry(seq.id, toks, [s.num_tokens - 1] if s.samples else [], src))
+                if s.samples:
+                    samplers.append(seq)
+            logits = self.runner.step(entries)
+            handle = self.sampler.sample_async(logits, [q.params for q in samplers],
+                                               [len(q.output) for q in samplers])
+            for s in plan.scheduled:
+                self.scheduler.advance(s)
+            for row, seq in enumerate(samplers):
+                seq.output.append(PENDING)
+                seq.pending_row = row
+                self.scheduler.token_sampled(seq)
+                if len(seq.output) >= seq.params.max_tokens:
+                    self.scheduler.finish(seq, "length")          # known without the token's value
+            launched = (handle, samplers)
+            st = self.stats
+            st.steps += 1
+            st.prefill_tokens += plan.prefill_tokens
+            st.decode_tokens += plan.decode_tokens
+            st.pages_high_water = max(g.pool.high_water for g in self.runner.cache.groups)
+        elif self._inflight is None and self.scheduler.has_work() and not plan.preempted:
+            raise RuntimeError("scheduler made no progress: the page pool is too small for the "
+                               "request at the head of the queue")
+        results = self._resolve(self._inflight)
+        self._inflight = launched
+        return results
+
+    def _resolve(self, inflight) -> List[TokenResult]:
+        """Read the tokens of a launched step and settle its sequences."""
+        if inflight is None:
             return []
-        entries, samplers = [], []
-        for s in plan.scheduled:
-            seq = s.seq
-            toks = seq.token_slice(seq.num_computed, seq.num_computed + s.num_tokens)
-            entries.append(StepEntry(seq.id, toks, [s.num_tokens - 1] if s.samples else []))
-            if s.samples:
-                samplers.append(seq)
-        logits = self.runner.step(entries)
-        tokens = self.sampler.sample(logits, [q.params for q in samplers], [len(q.output) for q in samplers]) \
-            if samplers else []
+        handle, samplers = inflight
+        tokens = self.sampler.wait(handle)
         self.runner.check_kernels()
         now = time.perf_counter()
-        for s in plan.scheduled:
-            self.scheduler.advance(s)
-        results = []
         eos = set(self.spec.eos_token_ids)
+        results = []
         for seq, tok in zip(samplers, tokens):
-            seq.output.append(int(tok))
+            if seq.dropped:                    # ended by an earlier token; this one was one step too many
+                continue
+            tok = int(tok)
+            idx = seq.resolved
+            seq.output[idx] = tok
+            seq.resolved += 1
             seq.token_times.append(now)
             if seq.first_token_at is None:
                 seq.first_token_at = now
             seq.last_token_at = now
-            self.scheduler.token_sampled(seq)
             reason = None
             if not seq.params.ignore_eos and tok in eos:
                 reason = "stop"
-            elif len(seq.output) >= seq.params.max_tokens:
+                del seq.output[idx + 1:]       # a placeholder of the step launched since
+                seq.dropped = True
+                if not seq.finished:
+                    self.scheduler.finish(seq, "stop")
+                seq.finish_reason = "stop"
+            elif seq.resolved >= seq.params.max_tokens:
                 reason = "length"
-            if reason:
-                self.scheduler.finish(seq, reason)
-            results.append(TokenResult(seq.request_id, int(tok), reason is not None, reason))
-        st = self.stats
-        st.steps += 1
-        st.prefill_tokens += plan.prefill_tokens
-        st.decode_tokens += plan.decode_tokens
-        st.generated_tokens += len(tokens)
-        st.pages_high_water = max(g.pool.high_water for g in self.runner.cache.groups)
+            results.append(TokenResult(seq.request_id, tok, reason is not None, reason))
+            self.stats.generated_tokens += 1
         return results
+
+    def has_unfinished(self) -> bool:
+        return self.scheduler.has_work() or self._inflight is not None
 
     # ------------------------------------------------------------------ whole requests
     def generate(self, prompts: Seq[Seq[int]], params=None, **param_options) -> List[RequestOutput]:
@@ -186,6 +228,8 @@ class Engine:
     def stop(self) -> None:
         """Finish every live request (reference: ServingEngine.Stop, serving.go:693-709)."""
         self._stopped = True
+        self._resolve(self._inflight)
+        self._inflight = None
         for seq in list(self.scheduler.running.values()):
             self.scheduler.finish(seq, "abort")
         while self.scheduler.waiting:

@@ -68,6 +68,10 @@ class ModelRunner:
                                   dtype=self.dtype, device=self.device)
         self.caches = [self._cache_view(i, n) for i, n in enumerate(needs)]
         self.builder = BatchBuilder(self.cache, self.device)
+        # tokens sampled on the device in the last step, by row: the next step may take its
+        # inputs from here before the host has read them
+        self.last_tokens = torch.zeros(max(engine_config.max_batch_size, 1), dtype=torch.int32,
+                                       device=self.device)
         self._graphs: Dict[int, "_CapturedStep"] = {}
         self.steps = 0
         self.launch_count = 0
@@ -136,6 +140,7 @@ class ModelRunner:
             if bucket is not None and bucket <= self.ctx.max_seqs:
                 return self._graph_step(entries, bucket)
         batch = self.builder.build(entries)
+        batch.prev_tokens = self.last_tokens if batch.token_src is not None else None
         logits = self.model.forward(batch, self.caches)
         self.steps += 1
         return logits
@@ -159,6 +164,7 @@ class ModelRunner:
             cs = _CapturedStep(torch.zeros(lay.size, dtype=torch.int32, device=self.device))
             self._graphs[bucket] = cs
         batch = self.builder.build(entries, fixed_seqs=bucket, fixed_stride=stride, static_dev=cs.meta)
+        batch.prev_tokens = self.last_tokens
         if cs.graph is None:
             torch.cuda.synchronize(self.device)
             # warm-up on a side stream, then capture

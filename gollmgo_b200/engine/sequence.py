@@ -14,6 +14,9 @@ from typing import List, Optional
 from ..sampling.params import SamplingParams
 
 
+PENDING = -1       # in Sequence.output: a token sampled on the device that the host has not read yet
+
+
 class SeqState(enum.Enum):
     WAITING = "WAITING"
     PREFILLING = "PREFILLING"
@@ -50,6 +53,9 @@ class Sequence:
         self.first_token_at: Optional[float] = None
         self.last_token_at: Optional[float] = None
         self.token_times: List[float] = []
+        self.resolved = 0                  # tokens of `output` whose value the host knows
+        self.pending_row = -1              # row of the unknown token in the sampler's device buffer
+        self.dropped = False               # ended by an end-of-sequence token; later samples are void
 
     @property
     def tokens(self) -> List[int]:

@@ -109,7 +109,8 @@ class DecoderModel:
         T, H = batch.num_tokens, self.spec.hidden_size
         ws = self.ctx.workspace
         resid = ws.get("residual", T, H)
-        ops.embed_gather(batch.token_ids, self.embed, resid, self.bad_id)
+        ops.embed_gather(batch.token_ids, self.embed, resid, self.bad_id,
+                         getattr(batch, "token_src", None), getattr(batch, "prev_tokens", None))
         delta = None
         for e in self.spec.run_order:
             delta = self.blocks[e.layer].forward(resid, delta, batch, caches[e.cache], e.writes_cache)

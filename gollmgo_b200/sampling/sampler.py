@@ -25,22 +25,30 @@ def _as_i64(x: int) -> int:
 
 
 class Sampler:
-    def __init__(self, device, max_rows: int):
+    """Samples on the device into ``tokens`` (a buffer the next step can read from
+    directly) and copies the result to one of two pinned host buffers; ``wait``
+    hands the tokens to the host.  Two steps can be in flight."""
+
+    def __init__(self, device, max_rows: int, tokens: torch.Tensor = None):
         self.device = torch.device(device)
         self.max_rows = max_rows
-        self.out = torch.empty(max_rows, dtype=torch.int32, device=self.device)
-        self.out_host = torch.empty(max_rows, dtype=torch.int32, pin_memory=True)
+        self.tokens = tokens if tokens is not None else torch.empty(max_rows, dtype=torch.int32, device=self.device)
+        self._host = [torch.empty(max_rows, dtype=torch.int32, pin_memory=True) for _ in range(2)]
+        self._events = [torch.cuda.Event(), torch.cuda.Event()]
+        self._turn = 0
 
-    def sample(self, logits: torch.Tensor, params: Sequence[SamplingParams],
-               draw_index: Sequence[int]) -> List[int]:
-        """One token per row of ``logits`` [R, V]; ``draw_index[r]`` is how many tokens
-        request r has drawn before."""
+    def sample_async(self, logits: torch.Tensor, params: Sequence[SamplingParams],
+                     draw_index: Sequence[int]):
+        """Launch the sampling of one token per row of ``logits`` [R, V]; ``draw_index[r]``
+        is how many tokens request r has drawn before.  Returns a handle for ``wait``."""
         R = logits.shape[0]
-        if R == 0:
-            return []
         if R > self.max_rows:
             raise ValueError(f"{R} rows to sample, room for {self.max_rows}")
-        out = self.out[:R]
+        slot = self._turn
+        self._turn ^= 1
+        if R == 0:
+            return (slot, 0)
+        out = self.tokens[:R]
         if all(p.greedy for p in params):
             ops.argmax(logits, out)
         else:
@@ -51,6 +59,17 @@ class Sampler:
             seeds = torch.tensor([_as_i64(p.seed or 0) for p in params], dtype=torch.int64).to(dev, non_blocking=True)
             draws = torch.tensor(list(draw_index), dtype=torch.int64).to(dev, non_blocking=True)
             ops.sample(logits, temps, top_k, top_p, seeds, draws, out)
-        self.out_host[:R].copy_(out, non_blocking=True)
-        torch.cuda.current_stream().synchronize()
-        return self.out_host[:R].tolist()
+        self._host[slot][:R].copy_(out, non_blocking=True)
+        self._events[slot].record()
+        return (slot, R)
+
+    def wait(self, handle) -> List[int]:
+        slot, R = handle
+        if R == 0:
+            return []
+        self._events[slot].synchronize()
+        return self._host[slot][:R].tolist()
+
+    def sample(self, logits: torch.Tensor, params: Sequence[SamplingParams],
+               draw_index: Sequence[int]) -> List[int]:
+        return self.wait(self.sample_async(logits, params, draw_index))

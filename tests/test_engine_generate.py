@@ -95,6 +95,41 @@ def test_eos_stops_and_is_delivered(models):
     assert o2.token_ids == free_run and o2.finish_reason == "length"
 
 
+def test_one_step_lookahead_drops_what_follows_an_end_token(models):
+    """The engine launches a step before it has read the tokens of the step before.  A
+    request that ends on an end-of-sequence token has then taken part in one step too
+    many: that token is dropped, its neighbours are not disturbed, pages come back."""
+    from gollmgo_b200 import Engine, SamplingParams
+    d, cfg, page, w = models["tiny_a"]
+    prompts = list(tt.random_requests(cfg["vocab_size"], [9, 4, 21, 2], seed=8).values())
+    free = [P.generate(w, cfg, p, 14, cast=torch.float32) for p in prompts]
+    eos = {free[0][5], free[2][9]}                 # request 0 ends at its 6th token, request 2 at its 10th
+    want = [P.generate(w, cfg, p, 14, eos=eos, cast=torch.float32) for p in prompts]
+    assert len(want[0]) <= 6 and len(want[2]) <= 10
+    d2 = os.path.join(os.path.dirname(d), "tiny_a_eos")
+    os.makedirs(d2, exist_ok=True)
+    if not os.path.exists(os.path.join(d2, "model.safetensors")):
+        os.link(os.path.join(d, "model.safetensors"), os.path.join(d2, "model.safetensors"))
+    with open(os.path.join(d2, "config.json"), "w") as f:
+        json.dump(dict(cfg, eos_token_id=sorted(eos)), f)
+    eng = Engine(d2, dtype="float32", block_size=page, num_blocks=24, max_batch_size=4, max_token_budget=64)
+    outs = eng.generate(prompts, SamplingParams(max_tokens=14))
+    assert [o.token_ids for o in outs] == want
+    assert [o.finish_reason for o in outs] == ["stop" if len(x) < 14 or x[-1] in eos else "length" for x in want]
+    stream = []
+    for p in prompts:
+        eng.enqueue(p, SamplingParams(max_tokens=14))
+    while eng.has_unfinished():
+        stream.extend(eng.step())
+    per_req = {}
+    for r in stream:
+        per_req.setdefault(r.request_id, []).append(r)
+    assert [[r.token_id for r in v] for v in per_req.values()] == want
+    assert all(v[-1].finished and not any(r.finished for r in v[:-1]) for v in per_req.values())
+    eng.runner.cache.audit()
+    assert eng.runner.cache.free_pages() == 24
+
+
 @pytest.mark.parametrize("dtype,tol", [("float32", 1e-4), ("bfloat16", 6e-2)])
 def test_first_tokens_and_long_decoding(models, dtype, tol):
     """Prompts of 1, 2 and 3 tokens, then 230 tokens decoded one by one through the
