@@ -35,10 +35,13 @@ import os
 GEMM_POLICY = os.environ.get("GOLLMGO_B200_GEMM", "auto")
 
 
+TC_MIN_TOKENS = 1024     # below this the tcgen05 kernel has too few tiles to fill the machine
+
+
 def use_tc(x: torch.Tensor, w: torch.Tensor, out_cols: int, gated: bool) -> bool:
     if GEMM_POLICY == "lib" or not ops.tc_ok(x, w, out_cols):
         return False
-    return GEMM_POLICY == "tc" or gated
+    return GEMM_POLICY == "tc" or (gated and x.shape[0] >= TC_MIN_TOKENS)
 
 
 def linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
