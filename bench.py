@@ -21,15 +21,8 @@ import time
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
-LLAMA_3_1_8B = {      # BASELINE.json configs[2]
-    "architectures": ["LlamaForCausalLM"], "model_type": "llama", "num_hidden_layers": 32,
-    "hidden_size": 4096, "num_attention_heads": 32, "num_key_value_heads": 8, "head_dim": 128,
-    "intermediate_size": 14336, "vocab_size": 128256, "rope_theta": 500000.0,
-    "rope_scaling": {"rope_type": "llama3", "factor": 8.0, "low_freq_factor": 1.0,
-                     "high_freq_factor": 4.0, "original_max_position_embeddings": 8192},
-    "rms_norm_eps": 1e-5, "tie_word_embeddings": False, "max_position_embeddings": 131072,
-    "hidden_act": "silu",
-}
+with open(os.path.join(ROOT, "gollmgo_b200", "bench_shapes", "llama_3_1_8b.json")) as _f:
+    LLAMA_3_1_8B = json.load(_f)      # the layer sizes of the headline configuration
 CONTEXT = 2048          # every sequence starts decoding at this context
 PREFILL_TOKENS = 2048
 PAGE = 16

@@ -308,16 +308,19 @@ int attn_merge_launch(const AttnArgs& a, int dtype, int n_dec, cudaStream_t stre
   return gg_check_launch("attn_merge");
 }
 
-// tile_seq/tile_q0 describe tiles of 16 queries (the general kernel) and
-// tile64_seq/tile64_q0 tiles of 64 queries (the tensor-core kernel); the launcher
-// picks the kernel from dtype and head size.
+// Three tile lists describe the same portions cut into 16, 64 and 128 query rows, for the
+// general kernel, the mma.sync kernel and the tcgen05 kernel; the launcher picks the kernel
+// from dtype, head size and what the caller allows.  T = rows of the q buffer, num_pages =
+// pages of the cache, status = the word the tcgen05 kernel reports a timed-out wait in.
 extern "C" int gg_attn_prefill(const void* q, long long q_stride, const void* kcache,
                                const void* vcache, int dtype, const int* block_tables,
                                int bt_stride, const int* cu_q_lens, const int* context_lens,
                                const int* tile_seq, const int* tile_q0, int num_tiles,
                                const int* tile64_seq, const int* tile64_q0, int num_tiles64,
-                               void* out, int nh, int nkv, int d, int page_size, int window,
-                               float scale, int allow_mma, cudaStream_t stream) {
+                               const int* tile128_seq, const int* tile128_q0, int num_tiles128,
+                               void* out, int T, int num_pages, int nh, int nkv, int d, int page_size,
+                               int window, float scale, int allow_mma, int allow_tc, int* status,
+                               cudaStream_t stream) {
   AttnArgs a = {};
   a.q = q; a.q_stride = q_stride; a.kcache = kcache; a.vcache = vcache;
   a.block_tables = block_tables; a.bt_stride = bt_stride; a.cu_q_lens = cu_q_lens;
@@ -325,6 +328,10 @@ extern "C" int gg_attn_prefill(const void* q, long long q_stride, const void* kc
   a.page_size = page_size; a.window = window; a.scale = scale;
   int rc = check_common(a, "attn_prefill");
   if (rc) return rc;
+  if (allow_tc && tile128_seq && status && attn_tc_supported(dtype, d, page_size) && q_stride % 8 == 0) {
+    a.tile_seq = tile128_seq; a.tile_q0 = tile128_q0;
+    return attn_prefill_tc(a, num_tiles128, T, num_pages, status, stream);
+  }
   if (allow_mma && tile64_seq && attn_mma_supported(dtype, d) && q_stride % 8 == 0) {
     a.tile_seq = tile64_seq; a.tile_q0 = tile64_q0;
     return attn_prefill_mma(a, num_tiles64, stream);

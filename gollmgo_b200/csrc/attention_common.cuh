@@ -33,6 +33,9 @@ int attn_merge_launch(const AttnArgs& a, int dtype, int n_dec, cudaStream_t stre
 bool attn_mma_supported(int dtype, int d);
 int attn_prefill_mma(const AttnArgs& a, int num_tiles, cudaStream_t stream);   // tiles of 64 queries
 int attn_decode_mma(const AttnArgs& a, int n_dec, cudaStream_t stream);
+// bfloat16 tcgen05 kernel for prompt portions, head size 128 (attention_tc.cu); tiles of 128 queries
+bool attn_tc_supported(int dtype, int d, int page_size);
+int attn_prefill_tc(const AttnArgs& a, int num_tiles, int T, int num_pages, int* status, cudaStream_t stream);
 
 __device__ __forceinline__ unsigned smem_u32(const void* p) {
   return (unsigned)__cvta_generic_to_shared(p);

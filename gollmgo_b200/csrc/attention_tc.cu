@@ -1,0 +1,363 @@
+// Causal attention of prompt portions on tcgen05, bfloat16, head size 128.
+//
+// Same contract as the other prompt kernels (attention.cu, attention_mma.cu): keys and
+// values come only from the paged cache through the sequence's block table, masking is by
+// absolute position (and an optional window), kv head = head / (nh/nkv), scale 1/sqrt(d).
+//
+// One CTA takes 128 query rows of one head and walks over the keys 128 at a time:
+//   warp 0   one lane drives TMA: the Q tile once (two 64-column boxes of the qkv
+//            buffer), then per step the K and V tiles, one box of [64 columns x page]
+//            per page and half, from a 4-d tensor map over the cache
+//            [pages, kv heads, page size, d].  A page that is not there (beyond the
+//            context, or given back behind a window) is asked for at a page index past
+//            the end, which TMA fills with zeros.  Two stages each for K and V.
+//   warp 1   one lane issues the MMAs: S = Q K^T (128 x 128 x 128, K-major operands)
+//            into one of two score buffers in tensor memory, and O += P V with V as an
+//            MN-major operand straight from its [key][d] layout.  The product for the
+//            next scores is issued before this step's P V, so the tensor core works on
+//            it while the softmax warps are busy.
+//   warps 2-5  softmax: thread = query row = tensor-memory lane, so row maxima and sums
+//            need no shuffles.  Scores are read with tcgen05.ld, exponentials are
+//            base 2 against a running reference maximum that is only moved (and O
+//            rescaled through tcgen05.ld/st) when a row's maximum has grown by more than
+//            2^8; P goes to shared memory in the swizzled K-major layout the second
+//            product reads.  At the end O is divided by the row sums and stored.
+// Tensor memory: columns [0,128) and [128,256) scores, [256,384) O.
+// All waits are bounded; a wait that runs out sets *status and the CTA winds down.
+#include "attention_common.cuh"
+#include "tc_common.cuh"
+
+#define ATC_D 128
+#define ATC_BQ 128
+#define ATC_BK 128
+#define ATC_THREADS 192
+#define ATC_TILE_BYTES (128 * 128 * 2)     // a 128 x 128 bf16 tile: two halves of [128 rows x 128 B]
+#define ATC_HALF_BYTES (128 * 64 * 2)
+#define ATC_LOG2E 1.4426950408889634f
+
+enum { ATC_ERR_PRODUCER = 11, ATC_ERR_MMA = 12, ATC_ERR_SOFTMAX = 13 };
+
+struct AtcArgs {
+  AttnArgs a;
+  int num_pages;          // pages in the cache (an index >= this is filled with zeros)
+  int* status;
+};
+
+__global__ void __launch_bounds__(ATC_THREADS)
+attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                       const __grid_constant__ CUtensorMap map_v, const AtcArgs args) {
+  extern __shared__ unsigned char atc_smem_raw[];
+  __shared__ __align__(8) unsigned long long bars[16];
+  __shared__ unsigned tmem_base_s;
+  __shared__ int abort_s;
+  const AttnArgs& a = args.a;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const unsigned base = (tc_smem(atc_smem_raw) + 1023u) & ~1023u;
+  const unsigned q_smem = base, k_smem = base + ATC_TILE_BYTES, v_smem = k_smem + 2 * ATC_TILE_BYTES,
+                 p_smem = v_smem + 2 * ATC_TILE_BYTES;
+  const unsigned q_full = tc_smem(&bars[0]), k_full0 = tc_smem(&bars[1]), k_empty0 = tc_smem(&bars[3]),
+                 v_full0 = tc_smem(&bars[5]), v_empty0 = tc_smem(&bars[7]), s_full0 = tc_smem(&bars[9]),
+                 s_empty0 = tc_smem(&bars[11]), p_full = tc_smem(&bars[13]), pv_done = tc_smem(&bars[14]);
+
+  if (threadIdx.x == 0) {
+    mbar_init(q_full, 1);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(k_full0 + 8 * s, 1); mbar_init(k_empty0 + 8 * s, 1);
+      mbar_init(v_full0 + 8 * s, 1); mbar_init(v_empty0 + 8 * s, 1);
+      mbar_init(s_full0 + 8 * s, 1); mbar_init(s_empty0 + 8 * s, 4);
+    }
+    mbar_init(p_full, 4);
+    mbar_init(pv_done, 1);
+    abort_s = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tc_smem(&tmem_base_s)), "r"(512u) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const unsigned tmem_base = tmem_base_s;
+  pdl_trigger();
+  pdl_wait();
+
+  // ---- what this CTA works on
+  const int b = a.tile_seq[blockIdx.x], q0 = a.tile_q0[blockIdx.x];
+  const int h = blockIdx.y, kvh = h / (a.nh / a.nkv);
+  const int t0 = a.cu_q_lens[b], qlen = a.cu_q_lens[b + 1] - t0;
+  const int ctx = a.context_lens[b];
+  const int qstart = ctx - qlen;
+  const int nrows = min(ATC_BQ, qlen - q0);
+  const int first = qstart + q0;                       // position of the tile's first query
+  const int hi = first + nrows;
+  const int lo = a.window > 0 ? max(0, first - a.window + 1) : 0;
+  const int kstart = (lo / ATC_BK) * ATC_BK;
+  const int ntiles = (hi - kstart + ATC_BK - 1) / ATC_BK;
+  const int ps = a.page_size, pages_per_tile = ATC_BK / ps;
+
+  if (warp == 0 && lane == 0) {
+    // ---------------- TMA producer
+    const int* bt = a.block_tables + (size_t)b * a.bt_stride;
+    mbar_expect_tx(q_full, ATC_TILE_BYTES);
+    tma_load_2d(q_smem, &map_q, h * ATC_D, t0 + q0, q_full);
+    tma_load_2d(q_smem + ATC_HALF_BYTES, &map_q, h * ATC_D + 64, t0 + q0, q_full);
+    bool ok = true;
+    for (int j = 0; j < ntiles && ok; ++j) {
+      const int s = j & 1;
+      const unsigned phase = (j >> 1) & 1;
+      const int kb = kstart + j * ATC_BK;
+      int pages[16];
+#pragma unroll
+      for (int p = 0; p < 16; ++p) {
+        const int tok = kb + p * ps;
+        pages[p] = (p < pages_per_tile && tok < hi && tok + ps > lo) ? __ldg(bt + tok / ps) : -1;
+      }
+      for (int which = 0; which < 2 && ok; ++which) {        // keys, then values
+        const unsigned full = (which ? v_full0 : k_full0) + 8 * s, empty = (which ? v_empty0 : k_empty0) + 8 * s;
+        const unsigned dst = (which ? v_smem : k_smem) + s * ATC_TILE_BYTES;
+        const CUtensorMap* map = which ? &map_v : &map_k;
+        if (!mbar_wait(empty, phase ^ 1) || *(volatile int*)&abort_s) { ok = false; break; }
+        mbar_expect_tx(full, ATC_TILE_BYTES);
+#pragma unroll
+        for (int p = 0; p < 16; ++p) {
+          if (p < pages_per_tile) {
+            const int page = pages[p] >= 0 ? pages[p] : args.num_pages;      // past the end: zeros
+            const unsigned row_off = (unsigned)(p * ps * 128);
+            tma_load_4d(dst + row_off, map, 0, 0, kvh, page, full);
+            tma_load_4d(dst + ATC_HALF_BYTES + row_off, map, 64, 0, kvh, page, full);
+          }
+        }
+      }
+    }
+    if (!ok) { atomicExch(args.status, ATC_ERR_PRODUCER); atomicExch(&abort_s, 1); }
+  } else if (warp == 1 && lane == 0) {
+    // ---------------- MMA issuer
+    // instruction descriptors: f32 accumulate, bf16 inputs, M = 128, N = 128
+    const unsigned idesc_qk = (1u << 4) | (1u << 7) | (1u << 10) | ((128u >> 3) << 17) | ((128u >> 4) << 24);
+    const unsigned idesc_pv = idesc_qk | (1u << 16);                 // B (V) is MN-major
+    const unsigned tmem_o = tmem_base + 256;
+    bool ok = mbar_wait(q_full, 0);
+    auto issue_qk = [&](int j) -> bool {
+      const int s = j & 1;
+      const unsigned phase = (j >> 1) & 1;
+      if (!mbar_wait(k_full0 + 8 * s, phase)) return false;
+      if (!mbar_wait(s_empty0 + 8 * s, phase ^ 1)) return false;
+      tc_fence_after();
+      const unsigned kt = k_smem + s * ATC_TILE_BYTES;
+#pragma unroll
+      for (int k = 0; k < ATC_D / 16; ++k) {
+        const unsigned off = (k >> 2) * ATC_HALF_BYTES + (k & 3) * 32;
+        tc_mma(tmem_base + s * 128, tc_smem_desc_lbo(q_smem + off, 1, 64), tc_smem_desc_lbo(kt + off, 1, 64),
+               idesc_qk, k > 0 ? 1u : 0u);
+      }
+      tc_commit(s_full0 + 8 * s);          // scores ready
+      tc_commit(k_empty0 + 8 * s);         // key tile free
+      return true;
+    };
+    if (ok) ok = issue_qk(0);
+    for (int j = 0; j < ntiles && ok; ++j) {
+      if (*(volatile int*)&abort_s) { ok = false; break; }
+      if (j + 1 < ntiles) ok = issue_qk(j + 1);
+      if (!ok) break;
+      const int s = j & 1;
+      if (!mbar_wait(p_full, j & 1)) { ok = false; break; }
+      if (!mbar_wait(v_full0 + 8 * s, (j >> 1) & 1)) { ok = false; break; }
+      tc_fence_after();
+      const unsigned vt = v_smem + s * ATC_TILE_BYTES;
+#pragma unroll
+      for (int k = 0; k < ATC_BK / 16; ++k) {
+        // A = P (K-major: keys contiguous), 16 keys = 32 bytes within a half of 64 keys
+        const unsigned p_off = (k >> 2) * ATC_HALF_BYTES + (k & 3) * 32;
+        // B = V (MN-major: d contiguous): 16 keys further = 16 rows of 128 bytes; the second
+        // half of d is one half tile (LBO) further; groups of 8 keys are 1024 bytes apart (SBO)
+        tc_mma(tmem_o, tc_smem_desc_lbo(p_smem + p_off, 1, 64),
+               tc_smem_desc_lbo(vt + k * 16 * 128, ATC_HALF_BYTES >> 4, 64), idesc_pv, (j > 0 || k > 0) ? 1u : 0u);
+      }
+      tc_commit(pv_done);                  // O holds this step; P may be overwritten
+      tc_commit(v_empty0 + 8 * s);
+    }
+    if (!ok) { atomicExch(args.status, ATC_ERR_MMA); atomicExch(&abort_s, 1); }
+  } else if (warp >= 2) {
+    // ---------------- softmax and epilogue: thread = query row
+    const int quarter = warp & 3;
+    const int r = quarter * 32 + lane;
+    const int pos = first + r;
+    const bool row_ok = r < nrows;
+    const unsigned lane_addr = tmem_base + ((unsigned)(quarter * 32) << 16);
+    const unsigned tmem_o = lane_addr + 256;
+    const float sc = a.scale * ATC_LOG2E;
+    float m_ref = -INFINITY, l = 0.f;
+    bool ok = true;
+    for (int j = 0; j < ntiles && ok; ++j) {
+      const int s = j & 1;
+      const int kb = kstart + j * ATC_BK;
+      if (!mbar_wait(s_full0 + 8 * s, (j >> 1) & 1) || *(volatile int*)&abort_s) { ok = false; break; }
+      tc_fence_after();
+      const unsigned tmem_s = lane_addr + s * 128;
+      const bool interior = kb >= lo && kb + ATC_BK - 1 <= first && (a.window <= 0 || kb > first + nrows - 1 - a.window);
+      // pass 1: the row's maximum over this step's keys
+      float mx = -INFINITY;
+#pragma unroll 1
+      for (int c = 0; c < ATC_BK; c += 32) {
+        unsigned v[32];
+        tc_load32(tmem_s + c, v);
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          const int tk = kb + c + i;
+          const bool keep = interior || (row_ok && tk >= lo && tk <= pos && (a.window <= 0 || tk > pos - a.window));
+          if (keep) mx = fmaxf(mx, __uint_as_float(v[i]));
+        }
+      }
+      mx *= sc;
+      // move the reference maximum only when some row of the warp has outgrown it by 2^8
+      const bool grow = mx > m_ref + 8.f;
+      const bool rescale = __any_sync(0xffffffffu, grow);
+      float alpha = 1.f;
+      if (rescale) {
+        const float m_new = fmaxf(m_ref, mx);
+        alpha = m_new == -INFINITY ? 1.f : exp2f(m_ref - m_new);       // m_ref = -inf gives 0
+        m_ref = m_new;
+        l *= alpha;
+      }
+      if (j > 0) {
+        // the product of the step before must be complete: it read P, and it wrote O
+        if (!mbar_wait(pv_done, (j - 1) & 1)) { ok = false; break; }
+        tc_fence_after();
+        if (rescale) {
+#pragma unroll 1
+          for (int c = 0; c < ATC_D; c += 32) {
+            unsigned v[32];
+            tc_load32(tmem_o + c, v);
+#pragma unroll
+            for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * alpha);
+            tc_store32(tmem_o + c, v);
+          }
+          tc_wait_store();
+        }
+      }
+      // pass 2: p = 2^(s*scale - m_ref), row sum, P to shared memory (bf16, swizzled K-major)
+      const float mr = m_ref == -INFINITY ? 0.f : m_ref;
+      float sum = 0.f;
+#pragma unroll 1
+      for (int c = 0; c < ATC_BK; c += 32) {
+        unsigned v[32];
+        tc_load32(tmem_s + c, v);
+        unsigned pk[16];
+#pragma unroll
+        for (int i = 0; i < 32; i += 2) {
+          const int tk = kb + c + i;
+          const bool k0 = interior || (row_ok && tk >= lo && tk <= pos && (a.window <= 0 || tk > pos - a.window));
+          const bool k1 = interior || (row_ok && tk + 1 >= lo && tk + 1 <= pos && (a.window <= 0 || tk + 1 > pos - a.window));
+          const float p0 = k0 ? exp2f(__uint_as_float(v[i]) * sc - mr) : 0.f;
+          const float p1 = k1 ? exp2f(__uint_as_float(v[i + 1]) * sc - mr) : 0.f;
+          sum += p0 + p1;
+          __nv_bfloat162 t = __floats2bfloat162_rn(p0, p1);
+          pk[i >> 1] = *reinterpret_cast<unsigned*>(&t);
+        }
+        // 32 keys = 64 bytes = four 16-byte chunks of this row in half (c / 64)
+        const unsigned row_base = p_smem + (c >> 6) * ATC_HALF_BYTES + (unsigned)r * 128;
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          const int chunk = ((c & 63) >> 3) + q;
+          const unsigned addr = row_base + (unsigned)((chunk ^ (r & 7)) << 4);
+          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(pk[4 * q]), "r"(pk[4 * q + 1]),
+                       "r"(pk[4 * q + 2]), "r"(pk[4 * q + 3]) : "memory");
+        }
+      }
+      l += sum;
+      fence_async_smem();                  // P is read by the tensor core (async proxy)
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) { mbar_arrive(p_full); mbar_arrive(s_empty0 + 8 * s); }
+    }
+    if (ok && ntiles > 0) ok = mbar_wait(pv_done, (ntiles - 1) & 1);
+    if (!ok) { atomicExch(args.status, ATC_ERR_SOFTMAX); atomicExch(&abort_s, 1); }
+    tc_fence_after();
+    if (ok && !*(volatile int*)&abort_s) {
+      const float inv = l > 0.f ? 1.f / l : 0.f;
+      __nv_bfloat16* o = (__nv_bfloat16*)a.out + (size_t)(t0 + q0 + r) * a.nh * ATC_D + (size_t)h * ATC_D;
+#pragma unroll 1
+      for (int c = 0; c < ATC_D; c += 32) {
+        unsigned v[32];
+        tc_load32(tmem_o + c, v);
+        if (row_ok) {
+#pragma unroll
+          for (int i = 0; i < 32; i += 8) {
+            uint4 pk;
+            __nv_bfloat162 t0v = __floats2bfloat162_rn(__uint_as_float(v[i]) * inv, __uint_as_float(v[i + 1]) * inv);
+            __nv_bfloat162 t1v = __floats2bfloat162_rn(__uint_as_float(v[i + 2]) * inv, __uint_as_float(v[i + 3]) * inv);
+            __nv_bfloat162 t2v = __floats2bfloat162_rn(__uint_as_float(v[i + 4]) * inv, __uint_as_float(v[i + 5]) * inv);
+            __nv_bfloat162 t3v = __floats2bfloat162_rn(__uint_as_float(v[i + 6]) * inv, __uint_as_float(v[i + 7]) * inv);
+            pk.x = *reinterpret_cast<unsigned*>(&t0v); pk.y = *reinterpret_cast<unsigned*>(&t1v);
+            pk.z = *reinterpret_cast<unsigned*>(&t2v); pk.w = *reinterpret_cast<unsigned*>(&t3v);
+            *reinterpret_cast<uint4*>(o + c + i) = pk;
+          }
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512u) : "memory");
+  }
+}
+
+// ---------------------------------------------------------------- host side
+bool attn_tc_supported(int dtype, int d, int page_size) {
+  return dtype == GG_BF16 && d == ATC_D && page_size >= 8 && page_size <= 128 && (page_size & (page_size - 1)) == 0;
+}
+
+static int encode(CUtensorMap* map, const void* ptr, int rank, const cuuint64_t* dims, const cuuint64_t* strides,
+                  const cuuint32_t* box) {
+  GgEncodeTiledFn fn = gg_encode_tiled();
+  if (!fn) return gg_fail(GG_ERR_CUDA, "attn_prefill_tc: the driver has no cuTensorMapEncodeTiled");
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, rank, const_cast<void*>(ptr), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return gg_fail(GG_ERR_CUDA, "attn_prefill_tc: cuTensorMapEncodeTiled failed with %d", (int)r);
+  return GG_OK;
+}
+
+// a.tile_seq / a.tile_q0 list tiles of 128 query rows.  T = rows of the q buffer.
+int attn_prefill_tc(const AttnArgs& a, int num_tiles, int T, int num_pages, int* status, cudaStream_t stream) {
+  GG_REQUIRE(num_tiles >= 0 && a.nh <= 65535, "attn_prefill_tc: bad grid %d x %d", num_tiles, a.nh);
+  GG_REQUIRE(status != nullptr, "attn_prefill_tc: no status word given");
+  GG_REQUIRE(a.q_stride % 8 == 0 && ((size_t)a.q % 16) == 0, "attn_prefill_tc: q rows must be 16-byte aligned");
+  if (num_tiles == 0) return GG_OK;
+  CUtensorMap map_q, map_k, map_v;
+  {
+    cuuint64_t dims[2] = {(cuuint64_t)a.nh * ATC_D, (cuuint64_t)T};
+    cuuint64_t strides[1] = {(cuuint64_t)a.q_stride * 2};
+    cuuint32_t box[2] = {64, ATC_BQ};
+    int rc = encode(&map_q, a.q, 2, dims, strides, box);
+    if (rc) return rc;
+  }
+  {
+    cuuint64_t dims[4] = {ATC_D, (cuuint64_t)a.page_size, (cuuint64_t)a.nkv, (cuuint64_t)num_pages};
+    cuuint64_t strides[3] = {ATC_D * 2, (cuuint64_t)a.page_size * ATC_D * 2, (cuuint64_t)a.nkv * a.page_size * ATC_D * 2};
+    cuuint32_t box[4] = {64, (cuuint32_t)a.page_size, 1, 1};
+    int rc = encode(&map_k, a.kcache, 4, dims, strides, box);
+    if (rc) return rc;
+    rc = encode(&map_v, a.vcache, 4, dims, strides, box);
+    if (rc) return rc;
+  }
+  AtcArgs args;
+  args.a = a;
+  args.num_pages = num_pages;
+  args.status = status;
+  const size_t smem = (size_t)6 * ATC_TILE_BYTES + 1024;       // Q, 2 K, 2 V, P
+  static bool set = false;
+  if (!set) {
+    cudaError_t e = cudaFuncSetAttribute(attn_prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return gg_fail(GG_ERR_CUDA, "attn_prefill_tc: %s", cudaGetErrorString(e));
+    set = true;
+  }
+  cudaError_t e = gg_launch(attn_prefill_tc_kernel, dim3(num_tiles, a.nh), dim3(ATC_THREADS), smem, stream, map_q,
+                            map_k, map_v, args);
+  if (e != cudaSuccess) return gg_fail(GG_ERR_CUDA, "attn_prefill_tc: launch: %s", cudaGetErrorString(e));
+  return gg_check_launch("attn_prefill_tc");
+}

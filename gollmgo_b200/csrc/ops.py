@@ -141,16 +141,25 @@ def attn_prefill(q: torch.Tensor, q_stride: int, kcache: torch.Tensor, vcache: t
                  num_tiles: int, out: torch.Tensor, nh: int, nkv: int, d: int, page_size: int,
                  window: int, scale: float, tile64_seq: Optional[torch.Tensor] = None,
                  tile64_q0: Optional[torch.Tensor] = None, num_tiles64: int = 0,
-                 allow_mma: bool = True) -> None:
+                 allow_mma: bool = True, tile128_seq: Optional[torch.Tensor] = None,
+                 tile128_q0: Optional[torch.Tensor] = None, num_tiles128: int = 0,
+                 allow_tc: bool = True) -> None:
     """Causal attention of prompt portions over the paged cache.  ``tile_*`` list tiles
-    of 16 queries (general kernel), ``tile64_*`` tiles of 64 (tensor-core kernel, used
-    for bfloat16 with head size 64 or 128 when the lists are given)."""
+    of 16 queries (general kernel), ``tile64_*`` of 64 (mma.sync kernel: bfloat16, head
+    size 64 or 128), ``tile128_*`` of 128 (tcgen05 kernel: bfloat16, head size 128); the
+    most specialised kernel whose list is given and that is allowed runs."""
+    global tc_launched
+    use_tc = allow_tc and tile128_seq is not None and kcache.dtype == torch.bfloat16 and d == 128
+    if use_tc:
+        tc_launched = True
     _check(lib().gg_attn_prefill(_p(q), ctypes.c_longlong(q_stride), _p(kcache), _p(vcache),
                                  dtype_code(kcache.dtype), _p(block_tables), bt_stride,
                                  _p(cu_q_lens), _p(context_lens), _p(tile_seq), _p(tile_q0),
-                                 num_tiles, _p(tile64_seq), _p(tile64_q0), num_tiles64, _p(out),
-                                 nh, nkv, d, page_size, window, ctypes.c_float(scale),
-                                 int(allow_mma), _stream()))
+                                 num_tiles, _p(tile64_seq), _p(tile64_q0), num_tiles64,
+                                 _p(tile128_seq), _p(tile128_q0), num_tiles128, _p(out),
+                                 q.shape[0], kcache.shape[0], nh, nkv, d, page_size, window,
+                                 ctypes.c_float(scale), int(allow_mma), int(allow_tc),
+                                 _p(tc_status(q.device)) if use_tc else ctypes.c_void_p(0), _stream()))
 
 
 def attn_decode(q: torch.Tensor, q_stride: int, kcache: torch.Tensor, vcache: torch.Tensor,

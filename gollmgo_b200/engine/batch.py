@@ -16,7 +16,8 @@ import numpy as np
 import torch
 
 ATTN_TILE_ROWS = 16        # query rows of one tile of the general attention kernel (ATT_BQ)
-ATTN_TILE_ROWS_MMA = 64    # ... and of the tensor-core kernel (csrc/attention_mma.cu)
+ATTN_TILE_ROWS_MMA = 64    # ... of the mma.sync kernel (csrc/attention_mma.cu)
+ATTN_TILE_ROWS_TC = 128    # ... and of the tcgen05 kernel (csrc/attention_tc.cu)
 
 
 @dataclass
@@ -51,6 +52,9 @@ class StepBatch:
     tile64_seq: torch.Tensor
     tile64_q0: torch.Tensor
     num_tiles64: int
+    tile128_seq: torch.Tensor
+    tile128_q0: torch.Tensor
+    num_tiles128: int
     dec_seqs: torch.Tensor
     slot_mapping: List[torch.Tensor]
     block_tables: List[torch.Tensor]
@@ -68,9 +72,10 @@ def _align(n: int) -> int:
 class BatchLayout:
     """Offsets of every array in the packed int32 buffer, for given capacities."""
 
-    def __init__(self, T: int, B: int, R: int, NT: int, ND: int, G: int, stride: int, NT64: int = 0):
+    def __init__(self, T: int, B: int, R: int, NT: int, ND: int, G: int, stride: int, NT64: int = 0,
+                 NT128: int = 0):
         self.T, self.B, self.R, self.NT, self.ND, self.G, self.stride = T, B, R, NT, ND, G, stride
-        self.NT64 = NT64
+        self.NT64, self.NT128 = NT64, NT128
         off = 0
 
         def take(n):
@@ -90,6 +95,8 @@ class BatchLayout:
         self.tile_q0 = take(NT)
         self.tile64_seq = take(NT64)
         self.tile64_q0 = take(NT64)
+        self.tile128_seq = take(NT128)
+        self.tile128_q0 = take(NT128)
         self.dec_seqs = take(ND)
         self.block_tables = [take(B * stride) for _ in range(G)]
         self.size = off
@@ -153,6 +160,8 @@ class BatchBuilder:
         tiles = [(b, q0) for b in range(B) if q_lens[b] > 1 for q0 in range(0, q_lens[b], ATTN_TILE_ROWS)]
         tiles64 = [(b, q0) for b in range(B) if q_lens[b] > 1
                    for q0 in range(0, q_lens[b], ATTN_TILE_ROWS_MMA)]
+        tiles128 = [(b, q0) for b in range(B) if q_lens[b] > 1
+                    for q0 in range(0, q_lens[b], ATTN_TILE_ROWS_TC)]
         dec = [b for b in range(B) if q_lens[b] == 1]
         max_pages = max(len(cache.block_table(e.request_id, g)) for e in entries for g in range(G)) if G else 1
         Bp = fixed_seqs if fixed_seqs is not None else B
@@ -168,7 +177,7 @@ class BatchBuilder:
             base += n
         rows.extend(range(T, Tp))    # ... whose logits are computed and ignored
         R = len(rows)
-        lay = BatchLayout(Tp, Bp, R, len(tiles), len(dec) + (Bp - B), G, stride, len(tiles64))
+        lay = BatchLayout(Tp, Bp, R, len(tiles), len(dec) + (Bp - B), G, stride, len(tiles64), len(tiles128))
         if static_dev is None:
             self._ensure(lay.size)
             if self._copied is not None:
@@ -210,6 +219,8 @@ class BatchBuilder:
             h[lay.tile_q0:lay.tile_q0 + len(tiles)] = [t[1] for t in tiles]
             h[lay.tile64_seq:lay.tile64_seq + len(tiles64)] = [t[0] for t in tiles64]
             h[lay.tile64_q0:lay.tile64_q0 + len(tiles64)] = [t[1] for t in tiles64]
+            h[lay.tile128_seq:lay.tile128_seq + len(tiles128)] = [t[0] for t in tiles128]
+            h[lay.tile128_q0:lay.tile128_q0 + len(tiles128)] = [t[1] for t in tiles128]
         nd = len(dec) + (Bp - B)
         h[lay.dec_seqs:lay.dec_seqs + len(dec)] = dec
         h[lay.dec_seqs + len(dec):lay.dec_seqs + nd] = -1
@@ -241,6 +252,8 @@ class BatchBuilder:
         sb.tile_seq, sb.tile_q0 = v(lay.tile_seq, len(tiles)), v(lay.tile_q0, len(tiles))
         sb.tile64_seq, sb.tile64_q0 = v(lay.tile64_seq, len(tiles64)), v(lay.tile64_q0, len(tiles64))
         sb.num_tiles64 = len(tiles64)
+        sb.tile128_seq, sb.tile128_q0 = v(lay.tile128_seq, len(tiles128)), v(lay.tile128_q0, len(tiles128))
+        sb.num_tiles128 = len(tiles128)
         sb.dec_seqs = v(lay.dec_seqs, nd)
         sb.slot_mapping = [v(o, Tp) for o in lay.slot_mapping]
         sb.block_tables = [v(o, Bp * stride) for o in lay.block_tables]

@@ -10,6 +10,7 @@ three weights stacked.
 from __future__ import annotations
 
 import math
+import os
 
 import torch
 
@@ -19,6 +20,10 @@ from ..weights import WeightSpec
 from .linear import linear
 from .registry import build_position, register_mixer
 
+# Which prompt-attention kernel the bfloat16 mode uses: "auto" = the most specialised one that
+# takes the sizes (tcgen05 for head size 128, mma.sync for 64), "mma" = no tcgen05 kernel,
+# "general" = only the general kernel.
+ATTN_POLICY = os.environ.get("GOLLMGO_B200_ATTN", "auto")
 MAX_SPLITS = 16
 CTAS_PER_SM = 3            # decode attention CTAs resident on one SM (csrc/attention_mma.cu)
 ASSUMED_TILES = 32         # context the choice is tuned for: 32 tiles of 64 keys
@@ -105,7 +110,10 @@ class Attention:
             ops.attn_prefill(qkv, self.qkv_width, kc, vc, bt, batch.bt_stride, batch.cu_q_lens,
                              batch.context_lens, batch.tile_seq, batch.tile_q0, batch.num_tiles,
                              out, self.nh, self.nkv, self.d, self.ctx.page_size, window, self.scale,
-                             batch.tile64_seq, batch.tile64_q0, batch.num_tiles64)
+                             batch.tile64_seq, batch.tile64_q0, batch.num_tiles64,
+                             allow_mma=ATTN_POLICY != "general",
+                             tile128_seq=batch.tile128_seq, tile128_q0=batch.tile128_q0,
+                             num_tiles128=batch.num_tiles128, allow_tc=ATTN_POLICY == "auto")
         if batch.num_decode:
             splits = decode_splits(batch.num_decode, self._ctas_per_split, self.num_sms)
             ops.attn_decode(qkv, self.qkv_width, kc, vc, bt, batch.bt_stride, batch.cu_q_lens,

@@ -220,18 +220,20 @@ def test_attn_decode(ops, cuda_device, dtype, nh, nkv, d, page, window, allow_mm
         torch.testing.assert_close(out.double(), ref, **tol(dtype))
 
 
-@pytest.mark.parametrize("allow_mma", [False, True])
+@pytest.mark.parametrize("allow_mma", [False, True, "tc"])
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("nh,nkv,d,page,window", [
     (4, 2, 16, 16, 0), (4, 1, 32, 8, 0), (5, 5, 48, 32, 24), (32, 8, 128, 16, 0), (6, 3, 96, 16, 40),
-    (6, 2, 64, 8, 0), (3, 1, 64, 32, 50), (5, 5, 128, 16, 70)])
+    (6, 2, 64, 8, 0), (3, 1, 64, 32, 50), (5, 5, 128, 16, 70), (2, 1, 128, 8, 0), (4, 4, 128, 64, 130)])
 def test_attn_prefill(ops, cuda_device, dtype, nh, nkv, d, page, window, allow_mma):
     """Portions of several sequences in one launch: (cached before, portion length)."""
-    if allow_mma and not (dtype == torch.bfloat16 and d in (64, 128)):
-        pytest.skip("the tensor-core kernel takes bfloat16 with head size 64 or 128")
+    if allow_mma is True and not (dtype == torch.bfloat16 and d in (64, 128)):
+        pytest.skip("the mma.sync kernel takes bfloat16 with head size 64 or 128")
+    if allow_mma == "tc" and not (dtype == torch.bfloat16 and d == 128):
+        pytest.skip("the tcgen05 kernel takes bfloat16 with head size 128")
     torch.manual_seed(5)
     shapes = [(0, 1), (0, 2), (0, 16), (0, 17), (5, 2), (13, 40), (64, 64), (100, 33), (250, 3), (0, 130),
-              (1, 63), (63, 65), (0, 64), (7, 200)]
+              (1, 63), (63, 65), (0, 64), (7, 200), (0, 128), (127, 129), (300, 260)]
     seqs, qs, refs, q_lens = [], [], [], []
     for i, (start, n) in enumerate(shapes):
         ctx = start + n
@@ -259,10 +261,17 @@ def test_attn_prefill(ops, cuda_device, dtype, nh, nkv, d, page, window, allow_m
     random.Random(7).shuffle(tiles64)
     t64_seq = torch.tensor([t[0] for t in tiles64], dtype=torch.int32, device="cuda")
     t64_q0 = torch.tensor([t[1] for t in tiles64], dtype=torch.int32, device="cuda")
+    tiles128 = [(b, q0) for b, n in enumerate(q_lens) for q0 in range(0, n, 128)]
+    random.Random(8).shuffle(tiles128)
+    t128_seq = torch.tensor([t[0] for t in tiles128], dtype=torch.int32, device="cuda")
+    t128_q0 = torch.tensor([t[1] for t in tiles128], dtype=torch.int32, device="cuda")
     out = torch.zeros(T, nh * d, device="cuda", dtype=dtype)
     ops.attn_prefill(buf, width, kc, vc, bt, stride, cu, ctx_t, tile_seq, tile_q0, len(tiles), out,
                      nh, nkv, d, page, window, 1 / math.sqrt(d), t64_seq, t64_q0, len(tiles64),
-                     allow_mma=allow_mma)
+                     allow_mma=bool(allow_mma), tile128_seq=t128_seq, tile128_q0=t128_q0,
+                     num_tiles128=len(tiles128), allow_tc=allow_mma == "tc")
+    if allow_mma == "tc":
+        ops.check_tc_status("cuda")
     torch.testing.assert_close(out.double(), torch.cat(refs).reshape(T, nh * d), **tol(dtype))
 
 
