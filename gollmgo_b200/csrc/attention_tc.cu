@@ -5,9 +5,9 @@
 // absolute position (and an optional window), kv head = head / (nh/nkv), scale 1/sqrt(d).
 //
 // One CTA takes 128 query rows of one head and walks over the keys 128 at a time:
-//   warp 0   one lane drives TMA: the Q tile once (two 64-column boxes of the qkv
-//            buffer), then per step the K and V tiles, one box of [64 columns x page]
-//            per page and half, from a 4-d tensor map over the cache
+//   warp 0   drives TMA: the Q tile once (two 64-column boxes of the qkv buffer), then
+//            per step the K and V tiles, lane p fetching page p as one box of
+//            [64 columns x page] per half, from a 4-d tensor map over the cache
 //            [pages, kv heads, page size, d].  A page that is not there (beyond the
 //            context, or given back behind a window) is asked for at a page index past
 //            the end, which TMA fills with zeros.  Two stages each for K and V.
@@ -17,7 +17,8 @@
 //            next scores is issued before this step's P V, so the tensor core works on
 //            it while the softmax warps are busy.
 //   warps 2-5  softmax: thread = query row = tensor-memory lane, so row maxima and sums
-//            need no shuffles.  Scores are read with tcgen05.ld, exponentials are
+//            need no shuffles.  A row's 128 scores are read once with tcgen05.ld and
+//            kept in registers, exponentials are
 //            base 2 against a running reference maximum that is only moved (and O
 //            rescaled through tcgen05.ld/st) when a row's maximum has grown by more than
 //            2^8; P goes to shared memory in the swizzled K-major layout the second
@@ -26,6 +27,7 @@
 // All waits are bounded; a wait that runs out sets *status and the CTA winds down.
 #include "attention_common.cuh"
 #include "tc_common.cuh"
+// fast_exp2 comes with attention_common.cuh
 
 #define ATC_D 128
 #define ATC_BQ 128
@@ -83,8 +85,10 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
   pdl_wait();
 
   // ---- what this CTA works on
-  const int b = a.tile_seq[blockIdx.x], q0 = a.tile_q0[blockIdx.x];
-  const int h = blockIdx.y, kvh = h / (a.nh / a.nkv);
+  // grid (heads, tiles): the heads of one tile are neighbours, and the caller lists the tiles
+  // with the most keys first, so the long ones start early and the short ones fill the end
+  const int b = a.tile_seq[blockIdx.y], q0 = a.tile_q0[blockIdx.y];
+  const int h = blockIdx.x, kvh = h / (a.nh / a.nkv);
   const int t0 = a.cu_q_lens[b], qlen = a.cu_q_lens[b + 1] - t0;
   const int ctx = a.context_lens[b];
   const int qstart = ctx - qlen;
@@ -96,41 +100,44 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
   const int ntiles = (hi - kstart + ATC_BK - 1) / ATC_BK;
   const int ps = a.page_size, pages_per_tile = ATC_BK / ps;
 
-  if (warp == 0 && lane == 0) {
-    // ---------------- TMA producer
+  if (warp == 0) {
+    // ---------------- TMA producer: the whole warp; lane p fetches page p of a tile (two
+    // boxes, one per half of d), first for the keys, then for the values, so the block
+    // table look-ups and the issue of the many small copies run side by side
     const int* bt = a.block_tables + (size_t)b * a.bt_stride;
-    mbar_expect_tx(q_full, ATC_TILE_BYTES);
-    tma_load_2d(q_smem, &map_q, h * ATC_D, t0 + q0, q_full);
-    tma_load_2d(q_smem + ATC_HALF_BYTES, &map_q, h * ATC_D + 64, t0 + q0, q_full);
+    if (lane == 0) {
+      mbar_expect_tx(q_full, ATC_TILE_BYTES);
+      tma_load_2d(q_smem, &map_q, h * ATC_D, t0 + q0, q_full);
+      tma_load_2d(q_smem + ATC_HALF_BYTES, &map_q, h * ATC_D + 64, t0 + q0, q_full);
+    }
     bool ok = true;
     for (int j = 0; j < ntiles && ok; ++j) {
       const int s = j & 1;
       const unsigned phase = (j >> 1) & 1;
       const int kb = kstart + j * ATC_BK;
-      int pages[16];
-#pragma unroll
-      for (int p = 0; p < 16; ++p) {
-        const int tok = kb + p * ps;
-        pages[p] = (p < pages_per_tile && tok < hi && tok + ps > lo) ? __ldg(bt + tok / ps) : -1;
+      int page = -1;
+      if (lane < pages_per_tile) {
+        const int tok = kb + lane * ps;
+        if (tok < hi && tok + ps > lo) page = __ldg(bt + tok / ps);
+        if (page < 0) page = args.num_pages;                   // past the end: TMA fills zeros
       }
-      for (int which = 0; which < 2 && ok; ++which) {        // keys, then values
+      const unsigned row_off = (unsigned)(lane * ps * 128);
+      for (int which = 0; which < 2 && ok; ++which) {          // keys, then values
         const unsigned full = (which ? v_full0 : k_full0) + 8 * s, empty = (which ? v_empty0 : k_empty0) + 8 * s;
         const unsigned dst = (which ? v_smem : k_smem) + s * ATC_TILE_BYTES;
         const CUtensorMap* map = which ? &map_v : &map_k;
-        if (!mbar_wait(empty, phase ^ 1) || *(volatile int*)&abort_s) { ok = false; break; }
-        mbar_expect_tx(full, ATC_TILE_BYTES);
-#pragma unroll
-        for (int p = 0; p < 16; ++p) {
-          if (p < pages_per_tile) {
-            const int page = pages[p] >= 0 ? pages[p] : args.num_pages;      // past the end: zeros
-            const unsigned row_off = (unsigned)(p * ps * 128);
-            tma_load_4d(dst + row_off, map, 0, 0, kvh, page, full);
-            tma_load_4d(dst + ATC_HALF_BYTES + row_off, map, 64, 0, kvh, page, full);
-          }
+        ok = mbar_wait(empty, phase ^ 1) && !*(volatile int*)&abort_s;
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        if (lane == 0) mbar_expect_tx(full, ATC_TILE_BYTES);
+        __syncwarp();
+        if (lane < pages_per_tile) {
+          tma_load_4d(dst + row_off, map, 0, 0, kvh, page, full);
+          tma_load_4d(dst + ATC_HALF_BYTES + row_off, map, 64, 0, kvh, page, full);
         }
       }
     }
-    if (!ok) { atomicExch(args.status, ATC_ERR_PRODUCER); atomicExch(&abort_s, 1); }
+    if (!ok && lane == 0) { atomicExch(args.status, ATC_ERR_PRODUCER); atomicExch(&abort_s, 1); }
   } else if (warp == 1 && lane == 0) {
     // ---------------- MMA issuer
     // instruction descriptors: f32 accumulate, bf16 inputs, M = 128, N = 128
@@ -196,20 +203,30 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       tc_fence_after();
       const unsigned tmem_s = lane_addr + s * 128;
       const bool interior = kb >= lo && kb + ATC_BK - 1 <= first && (a.window <= 0 || kb > first + nrows - 1 - a.window);
-      // pass 1: the row's maximum over this step's keys
-      float mx = -INFINITY;
-#pragma unroll 1
+      // the row's 128 scores, once, into registers (scaled to base 2; masked ones -inf)
+      float sv[ATC_BK];
+#pragma unroll
       for (int c = 0; c < ATC_BK; c += 32) {
         unsigned v[32];
         tc_load32(tmem_s + c, v);
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          const int tk = kb + c + i;
-          const bool keep = interior || (row_ok && tk >= lo && tk <= pos && (a.window <= 0 || tk > pos - a.window));
-          if (keep) mx = fmaxf(mx, __uint_as_float(v[i]));
+        for (int i = 0; i < 32; ++i) sv[c + i] = __uint_as_float(v[i]) * sc;
+      }
+      // the scores are in registers: the buffer can take the scores after next
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(s_empty0 + 8 * s);
+      if (!interior) {
+#pragma unroll
+        for (int i = 0; i < ATC_BK; ++i) {
+          const int tk = kb + i;
+          const bool keep = row_ok && tk >= lo && tk <= pos && (a.window <= 0 || tk > pos - a.window);
+          if (!keep) sv[i] = -INFINITY;
         }
       }
-      mx *= sc;
+      float mx = -INFINITY;
+#pragma unroll
+      for (int i = 0; i < ATC_BK; ++i) mx = fmaxf(mx, sv[i]);
       // move the reference maximum only when some row of the warp has outgrown it by 2^8
       const bool grow = mx > m_ref + 8.f;
       const bool rescale = __any_sync(0xffffffffu, grow);
@@ -236,40 +253,30 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
           tc_wait_store();
         }
       }
-      // pass 2: p = 2^(s*scale - m_ref), row sum, P to shared memory (bf16, swizzled K-major)
+      // p = 2^(s - m_ref), row sum, P to shared memory (bf16, swizzled K-major)
       const float mr = m_ref == -INFINITY ? 0.f : m_ref;
       float sum = 0.f;
-#pragma unroll 1
-      for (int c = 0; c < ATC_BK; c += 32) {
-        unsigned v[32];
-        tc_load32(tmem_s + c, v);
-        unsigned pk[16];
 #pragma unroll
-        for (int i = 0; i < 32; i += 2) {
-          const int tk = kb + c + i;
-          const bool k0 = interior || (row_ok && tk >= lo && tk <= pos && (a.window <= 0 || tk > pos - a.window));
-          const bool k1 = interior || (row_ok && tk + 1 >= lo && tk + 1 <= pos && (a.window <= 0 || tk + 1 > pos - a.window));
-          const float p0 = k0 ? exp2f(__uint_as_float(v[i]) * sc - mr) : 0.f;
-          const float p1 = k1 ? exp2f(__uint_as_float(v[i + 1]) * sc - mr) : 0.f;
+      for (int c = 0; c < ATC_BK; c += 8) {
+        unsigned pk[4];
+#pragma unroll
+        for (int i = 0; i < 8; i += 2) {
+          const float p0 = fast_exp2(sv[c + i] - mr), p1 = fast_exp2(sv[c + i + 1] - mr);   // 2^-inf = 0
           sum += p0 + p1;
           __nv_bfloat162 t = __floats2bfloat162_rn(p0, p1);
           pk[i >> 1] = *reinterpret_cast<unsigned*>(&t);
         }
-        // 32 keys = 64 bytes = four 16-byte chunks of this row in half (c / 64)
-        const unsigned row_base = p_smem + (c >> 6) * ATC_HALF_BYTES + (unsigned)r * 128;
-#pragma unroll
-        for (int q = 0; q < 4; ++q) {
-          const int chunk = ((c & 63) >> 3) + q;
-          const unsigned addr = row_base + (unsigned)((chunk ^ (r & 7)) << 4);
-          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(pk[4 * q]), "r"(pk[4 * q + 1]),
-                       "r"(pk[4 * q + 2]), "r"(pk[4 * q + 3]) : "memory");
-        }
+        // 8 keys = one 16-byte chunk of this row in half (c / 64)
+        const unsigned addr = p_smem + (c >> 6) * ATC_HALF_BYTES + (unsigned)r * 128 +
+                              (unsigned)((((c & 63) >> 3) ^ (r & 7)) << 4);
+        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(pk[0]), "r"(pk[1]), "r"(pk[2]),
+                     "r"(pk[3]) : "memory");
       }
       l += sum;
       fence_async_smem();                  // P is read by the tensor core (async proxy)
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) { mbar_arrive(p_full); mbar_arrive(s_empty0 + 8 * s); }
+      if (lane == 0) mbar_arrive(p_full);
     }
     if (ok && ntiles > 0) ok = mbar_wait(pv_done, (ntiles - 1) & 1);
     if (!ok) { atomicExch(args.status, ATC_ERR_SOFTMAX); atomicExch(&abort_s, 1); }
@@ -324,7 +331,7 @@ static int encode(CUtensorMap* map, const void* ptr, int rank, const cuuint64_t*
 
 // a.tile_seq / a.tile_q0 list tiles of 128 query rows.  T = rows of the q buffer.
 int attn_prefill_tc(const AttnArgs& a, int num_tiles, int T, int num_pages, int* status, cudaStream_t stream) {
-  GG_REQUIRE(num_tiles >= 0 && a.nh <= 65535, "attn_prefill_tc: bad grid %d x %d", num_tiles, a.nh);
+  GG_REQUIRE(num_tiles >= 0 && num_tiles <= 65535, "attn_prefill_tc: %d tiles in one launch", num_tiles);
   GG_REQUIRE(status != nullptr, "attn_prefill_tc: no status word given");
   GG_REQUIRE(a.q_stride % 8 == 0 && ((size_t)a.q % 16) == 0, "attn_prefill_tc: q rows must be 16-byte aligned");
   if (num_tiles == 0) return GG_OK;
@@ -356,7 +363,7 @@ int attn_prefill_tc(const AttnArgs& a, int num_tiles, int T, int num_pages, int*
     if (e != cudaSuccess) return gg_fail(GG_ERR_CUDA, "attn_prefill_tc: %s", cudaGetErrorString(e));
     set = true;
   }
-  cudaError_t e = gg_launch(attn_prefill_tc_kernel, dim3(num_tiles, a.nh), dim3(ATC_THREADS), smem, stream, map_q,
+  cudaError_t e = gg_launch(attn_prefill_tc_kernel, dim3(a.nh, num_tiles), dim3(ATC_THREADS), smem, stream, map_q,
                             map_k, map_v, args);
   if (e != cudaSuccess) return gg_fail(GG_ERR_CUDA, "attn_prefill_tc: launch: %s", cudaGetErrorString(e));
   return gg_check_launch("attn_prefill_tc");

@@ -162,6 +162,7 @@ class BatchBuilder:
                    for q0 in range(0, q_lens[b], ATTN_TILE_ROWS_MMA)]
         tiles128 = [(b, q0) for b in range(B) if q_lens[b] > 1
                     for q0 in range(0, q_lens[b], ATTN_TILE_ROWS_TC)]
+        tiles128.sort(key=lambda t: -(q_starts[t[0]] + t[1]))      # most keys to attend to first
         dec = [b for b in range(B) if q_lens[b] == 1]
         max_pages = max(len(cache.block_table(e.request_id, g)) for e in entries for g in range(G)) if G else 1
         Bp = fixed_seqs if fixed_seqs is not None else B

@@ -119,12 +119,21 @@ def attn_prefill(args) -> None:
     ctxs = torch.tensor([T], dtype=torch.int32, device="cuda")
     t16 = torch.arange(0, T, 16, dtype=torch.int32, device="cuda")
     t64 = torch.arange(0, T, 64, dtype=torch.int32, device="cuda")
+    t128 = torch.arange(0, T, 128, dtype=torch.int32, device="cuda").flip(0).contiguous()   # longest first
     out = torch.empty(T, nh * d, device="cuda", dtype=torch.bfloat16)
-    t = _time(lambda i: ops.attn_prefill(q, q.shape[1], kc, vc, tables[i % 4:i % 4 + 1].contiguous(), stride, cu,
-                                         ctxs, torch.zeros_like(t16), t16, len(t16), out, nh, nkv, d, page, 0,
-                                         1 / math.sqrt(d), torch.zeros_like(t64), t64, len(t64)), args.reps)
     flops = 2.0 * 2.0 * nh * d * T * T / 2
-    print(f"attn_prefill T={T} heads={nh}/{nkv} d={d}: {t:7.1f} us {flops / t / 1e6:6.1f} TFLOP/s (causal)", flush=True)
+    for name, tc in (("tcgen05", True), ("mma.sync", False)):
+        if tc and d != 128:
+            continue
+        t = _time(lambda i: ops.attn_prefill(q, q.shape[1], kc, vc, tables[i % 4:i % 4 + 1].contiguous(), stride, cu,
+                                             ctxs, torch.zeros_like(t16), t16, len(t16), out, nh, nkv, d, page, 0,
+                                             1 / math.sqrt(d), torch.zeros_like(t64), t64, len(t64),
+                                             tile128_seq=torch.zeros_like(t128), tile128_q0=t128,
+                                             num_tiles128=len(t128), allow_tc=tc), args.reps)
+        if tc:
+            ops.check_tc_status("cuda")
+        print(f"attn_prefill ({name}) T={T} heads={nh}/{nkv} d={d}: {t:7.1f} us {flops / t / 1e6:6.1f} TFLOP/s (causal)",
+              flush=True)
 
 
 def main(argv=None) -> int:
