@@ -179,14 +179,19 @@ class BatchBuilder:
         rows.extend(range(T, Tp))    # ... whose logits are computed and ignored
         R = len(rows)
         lay = BatchLayout(Tp, Bp, R, len(tiles), len(dec) + (Bp - B), G, stride, len(tiles64), len(tiles128))
+        # on the host the block tables are packed with only as many columns as are in use; with a
+        # fixed (wide) device stride they are copied as a 2-d block, not as the whole table
+        used = min(stride, max(1, max_pages))
+        hlay = lay if used == stride else BatchLayout(Tp, Bp, R, len(tiles), len(dec) + (Bp - B), G, used,
+                                                      len(tiles64), len(tiles128))
         if static_dev is None:
             self._ensure(lay.size)
             if self._copied is not None:
                 self._copied.synchronize()
-        host = self._host if static_dev is None else torch.empty(lay.size, dtype=torch.int32,
+        host = self._host if static_dev is None else torch.empty(hlay.size, dtype=torch.int32,
                                                                   pin_memory=self.device.type == "cuda")
         h = host.numpy()
-        h[:lay.size] = 0
+        h[:hlay.size] = 0
         flat_tokens = np.fromiter((t for e in entries for t in e.tokens), dtype=np.int64, count=T)
         h[lay.token_ids:lay.token_ids + T] = flat_tokens
         h[lay.token_src:lay.token_src + Tp] = -1
@@ -226,7 +231,7 @@ class BatchBuilder:
         h[lay.dec_seqs:lay.dec_seqs + len(dec)] = dec
         h[lay.dec_seqs + len(dec):lay.dec_seqs + nd] = -1
         for g in range(G):
-            bt = h[lay.block_tables[g]:lay.block_tables[g] + Bp * stride].reshape(Bp, stride)
+            bt = h[hlay.block_tables[g]:hlay.block_tables[g] + Bp * used].reshape(Bp, used)
             bt[:] = -1
             for b, e in enumerate(entries):
                 pages = cache.block_table(e.request_id, g)
@@ -234,13 +239,19 @@ class BatchBuilder:
         dev = self._dev if static_dev is None else static_dev
         if dev.numel() < lay.size:
             raise ValueError("static batch buffer is too small for this layout")
-        if self.device.type == "cuda":
-            dev[:lay.size].copy_(host[:lay.size], non_blocking=True)
-            if static_dev is None:
-                self._copied = torch.cuda.Event()
-                self._copied.record()
+        cuda = self.device.type == "cuda"
+        if hlay is lay:
+            dev[:lay.size].copy_(host[:lay.size], non_blocking=cuda)
         else:
-            dev[:lay.size].copy_(host[:lay.size])
+            head = lay.block_tables[0] if G else lay.size          # everything before the block tables
+            dev[:head].copy_(host[:head], non_blocking=cuda)
+            for g in range(G):
+                src = host[hlay.block_tables[g]:hlay.block_tables[g] + Bp * used].view(Bp, used)
+                dev[lay.block_tables[g]:lay.block_tables[g] + Bp * stride].view(Bp, stride)[:, :used] \
+                    .copy_(src, non_blocking=cuda)
+        if cuda and static_dev is None:
+            self._copied = torch.cuda.Event()
+            self._copied.record()
 
         sb = StepBatch()
         sb.num_tokens, sb.num_seqs, sb.num_logit_rows = Tp, Bp, R
