@@ -29,9 +29,26 @@ __device__ __forceinline__ float uniform_draw(unsigned long long seed, unsigned 
 __device__ int block_argmax(const float* row, int V, float* red_f, int* red_i, float* max_out) {
   float best = -INFINITY;
   int bi = 0x7fffffff;
-  for (int i = threadIdx.x; i < V; i += blockDim.x) {
-    const float v = row[i];
-    if (v > best || (v == best && i < bi)) { best = v; bi = i; }
+  if ((((size_t)row) & 15) == 0) {
+    // four values per load; within a thread indices only grow, so ">" keeps the first maximum
+    const int V4 = V >> 2;
+    const float4* row4 = reinterpret_cast<const float4*>(row);
+    for (int i = threadIdx.x; i < V4; i += blockDim.x) {
+      const float4 v = row4[i];
+      if (v.x > best) { best = v.x; bi = 4 * i; }
+      if (v.y > best) { best = v.y; bi = 4 * i + 1; }
+      if (v.z > best) { best = v.z; bi = 4 * i + 2; }
+      if (v.w > best) { best = v.w; bi = 4 * i + 3; }
+    }
+    for (int i = (V4 << 2) + threadIdx.x; i < V; i += blockDim.x) {
+      const float v = row[i];
+      if (v > best || (v == best && i < bi)) { best = v; bi = i; }
+    }
+  } else {
+    for (int i = threadIdx.x; i < V; i += blockDim.x) {
+      const float v = row[i];
+      if (v > best || (v == best && i < bi)) { best = v; bi = i; }
+    }
   }
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
 #pragma unroll

@@ -190,7 +190,7 @@ def test_attn_decode(ops, cuda_device, dtype, nh, nkv, d, page, window, allow_mm
     if allow_mma and not (dtype == torch.bfloat16 and d in (64, 128)):
         pytest.skip("the tensor-core kernel takes bfloat16 with head size 64 or 128")
     torch.manual_seed(4)
-    ctxs = [1, 2, page - 1, page, page + 1, 63, 64, 65, 127, 129, 300, 777]
+    ctxs = [1, 2, page - 1, page, page + 1, 63, 64, 65, 127, 129, 300, 777, 3000, 5001]
     B = len(ctxs)
     seqs, qs, refs = [], [], []
     for i, ctx in enumerate(ctxs):
@@ -198,6 +198,8 @@ def test_attn_decode(ops, cuda_device, dtype, nh, nkv, d, page, window, allow_mm
         q = torch.randn(1, nh, d, device="cuda")
         lo = max(0, ctx - window) if window else 0
         far = [lo, min(ctx - 1, lo + 1), ctx - 1, (lo + ctx) // 2, max(lo, ctx - 65)][i % 5]
+        if ctx > 2000:
+            far = lo + 3                                               # a key thousands of tokens back
         spike(q, k, v, i % nh, (i % nh) // (nh // nkv), far)
         q, k, v = q.to(dtype), k.to(dtype), v.to(dtype)
         seqs.append((k, v)), qs.append(q)
@@ -233,7 +235,7 @@ def test_attn_prefill(ops, cuda_device, dtype, nh, nkv, d, page, window, allow_m
         pytest.skip("the tcgen05 kernel takes bfloat16 with head size 128")
     torch.manual_seed(5)
     shapes = [(0, 1), (0, 2), (0, 16), (0, 17), (5, 2), (13, 40), (64, 64), (100, 33), (250, 3), (0, 130),
-              (1, 63), (63, 65), (0, 64), (7, 200), (0, 128), (127, 129), (300, 260)]
+              (1, 63), (63, 65), (0, 64), (7, 200), (0, 128), (127, 129), (300, 260), (2100, 700)]
     seqs, qs, refs, q_lens = [], [], [], []
     for i, (start, n) in enumerate(shapes):
         ctx = start + n
