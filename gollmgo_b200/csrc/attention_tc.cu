@@ -1,4 +1,4 @@
-// Causal attention of prompt portions on tcgen05, bfloat16, head size 128.
+// Causal attention of prompt portions on tcgen05, bfloat16, head sizes 64 and 128.
 //
 // Same contract as the other prompt kernels (attention.cu, attention_mma.cu): keys and
 // values come only from the paged cache through the sequence's block table, masking is by
@@ -29,12 +29,11 @@
 #include "tc_common.cuh"
 // fast_exp2 comes with attention_common.cuh
 
-#define ATC_D 128
 #define ATC_BQ 128
 #define ATC_BK 128
 #define ATC_THREADS 192
-#define ATC_TILE_BYTES (128 * 128 * 2)     // a 128 x 128 bf16 tile: two halves of [128 rows x 128 B]
-#define ATC_HALF_BYTES (128 * 64 * 2)
+#define ATC_HALF_BYTES (128 * 64 * 2)       // [128 rows x 64 columns] bf16: rows of 128 bytes, swizzled
+#define ATC_P_BYTES (2 * ATC_HALF_BYTES)    // P: 128 rows x 128 keys
 #define ATC_LOG2E 1.4426950408889634f
 
 enum { ATC_ERR_PRODUCER = 11, ATC_ERR_MMA = 12, ATC_ERR_SOFTMAX = 13 };
@@ -45,6 +44,8 @@ struct AtcArgs {
   int* status;
 };
 
+// A Q, K or V tile is [128 rows x D]: D/64 halves.
+template <int D>
 __global__ void __launch_bounds__(ATC_THREADS)
 attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                        const __grid_constant__ CUtensorMap map_v, const AtcArgs args) {
@@ -52,6 +53,9 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
   __shared__ __align__(8) unsigned long long bars[16];
   __shared__ unsigned tmem_base_s;
   __shared__ int abort_s;
+  constexpr int ATC_D = D;
+  constexpr int HALVES = D / 64;
+  constexpr unsigned ATC_TILE_BYTES = HALVES * ATC_HALF_BYTES;
   const AttnArgs& a = args.a;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const unsigned base = (tc_smem(atc_smem_raw) + 1023u) & ~1023u;
@@ -107,8 +111,9 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     const int* bt = a.block_tables + (size_t)b * a.bt_stride;
     if (lane == 0) {
       mbar_expect_tx(q_full, ATC_TILE_BYTES);
-      tma_load_2d(q_smem, &map_q, h * ATC_D, t0 + q0, q_full);
-      tma_load_2d(q_smem + ATC_HALF_BYTES, &map_q, h * ATC_D + 64, t0 + q0, q_full);
+#pragma unroll
+      for (int hf = 0; hf < HALVES; ++hf)
+        tma_load_2d(q_smem + hf * ATC_HALF_BYTES, &map_q, h * ATC_D + hf * 64, t0 + q0, q_full);
     }
     bool ok = true;
     for (int j = 0; j < ntiles && ok; ++j) {
@@ -132,17 +137,19 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         if (lane == 0) mbar_expect_tx(full, ATC_TILE_BYTES);
         __syncwarp();
         if (lane < pages_per_tile) {
-          tma_load_4d(dst + row_off, map, 0, 0, kvh, page, full);
-          tma_load_4d(dst + ATC_HALF_BYTES + row_off, map, 64, 0, kvh, page, full);
+#pragma unroll
+          for (int hf = 0; hf < HALVES; ++hf)
+            tma_load_4d(dst + hf * ATC_HALF_BYTES + row_off, map, hf * 64, 0, kvh, page, full);
         }
       }
     }
     if (!ok && lane == 0) { atomicExch(args.status, ATC_ERR_PRODUCER); atomicExch(&abort_s, 1); }
   } else if (warp == 1 && lane == 0) {
     // ---------------- MMA issuer
-    // instruction descriptors: f32 accumulate, bf16 inputs, M = 128, N = 128
+    // instruction descriptors: f32 accumulate, bf16 inputs, M = 128; scores: N = 128 keys
     const unsigned idesc_qk = (1u << 4) | (1u << 7) | (1u << 10) | ((128u >> 3) << 17) | ((128u >> 4) << 24);
-    const unsigned idesc_pv = idesc_qk | (1u << 16);                 // B (V) is MN-major
+    // O += P V: N = D, B (V) is MN-major
+    const unsigned idesc_pv = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | (((unsigned)D >> 3) << 17) | ((128u >> 4) << 24);
     const unsigned tmem_o = tmem_base + 256;
     bool ok = mbar_wait(q_full, 0);
     auto issue_qk = [&](int j) -> bool {
@@ -314,7 +321,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
 
 // ---------------------------------------------------------------- host side
 bool attn_tc_supported(int dtype, int d, int page_size) {
-  return dtype == GG_BF16 && d == ATC_D && page_size >= 8 && page_size <= 128 && (page_size & (page_size - 1)) == 0;
+  return dtype == GG_BF16 && (d == 64 || d == 128) && page_size >= 8 && page_size <= 128 && (page_size & (page_size - 1)) == 0;
 }
 
 static int encode(CUtensorMap* map, const void* ptr, int rank, const cuuint64_t* dims, const cuuint64_t* strides,
@@ -337,15 +344,16 @@ int attn_prefill_tc(const AttnArgs& a, int num_tiles, int T, int num_pages, int*
   if (num_tiles == 0) return GG_OK;
   CUtensorMap map_q, map_k, map_v;
   {
-    cuuint64_t dims[2] = {(cuuint64_t)a.nh * ATC_D, (cuuint64_t)T};
+    cuuint64_t dims[2] = {(cuuint64_t)a.nh * a.d, (cuuint64_t)T};
     cuuint64_t strides[1] = {(cuuint64_t)a.q_stride * 2};
     cuuint32_t box[2] = {64, ATC_BQ};
     int rc = encode(&map_q, a.q, 2, dims, strides, box);
     if (rc) return rc;
   }
   {
-    cuuint64_t dims[4] = {ATC_D, (cuuint64_t)a.page_size, (cuuint64_t)a.nkv, (cuuint64_t)num_pages};
-    cuuint64_t strides[3] = {ATC_D * 2, (cuuint64_t)a.page_size * ATC_D * 2, (cuuint64_t)a.nkv * a.page_size * ATC_D * 2};
+    const cuuint64_t D = (cuuint64_t)a.d;
+    cuuint64_t dims[4] = {D, (cuuint64_t)a.page_size, (cuuint64_t)a.nkv, (cuuint64_t)num_pages};
+    cuuint64_t strides[3] = {D * 2, (cuuint64_t)a.page_size * D * 2, (cuuint64_t)a.nkv * a.page_size * D * 2};
     cuuint32_t box[4] = {64, (cuuint32_t)a.page_size, 1, 1};
     int rc = encode(&map_k, a.kcache, 4, dims, strides, box);
     if (rc) return rc;
@@ -356,15 +364,28 @@ int attn_prefill_tc(const AttnArgs& a, int num_tiles, int T, int num_pages, int*
   args.a = a;
   args.num_pages = num_pages;
   args.status = status;
-  const size_t smem = (size_t)6 * ATC_TILE_BYTES + 1024;       // Q, 2 K, 2 V, P
-  static bool set = false;
-  if (!set) {
-    cudaError_t e = cudaFuncSetAttribute(attn_prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) return gg_fail(GG_ERR_CUDA, "attn_prefill_tc: %s", cudaGetErrorString(e));
-    set = true;
+  const size_t tile_bytes = (size_t)(a.d / 64) * ATC_HALF_BYTES;
+  const size_t smem = 5 * tile_bytes + ATC_P_BYTES + 1024;     // Q, 2 K, 2 V, P
+  cudaError_t e;
+  if (a.d == 128) {
+    static bool set = false;
+    if (!set) {
+      e = cudaFuncSetAttribute(attn_prefill_tc_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+      if (e != cudaSuccess) return gg_fail(GG_ERR_CUDA, "attn_prefill_tc: %s", cudaGetErrorString(e));
+      set = true;
+    }
+    e = gg_launch(attn_prefill_tc_kernel<128>, dim3(a.nh, num_tiles), dim3(ATC_THREADS), smem, stream, map_q, map_k,
+                  map_v, args);
+  } else {
+    static bool set = false;
+    if (!set) {
+      e = cudaFuncSetAttribute(attn_prefill_tc_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+      if (e != cudaSuccess) return gg_fail(GG_ERR_CUDA, "attn_prefill_tc: %s", cudaGetErrorString(e));
+      set = true;
+    }
+    e = gg_launch(attn_prefill_tc_kernel<64>, dim3(a.nh, num_tiles), dim3(ATC_THREADS), smem, stream, map_q, map_k,
+                  map_v, args);
   }
-  cudaError_t e = gg_launch(attn_prefill_tc_kernel, dim3(a.nh, num_tiles), dim3(ATC_THREADS), smem, stream, map_q,
-                            map_k, map_v, args);
   if (e != cudaSuccess) return gg_fail(GG_ERR_CUDA, "attn_prefill_tc: launch: %s", cudaGetErrorString(e));
   return gg_check_launch("attn_prefill_tc");
 }

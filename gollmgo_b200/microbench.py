@@ -123,7 +123,7 @@ def attn_prefill(args) -> None:
     out = torch.empty(T, nh * d, device="cuda", dtype=torch.bfloat16)
     flops = 2.0 * 2.0 * nh * d * T * T / 2
     for name, tc in (("tcgen05", True), ("mma.sync", False)):
-        if tc and d != 128:
+        if tc and d not in (64, 128):
             continue
         t = _time(lambda i: ops.attn_prefill(q, q.shape[1], kc, vc, tables[i % 4:i % 4 + 1].contiguous(), stride, cu,
                                              ctxs, torch.zeros_like(t16), t16, len(t16), out, nh, nkv, d, page, 0,

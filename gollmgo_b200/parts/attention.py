@@ -21,7 +21,7 @@ from .linear import linear
 from .registry import build_position, register_mixer
 
 # Which prompt-attention kernel the bfloat16 mode uses: "auto" = the most specialised one that
-# takes the sizes (tcgen05 for head size 128, mma.sync for 64), "mma" = no tcgen05 kernel,
+# takes the sizes (tcgen05 for head sizes 64 and 128 in prompt portions, mma.sync for decode), "mma" = no tcgen05 kernel,
 # "general" = only the general kernel.
 ATTN_POLICY = os.environ.get("GOLLMGO_B200_ATTN", "auto")
 MAX_SPLITS = 16

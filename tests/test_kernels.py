@@ -231,8 +231,8 @@ def test_attn_prefill(ops, cuda_device, dtype, nh, nkv, d, page, window, allow_m
     """Portions of several sequences in one launch: (cached before, portion length)."""
     if allow_mma is True and not (dtype == torch.bfloat16 and d in (64, 128)):
         pytest.skip("the mma.sync kernel takes bfloat16 with head size 64 or 128")
-    if allow_mma == "tc" and not (dtype == torch.bfloat16 and d == 128):
-        pytest.skip("the tcgen05 kernel takes bfloat16 with head size 128")
+    if allow_mma == "tc" and not (dtype == torch.bfloat16 and d in (64, 128)):
+        pytest.skip("the tcgen05 kernel takes bfloat16 with head size 64 or 128")
     torch.manual_seed(5)
     shapes = [(0, 1), (0, 2), (0, 16), (0, 17), (5, 2), (13, 40), (64, 64), (100, 33), (250, 3), (0, 130),
               (1, 63), (63, 65), (0, 64), (7, 200), (0, 128), (127, 129), (300, 260), (2100, 700)]
