@@ -16,9 +16,10 @@
 //            MN-major operand straight from its [key][d] layout.  The product for the
 //            next scores is issued before this step's P V, so the tensor core works on
 //            it while the softmax warps are busy.
-//   warps 2-5  softmax: thread = query row = tensor-memory lane, so row maxima and sums
-//            need no shuffles.  A row's 128 scores are read once with tcgen05.ld and
-//            kept in registers, exponentials are
+//   warps 2-9  softmax: two threads per query row (row = tensor-memory lane; each takes
+//            64 of a step's 128 keys and half of O's columns), so row maxima and sums
+//            need no shuffles, only one exchange per step.  A thread's 64 scores are read
+//            once with tcgen05.ld and kept in registers, exponentials are
 //            base 2 against a running reference maximum that is only moved (and O
 //            rescaled through tcgen05.ld/st) when a row's maximum has grown by more than
 //            2^8; P goes to shared memory in the swizzled K-major layout the second
@@ -31,12 +32,28 @@
 
 #define ATC_BQ 128
 #define ATC_BK 128
-#define ATC_THREADS 192
+#define ATC_THREADS 320                     // TMA warp, MMA warp, eight softmax warps
+#define ATC_SOFTMAX_THREADS 256
 #define ATC_HALF_BYTES (128 * 64 * 2)       // [128 rows x 64 columns] bf16: rows of 128 bytes, swizzled
 #define ATC_P_BYTES (2 * ATC_HALF_BYTES)    // P: 128 rows x 128 keys
 #define ATC_LOG2E 1.4426950408889634f
 
 enum { ATC_ERR_PRODUCER = 11, ATC_ERR_MMA = 12, ATC_ERR_SOFTMAX = 13 };
+
+// Barrier over the 256 softmax threads only (named barrier 1), and the same with a vote:
+// true only if every thread passes true.  Every softmax thread reaches these in the same
+// order whatever its waits returned, so nobody is left behind at one.
+__device__ __forceinline__ void softmax_sync() { asm volatile("bar.sync 1, 256;" ::: "memory"); }
+__device__ __forceinline__ bool softmax_all(bool mine) {
+  unsigned out;
+  asm volatile(
+      "{\n\t.reg .pred p, q;\n\t"
+      "setp.ne.b32 q, %1, 0;\n\t"
+      "bar.red.and.pred p, 1, 256, q;\n\t"
+      "selp.b32 %0, 1, 0, p;\n\t}"
+      : "=r"(out) : "r"((unsigned)mine) : "memory");
+  return out != 0;
+}
 
 struct AtcArgs {
   AttnArgs a;
@@ -53,6 +70,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
   __shared__ __align__(8) unsigned long long bars[16];
   __shared__ unsigned tmem_base_s;
   __shared__ int abort_s;
+  __shared__ float xchg[2][2][ATC_BQ];       // [step parity][half][row]: row maxima of the two halves
+  __shared__ float xsum[2][ATC_BQ];
   constexpr int ATC_D = D;
   constexpr int HALVES = D / 64;
   constexpr unsigned ATC_TILE_BYTES = HALVES * ATC_HALF_BYTES;
@@ -70,9 +89,9 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     for (int s = 0; s < 2; ++s) {
       mbar_init(k_full0 + 8 * s, 1); mbar_init(k_empty0 + 8 * s, 1);
       mbar_init(v_full0 + 8 * s, 1); mbar_init(v_empty0 + 8 * s, 1);
-      mbar_init(s_full0 + 8 * s, 1); mbar_init(s_empty0 + 8 * s, 4);
+      mbar_init(s_full0 + 8 * s, 1); mbar_init(s_empty0 + 8 * s, 8);
     }
-    mbar_init(p_full, 4);
+    mbar_init(p_full, 8);
     mbar_init(pv_done, 1);
     abort_s = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -193,27 +212,32 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     }
     if (!ok) { atomicExch(args.status, ATC_ERR_MMA); atomicExch(&abort_s, 1); }
   } else if (warp >= 2) {
-    // ---------------- softmax and epilogue: thread = query row
-    const int quarter = warp & 3;
+    // ---------------- softmax and epilogue: two threads per query row.  Warps 2-5 take the
+    // first 64 keys of a step (and the first half of O's columns), warps 6-9 the second; a
+    // warp reads the tensor-memory lanes of its quarter (warp % 4).  The two threads of a row
+    // exchange their maxima through shared memory once per step and their sums at the end.
+    const int quarter = warp & 3, sub = (warp - 2) >> 2;
     const int r = quarter * 32 + lane;
     const int pos = first + r;
     const bool row_ok = r < nrows;
     const unsigned lane_addr = tmem_base + ((unsigned)(quarter * 32) << 16);
-    const unsigned tmem_o = lane_addr + 256;
+    constexpr int OC = D / 2;                             // O columns of this thread
+    const unsigned tmem_o = lane_addr + 256 + sub * OC;
     const float sc = a.scale * ATC_LOG2E;
     float m_ref = -INFINITY, l = 0.f;
     bool ok = true;
-    for (int j = 0; j < ntiles && ok; ++j) {
+    for (int j = 0; j < ntiles; ++j) {
       const int s = j & 1;
-      const int kb = kstart + j * ATC_BK;
-      if (!mbar_wait(s_full0 + 8 * s, (j >> 1) & 1) || *(volatile int*)&abort_s) { ok = false; break; }
+      const int kb = kstart + j * ATC_BK + sub * 64;      // first key of this thread's 64
+      ok = softmax_all(mbar_wait(s_full0 + 8 * s, (j >> 1) & 1) && !*(volatile int*)&abort_s);
+      if (!ok) break;
       tc_fence_after();
-      const unsigned tmem_s = lane_addr + s * 128;
-      const bool interior = kb >= lo && kb + ATC_BK - 1 <= first && (a.window <= 0 || kb > first + nrows - 1 - a.window);
-      // the row's 128 scores, once, into registers (scaled to base 2; masked ones -inf)
-      float sv[ATC_BK];
+      const unsigned tmem_s = lane_addr + s * 128 + sub * 64;
+      const bool interior = kb >= lo && kb + 63 <= first && (a.window <= 0 || kb > first + nrows - 1 - a.window);
+      // the row's 64 scores, once, into registers (scaled to base 2; masked ones -inf)
+      float sv[64];
 #pragma unroll
-      for (int c = 0; c < ATC_BK; c += 32) {
+      for (int c = 0; c < 64; c += 32) {
         unsigned v[32];
         tc_load32(tmem_s + c, v);
 #pragma unroll
@@ -225,7 +249,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       if (lane == 0) mbar_arrive(s_empty0 + 8 * s);
       if (!interior) {
 #pragma unroll
-        for (int i = 0; i < ATC_BK; ++i) {
+        for (int i = 0; i < 64; ++i) {
           const int tk = kb + i;
           const bool keep = row_ok && tk >= lo && tk <= pos && (a.window <= 0 || tk > pos - a.window);
           if (!keep) sv[i] = -INFINITY;
@@ -233,7 +257,10 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       }
       float mx = -INFINITY;
 #pragma unroll
-      for (int i = 0; i < ATC_BK; ++i) mx = fmaxf(mx, sv[i]);
+      for (int i = 0; i < 64; ++i) mx = fmaxf(mx, sv[i]);
+      xchg[j & 1][sub][r] = mx;
+      softmax_sync();
+      mx = fmaxf(mx, xchg[j & 1][sub ^ 1][r]);
       // move the reference maximum only when some row of the warp has outgrown it by 2^8
       const bool grow = mx > m_ref + 8.f;
       const bool rescale = __any_sync(0xffffffffu, grow);
@@ -246,11 +273,12 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       }
       if (j > 0) {
         // the product of the step before must be complete: it read P, and it wrote O
-        if (!mbar_wait(pv_done, (j - 1) & 1)) { ok = false; break; }
+        ok = softmax_all(mbar_wait(pv_done, (j - 1) & 1));
+        if (!ok) break;
         tc_fence_after();
         if (rescale) {
-#pragma unroll 1
-          for (int c = 0; c < ATC_D; c += 32) {
+#pragma unroll
+          for (int c = 0; c < OC; c += 32) {
             unsigned v[32];
             tc_load32(tmem_o + c, v);
 #pragma unroll
@@ -260,11 +288,12 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
           tc_wait_store();
         }
       }
-      // p = 2^(s - m_ref), row sum, P to shared memory (bf16, swizzled K-major)
+      // p = 2^(s - m_ref), row sum, P to shared memory (bf16, swizzled K-major): this thread's
+      // 64 keys are half `sub` of the P tile
       const float mr = m_ref == -INFINITY ? 0.f : m_ref;
       float sum = 0.f;
 #pragma unroll
-      for (int c = 0; c < ATC_BK; c += 8) {
+      for (int c = 0; c < 64; c += 8) {
         unsigned pk[4];
 #pragma unroll
         for (int i = 0; i < 8; i += 2) {
@@ -273,9 +302,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
           __nv_bfloat162 t = __floats2bfloat162_rn(p0, p1);
           pk[i >> 1] = *reinterpret_cast<unsigned*>(&t);
         }
-        // 8 keys = one 16-byte chunk of this row in half (c / 64)
-        const unsigned addr = p_smem + (c >> 6) * ATC_HALF_BYTES + (unsigned)r * 128 +
-                              (unsigned)((((c & 63) >> 3) ^ (r & 7)) << 4);
+        const unsigned addr = p_smem + sub * ATC_HALF_BYTES + (unsigned)r * 128 + (unsigned)(((c >> 3) ^ (r & 7)) << 4);
         asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(pk[0]), "r"(pk[1]), "r"(pk[2]),
                      "r"(pk[3]) : "memory");
       }
@@ -285,14 +312,18 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       __syncwarp();
       if (lane == 0) mbar_arrive(p_full);
     }
-    if (ok && ntiles > 0) ok = mbar_wait(pv_done, (ntiles - 1) & 1);
+    if (ok && ntiles > 0) ok = softmax_all(mbar_wait(pv_done, (ntiles - 1) & 1));
     if (!ok) { atomicExch(args.status, ATC_ERR_SOFTMAX); atomicExch(&abort_s, 1); }
+    // the row's sum is the two threads' sums (both used the same reference maxima)
+    xsum[sub][r] = l;
+    softmax_sync();
+    l += xsum[sub ^ 1][r];
     tc_fence_after();
     if (ok && !*(volatile int*)&abort_s) {
       const float inv = l > 0.f ? 1.f / l : 0.f;
-      __nv_bfloat16* o = (__nv_bfloat16*)a.out + (size_t)(t0 + q0 + r) * a.nh * ATC_D + (size_t)h * ATC_D;
-#pragma unroll 1
-      for (int c = 0; c < ATC_D; c += 32) {
+      __nv_bfloat16* o = (__nv_bfloat16*)a.out + (size_t)(t0 + q0 + r) * a.nh * ATC_D + (size_t)h * ATC_D + sub * OC;
+#pragma unroll
+      for (int c = 0; c < OC; c += 32) {
         unsigned v[32];
         tc_load32(tmem_o + c, v);
         if (row_ok) {

@@ -66,7 +66,7 @@ template <int MODE>
 __global__ void __launch_bounds__(TC_THREADS)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
                void* __restrict__ out, int M, int N, int K, int tiles_m, int num_tiles,
-               int* __restrict__ status) {
+               int* __restrict__ status, int withhold_loads) {
   constexpr int BN = 256;
   constexpr unsigned A_BYTES = TC_BM * TC_BK * 2, B_BYTES = BN * TC_BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
   extern __shared__ unsigned char tc_smem_raw[];
@@ -98,8 +98,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
   pdl_trigger();
   pdl_wait();                                   // x is the previous kernel's output
 
-  if (warp == 0 && lane == 0) {
-    // ---------------- TMA producer
+  if (warp == 0 && lane == 0 && !withhold_loads) {
+    // ---------------- TMA producer (withhold_loads: the self-test of the bounded waits; nothing is
+    // loaded, so the consumers' waits must run out, report, and let the CTA return)
     int issued = 0, it = 0;
     bool ok = true;
     for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
@@ -240,8 +241,24 @@ static int make_map(CUtensorMap* map, const void* ptr, int rows, int cols, long 
 // mode: 0 = bfloat16 out [M, N]; 1 = float32 out [M, N]; 2 = W is [2N, K] (gate rows then up
 // rows), out is bfloat16 [M, N] = silu(x Wg^T) * (x Wu^T).  status: one int in device memory,
 // left untouched unless a wait inside the kernel ran out (then non-zero).
+static int gemm_tc_launch(const void* x, long long ldx, const void* W, void* out, int M, int N, int K,
+                          int mode, int* status, int withhold_loads, cudaStream_t stream);
+
 extern "C" int gg_gemm_tc(const void* x, long long ldx, const void* W, void* out, int M, int N, int K,
                           int mode, int* status, cudaStream_t stream) {
+  return gemm_tc_launch(x, ldx, W, out, M, N, K, mode, status, 0, stream);
+}
+
+// Self-test of the bounded waits: the same launch, but the loads are withheld, so no barrier a
+// consumer waits on ever completes.  The kernel must set *status non-zero and return within a
+// few seconds, leaving the context usable.  out is not written.
+extern "C" int gg_gemm_tc_withheld(const void* x, long long ldx, const void* W, void* out, int M, int N,
+                                   int K, int* status, cudaStream_t stream) {
+  return gemm_tc_launch(x, ldx, W, out, M, N, K, TC_OUT_BF16, status, 1, stream);
+}
+
+static int gemm_tc_launch(const void* x, long long ldx, const void* W, void* out, int M, int N, int K,
+                          int mode, int* status, int withhold_loads, cudaStream_t stream) {
   GG_REQUIRE(M >= 0 && N > 0 && K > 0, "gemm_tc: bad sizes M=%d N=%d K=%d", M, N, K);
   GG_REQUIRE(K % 8 == 0 && ldx % 8 == 0, "gemm_tc: K=%d and the row stride %lld of x must be multiples of 8", K, ldx);
   GG_REQUIRE(((size_t)x % 16) == 0 && ((size_t)W % 16) == 0, "gemm_tc: x and W must be 16-byte aligned");
@@ -279,7 +296,7 @@ extern "C" int gg_gemm_tc(const void* x, long long ldx, const void* W, void* out
       if (e != cudaSuccess) return gg_fail(GG_ERR_CUDA, "gemm_tc: %s", cudaGetErrorString(e));            \
       set = true;                                                                                         \
     }                                                                                                     \
-    e = gg_launch(gemm_tc_kernel<MODE>, grid, dim3(TC_THREADS), smem, stream, map_x, map_w, out, M, N, K, tiles_m, num_tiles, status); \
+    e = gg_launch(gemm_tc_kernel<MODE>, grid, dim3(TC_THREADS), smem, stream, map_x, map_w, out, M, N, K, tiles_m, num_tiles, status, withhold_loads); \
   } while (0)
   if (mode == TC_OUT_BF16) TC_LAUNCH(TC_OUT_BF16);
   else if (mode == TC_OUT_F32) TC_LAUNCH(TC_OUT_F32);

@@ -254,6 +254,16 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, gated: bool = F
                             _p(tc_status(x.device)), _stream()))
 
 
+def gemm_tc_withheld(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
+    """Self-test of gemm_tc's bounded waits: launches it with its loads withheld.  The kernel
+    gives up after about a second, sets the status word and returns (check_tc_status raises)."""
+    M, K = x.shape
+    global tc_launched
+    tc_launched = True
+    _check(lib().gg_gemm_tc_withheld(_p(x), ctypes.c_longlong(x.stride(0)), _p(w), _p(out), M, out.shape[1], K,
+                                     _p(tc_status(x.device)), _stream()))
+
+
 def argmax(logits: torch.Tensor, out: torch.Tensor) -> None:
     """out[r] = first index of the maximum of logits[r, :] (float32 [R, V])."""
     _cuda(logits, out)

@@ -6,7 +6,7 @@
 
 #include "common.cuh"
 
-#define TC_SPIN_LIMIT (1u << 22)
+#define TC_SPIN_LIMIT (1u << 20)       // about a second: each try carries a suspend hint of a microsecond
 
 
 __device__ __forceinline__ unsigned tc_smem(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }

@@ -432,3 +432,24 @@ def test_gemm_tc_gated(ops, cuda_device, M, I, K):
     gate, up = gu[:, :I], gu[:, I:]
     ref = gate / (1 + torch.exp(-gate)) * up
     torch.testing.assert_close(out.float(), ref.to(torch.bfloat16).float(), rtol=1e-2, atol=1e-2)
+
+
+def test_gemm_tc_bounded_waits_report_and_return(ops, cuda_device):
+    """No barrier inside the tcgen05 kernels is waited on without a limit.  With the loads
+    withheld nothing a consumer waits for ever arrives: the kernel must give up, say so in its
+    status word, free its tensor memory and return, and the next launch must work as usual."""
+    import time
+    x = torch.randn(128, 256, device="cuda").to(torch.bfloat16)
+    w = torch.randn(256, 256, device="cuda").to(torch.bfloat16)
+    out = torch.zeros(128, 256, device="cuda", dtype=torch.bfloat16)
+    torch.cuda.synchronize()
+    t0 = time.time()
+    ops.gemm_tc_withheld(x, w, out)
+    torch.cuda.synchronize()
+    assert time.time() - t0 < 30
+    with pytest.raises(ops.KernelError, match="gave up waiting"):
+        ops.check_tc_status("cuda")
+    ops.check_tc_status("cuda")                                        # the word was cleared
+    ops.gemm_tc(x, w, out)                                             # tensor memory was given back
+    ops.check_tc_status("cuda")
+    torch.testing.assert_close(out.float(), (x.float() @ w.float().T).to(torch.bfloat16).float(), rtol=1e-2, atol=1e-2)
