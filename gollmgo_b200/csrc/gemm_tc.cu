@@ -33,31 +33,6 @@
 enum { TC_OUT_BF16 = 0, TC_OUT_F32 = 1, TC_OUT_SILU = 2 };
 enum { TC_ERR_EMPTY_WAIT = 1, TC_ERR_FULL_WAIT = 2, TC_ERR_ACC_WAIT = 3, TC_ERR_DRAIN = 4 };
 
-// Stores 32 consecutive outputs of one row; `valid` of them lie inside the matrix.
-__device__ __forceinline__ void store_row32(__nv_bfloat16* o, const float* v, int valid) {
-  if (valid >= 32 && ((size_t)o % 16) == 0) {
-#pragma unroll
-    for (int j = 0; j < 32; j += 8) {
-      uint4 pk;
-      __nv_bfloat162 t0 = __floats2bfloat162_rn(v[j], v[j + 1]), t1 = __floats2bfloat162_rn(v[j + 2], v[j + 3]);
-      __nv_bfloat162 t2 = __floats2bfloat162_rn(v[j + 4], v[j + 5]), t3 = __floats2bfloat162_rn(v[j + 6], v[j + 7]);
-      pk.x = *reinterpret_cast<unsigned*>(&t0); pk.y = *reinterpret_cast<unsigned*>(&t1);
-      pk.z = *reinterpret_cast<unsigned*>(&t2); pk.w = *reinterpret_cast<unsigned*>(&t3);
-      *reinterpret_cast<uint4*>(o + j) = pk;
-    }
-  } else {
-    for (int j = 0; j < 32 && j < valid; ++j) o[j] = __float2bfloat16_rn(v[j]);
-  }
-}
-__device__ __forceinline__ void store_row32(float* o, const float* v, int valid) {
-  if (valid >= 32 && ((size_t)o % 16) == 0) {
-#pragma unroll
-    for (int j = 0; j < 32; j += 4) *reinterpret_cast<float4*>(o + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
-  } else {
-    for (int j = 0; j < 32 && j < valid; ++j) o[j] = v[j];
-  }
-}
-
 // A persistent CTA walks over output tiles blockIdx.x, blockIdx.x + gridDim.x, ...; tile t is
 // (row block t % tiles_m, column block t / tiles_m), so CTAs that run together share a block of
 // W.  The accumulator is double-buffered in tensor memory (2 x 256 columns): while the
@@ -224,7 +199,7 @@ GgEncodeTiledFn gg_encode_tiled() {
 
 // Tensor map of a row-major bf16 matrix [rows, cols] with row stride ld (elements), boxes of
 // box_rows x 64 columns, 128-byte swizzle, zero fill outside.
-static int make_map(CUtensorMap* map, const void* ptr, int rows, int cols, long long ld, int box_rows) {
+int gg_make_map_2d(CUtensorMap* map, const void* ptr, int rows, int cols, long long ld, int box_rows) {
   GgEncodeTiledFn fn = gg_encode_tiled();
   if (!fn) return gg_fail(GG_ERR_CUDA, "gemm_tc: the driver has no cuTensorMapEncodeTiled");
   cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
@@ -268,10 +243,10 @@ static int gemm_tc_launch(const void* x, long long ldx, const void* W, void* out
   GG_REQUIRE(status != nullptr, "gemm_tc: no status word given");
   if (M == 0) return GG_OK;
   CUtensorMap map_x, map_w;
-  int rc = make_map(&map_x, x, M, K, ldx, TC_BM);
+  int rc = gg_make_map_2d(&map_x, x, M, K, ldx, TC_BM);
   if (rc) return rc;
   const int w_rows = mode == TC_OUT_SILU ? 2 * N : N;
-  rc = make_map(&map_w, W, w_rows, K, K, mode == TC_OUT_SILU ? 128 : 256);
+  rc = gg_make_map_2d(&map_w, W, w_rows, K, K, mode == TC_OUT_SILU ? 128 : 256);
   if (rc) return rc;
   const int n_tile = mode == TC_OUT_SILU ? 128 : 256;
   const int tiles_m = (M + TC_BM - 1) / TC_BM, tiles_n = (N + n_tile - 1) / n_tile;

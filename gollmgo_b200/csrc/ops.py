@@ -235,10 +235,12 @@ def tc_ok(x: torch.Tensor, w: torch.Tensor, out_cols: int) -> bool:
             and out_cols % 2 == 0)
 
 
-def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, gated: bool = False) -> None:
+def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, gated: bool = False,
+            pair: bool = False) -> None:
     """out[M, N] = x[M, K] @ w[N, K]^T on tcgen05 (bfloat16 in, float32 accumulate in tensor
     memory); out bfloat16 or float32.  ``gated``: w is [2N, K] (gate rows, then up rows) and
-    out = silu(x Wg^T) * (x Wu^T) in bfloat16."""
+    out = silu(x Wg^T) * (x Wu^T) in bfloat16.  ``pair``: the kernel in which two CTAs on two
+    SMs share a 256 x 256 tile (cta_group::2)."""
     M, K = x.shape
     N = out.shape[1]
     if w.shape != ((2 * N, K) if gated else (N, K)) or out.shape[0] != M or not out.is_contiguous():
@@ -250,8 +252,9 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, gated: bool = F
     mode = 2 if gated else (1 if out.dtype == torch.float32 else 0)
     global tc_launched
     tc_launched = True
-    _check(lib().gg_gemm_tc(_p(x), ctypes.c_longlong(x.stride(0)), _p(w), _p(out), M, N, K, mode,
-                            _p(tc_status(x.device)), _stream()))
+    fn = lib().gg_gemm_tc2 if pair else lib().gg_gemm_tc
+    _check(fn(_p(x), ctypes.c_longlong(x.stride(0)), _p(w), _p(out), M, N, K, mode,
+              _p(tc_status(x.device)), _stream()))
 
 
 def gemm_tc_withheld(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:

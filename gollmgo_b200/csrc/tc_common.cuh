@@ -104,8 +104,37 @@ __device__ __forceinline__ unsigned long long tc_smem_desc_lbo(unsigned addr, un
          ((unsigned long long)sbo16 << 32) | (1ull << 46) | (2ull << 61);
 }
 
+// Stores 32 consecutive outputs of one row; `valid` of them lie inside the matrix.
+__device__ __forceinline__ void store_row32(__nv_bfloat16* o, const float* v, int valid) {
+  if (valid >= 32 && ((size_t)o % 16) == 0) {
+#pragma unroll
+    for (int j = 0; j < 32; j += 8) {
+      uint4 pk;
+      __nv_bfloat162 t0 = __floats2bfloat162_rn(v[j], v[j + 1]), t1 = __floats2bfloat162_rn(v[j + 2], v[j + 3]);
+      __nv_bfloat162 t2 = __floats2bfloat162_rn(v[j + 4], v[j + 5]), t3 = __floats2bfloat162_rn(v[j + 6], v[j + 7]);
+      pk.x = *reinterpret_cast<unsigned*>(&t0); pk.y = *reinterpret_cast<unsigned*>(&t1);
+      pk.z = *reinterpret_cast<unsigned*>(&t2); pk.w = *reinterpret_cast<unsigned*>(&t3);
+      *reinterpret_cast<uint4*>(o + j) = pk;
+    }
+  } else {
+    for (int j = 0; j < 32 && j < valid; ++j) o[j] = __float2bfloat16_rn(v[j]);
+  }
+}
+__device__ __forceinline__ void store_row32(float* o, const float* v, int valid) {
+  if (valid >= 32 && ((size_t)o % 16) == 0) {
+#pragma unroll
+    for (int j = 0; j < 32; j += 4) *reinterpret_cast<float4*>(o + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+  } else {
+    for (int j = 0; j < 32 && j < valid; ++j) o[j] = v[j];
+  }
+}
+
 typedef CUresult (*GgEncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                     const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
                                     CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 // cuTensorMapEncodeTiled through the runtime's driver entry point, or null.
 GgEncodeTiledFn gg_encode_tiled();
+
+// Tensor map of a row-major bf16 matrix [rows, cols] with row stride ld (elements), boxes of
+// box_rows x 64 columns, 128-byte swizzle, zero fill outside.  (gemm_tc.cu)
+int gg_make_map_2d(CUtensorMap* map, const void* ptr, int rows, int cols, long long ld, int box_rows);

@@ -73,9 +73,11 @@ def gemm_tc(args) -> None:
         out = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
         lib_out = torch.empty(M, rows, device="cuda", dtype=torch.bfloat16)
         own = _time(lambda i: ops.gemm_tc(x, ws[i % copies], out, gated=gated), args.reps)
+        two = _time(lambda i: ops.gemm_tc(x, ws[i % copies], out, gated=gated, pair=True), args.reps)
         ops.check_tc_status("cuda")
         lib = _time(lambda i: torch.mm(x, ws[i % copies].t(), out=lib_out), args.reps)
-        print(f"gemm_tc {name:13s} M={M:4d} N={N:6d} K={K:5d}: {own:7.1f} us {flops / own / 1e6:7.1f} TFLOP/s"
+        print(f"gemm_tc {name:13s} M={M:4d} N={N:6d} K={K:5d}: one CTA per tile {own:7.1f} us {flops / own / 1e6:7.1f} TFLOP/s,"
+              f" CTA pairs {two:7.1f} us {flops / two / 1e6:7.1f} TFLOP/s"
               f"   (vendor library: {lib:7.1f} us {flops / lib / 1e6:7.1f} TFLOP/s)", flush=True)
         del ws
 

@@ -47,7 +47,7 @@ class GatedMLP:
         if ops.small_m_ok(x, self.w_gate_up):
             ops.gemm_small_m(x, self.w_gate_up, a, gated=True)       # product and activation in one
         elif use_tc(x, self.w_gate_up, self.inter, True):
-            ops.gemm_tc(x, self.w_gate_up, a, gated=True)            # the same, on tcgen05
+            ops.gemm_tc(x, self.w_gate_up, a, gated=True, pair=True)  # the same, on tcgen05 (CTA pairs)
         else:
             gu = ws.get("gate_up", T, 2 * self.inter)
             linear(x, self.w_gate_up, gu)

@@ -396,37 +396,39 @@ def test_gemm_small_m_refuses_what_it_cannot_do(ops, cuda_device):
 
 
 # ---------------------------------------------------------------- products on tcgen05
+@pytest.mark.parametrize("pair", [False, True])
 @pytest.mark.parametrize("M,N,K", [(128, 256, 64), (128, 256, 256), (256, 512, 4096), (200, 300, 136),
                                    (2048, 6144, 4096), (77, 4096, 14336), (1, 256, 64)])
-def test_gemm_tc(ops, cuda_device, M, N, K):
+def test_gemm_tc(ops, cuda_device, M, N, K, pair):
     g = torch.Generator(device="cuda").manual_seed(M + N + K)
     x_wide = torch.randn(M, K + 24, device="cuda", generator=g).to(torch.bfloat16)
     x = x_wide[:, :K]
     w = (torch.randn(N, K, device="cuda", generator=g) / math.sqrt(K)).to(torch.bfloat16)
     ref = x.float() @ w.float().T
     out32 = torch.full((M, N), float("nan"), device="cuda")
-    ops.gemm_tc(x, w, out32)
+    ops.gemm_tc(x, w, out32, pair=pair)
     ops.check_tc_status("cuda")
     torch.testing.assert_close(out32, ref, rtol=2e-4, atol=2e-4)
     out16 = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
-    ops.gemm_tc(x, w, out16)
+    ops.gemm_tc(x, w, out16, pair=pair)
     ops.check_tc_status("cuda")
     assert torch.equal(out16, out32.to(torch.bfloat16))
     # one large entry in a far corner of K must reach exactly one output
     x2, w2 = x.clone(), w.clone()
     x2[M - 1, K - 5] = 64.0
     w2[N - 1, K - 5] = 8.0
-    ops.gemm_tc(x2, w2, out32)
+    ops.gemm_tc(x2, w2, out32, pair=pair)
     torch.testing.assert_close(out32, x2.float() @ w2.float().T, rtol=2e-4, atol=2e-3)
 
 
+@pytest.mark.parametrize("pair", [False, True])
 @pytest.mark.parametrize("M,I,K", [(128, 128, 64), (300, 352, 128), (2048, 14336, 4096), (65, 200, 72)])
-def test_gemm_tc_gated(ops, cuda_device, M, I, K):
+def test_gemm_tc_gated(ops, cuda_device, M, I, K, pair):
     g = torch.Generator(device="cuda").manual_seed(M + I)
     x = torch.randn(M, K, device="cuda", generator=g).to(torch.bfloat16)
     w = (torch.randn(2 * I, K, device="cuda", generator=g) * (2.0 / math.sqrt(K))).to(torch.bfloat16)
     out = torch.full((M, I), float("nan"), device="cuda", dtype=torch.bfloat16)
-    ops.gemm_tc(x, w, out, gated=True)
+    ops.gemm_tc(x, w, out, gated=True, pair=pair)
     ops.check_tc_status("cuda")
     gu = x.float() @ w.float().T
     gate, up = gu[:, :I], gu[:, I:]
