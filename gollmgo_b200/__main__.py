@@ -131,9 +131,13 @@ def _git_sha() -> str:
 def cmd_bench(argv) -> int:
     ap = argparse.ArgumentParser(prog="gollmgo_b200 bench")
     _engine_flags(ap)
-    ap.add_argument("--mode", default="offline", choices=["offline", "synthetic"],
-                    help="offline/synthetic: synthetic token prompts through the engine "
+    ap.add_argument("--mode", default="offline", choices=["offline", "synthetic", "decode", "prefill"],
+                    help="offline/synthetic: synthetic token prompts through the engine; decode: --batch "
+                         "sequences at --context tokens, --output-len single-token steps, timed on the "
+                         "device; prefill: one prompt of --prompt-len tokens in one step "
                          "(the reference's serving mode needs its HTTP server and is not built)")
+    ap.add_argument("--batch", type=int, default=8, help="sequences (decode mode)")
+    ap.add_argument("--context", type=int, default=2048, help="tokens cached per sequence (decode mode)")
     ap.add_argument("--num-prompts", type=int, default=100)
     ap.add_argument("--prompt-len", type=int, default=128)
     ap.add_argument("--output-len", type=int, default=128)
@@ -142,6 +146,8 @@ def cmd_bench(argv) -> int:
     args = ap.parse_args(argv)
     import torch
     from .sampling import SamplingParams
+    if args.mode in ("decode", "prefill"):
+        return _bench_step(args)
     eng = _make_engine(args)
     V = eng.spec.vocab_size
     params = SamplingParams(max_tokens=args.output_len, ignore_eos=True)
@@ -178,6 +184,73 @@ def cmd_bench(argv) -> int:
             "pages_high_water": eng.stats.pages_high_water,
         }
         _log(args, "info", "repetition done", rep=rep, tokens_per_second=result["tokens_per_second"])
+    print(json.dumps(result, indent=2))
+    return 0
+
+
+def _bench_step(args) -> int:
+    """Device-timed single steps through the runner (no scheduler, no sampling on the host)."""
+    import torch
+    from .csrc import ops
+    from .engine.batch import StepEntry
+    if args.mode == "decode":
+        need = args.batch * (args.context + args.output_len + 16)
+        args.max_batch_size = max(args.max_batch_size or 0, args.batch)
+        args.max_token_budget = max(args.max_token_budget or 0, args.context)
+    else:
+        need = 2 * args.prompt_len + 64
+        args.max_token_budget = max(args.max_token_budget or 0, args.prompt_len)
+    bs = args.block_size or 16
+    args.num_blocks = args.num_blocks or (-(-need // bs) + 4 * (args.batch + 1))
+    args.max_model_len = args.max_model_len or (args.context + args.output_len + args.prompt_len + 64)
+    eng = _make_engine(args)
+    runner, V = eng.runner, eng.spec.vocab_size
+    gen = torch.Generator().manual_seed(args.seed)
+    rand = lambda n: torch.randint(0, V, (n,), generator=gen).tolist()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    if args.mode == "prefill":
+        def once(i):
+            runner.step([StepEntry(f"p{i}", rand(args.prompt_len), [args.prompt_len - 1])])
+            runner.release(f"p{i}")
+        for i in range(3):
+            once(i)
+        reps = max(args.repetitions, 3)
+        torch.cuda.synchronize()
+        a.record()
+        for i in range(reps):
+            once(3 + i)
+        b.record()
+        torch.cuda.synchronize()
+        ms = a.elapsed_time(b) / reps
+        result = {"mode": "prefill", "prompt_len": args.prompt_len, "ms_per_step": round(ms, 3),
+                  "tokens_per_second": round(args.prompt_len / ms * 1e3, 1)}
+    else:
+        ids = [f"d{j}" for j in range(args.batch)]
+        for rid in ids:
+            runner.step([StepEntry(rid, rand(args.context), [])])
+        toks = rand(args.batch)
+        out = torch.empty(args.batch, dtype=torch.int32, device=runner.device)
+
+        def one():
+            logits = runner.step([StepEntry(rid, [toks[j]], [0]) for j, rid in enumerate(ids)])
+            ops.argmax(logits, out)
+        warm = max(3, args.warmup_requests)
+        steps = max(1, args.output_len - warm)
+        for _ in range(warm):
+            one()
+        torch.cuda.synchronize()
+        a.record()
+        for _ in range(steps):
+            one()
+        b.record()
+        torch.cuda.synchronize()
+        ms = a.elapsed_time(b) / steps
+        result = {"mode": "decode", "batch": args.batch, "context": args.context, "steps": steps,
+                  "ms_per_step": round(ms, 4), "tokens_per_second": round(args.batch / ms * 1e3, 1)}
+    runner.check_kernels()
+    result.update({"timestamp": datetime.datetime.now(datetime.timezone.utc).isoformat(timespec="seconds"),
+                   "git_sha": _git_sha(), "hardware": torch.cuda.get_device_name(args.device),
+                   "dtype": args.dtype, **runner.memory_report()})
     print(json.dumps(result, indent=2))
     return 0
 

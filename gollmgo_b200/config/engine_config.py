@@ -18,6 +18,9 @@ class EngineConfig:
     max_queue_depth: int = 256
     prefill_chunk_size: int = 512          # most prompt tokens of one request per step; 0 = no cut
     max_model_len: Optional[int] = None    # longest sequence; None => max_position_embeddings
+    strict_fcfs: bool = True               # the head of the queue blocks those behind it; False: a
+                                           # request that does not fit is passed over, as in the
+                                           # reference (internal/scheduler/fcfs.go:130-161)
     cuda_graphs: bool = True               # capture decode-only steps
     device: int = 0
 

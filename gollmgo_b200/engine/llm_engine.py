@@ -198,6 +198,18 @@ class Engine:
     def has_unfinished(self) -> bool:
         return self.scheduler.has_work() or self._inflight is not None
 
+    add_request = enqueue
+
+    def replay(self, lines, out_dir: str) -> int:
+        """Trace replay (engine/trace.py) on this engine's runner: ``lines`` is an iterable of
+        JSON steps; logits at the wanted places are written to ``out_dir``.  Returns the
+        number of steps.  Use it on an engine with no requests of its own in flight."""
+        from .trace import replay
+        if self.has_unfinished():
+            raise RuntimeError("replay needs an idle engine")
+        import io
+        return replay(self.runner, lines, out_dir, log=io.StringIO())
+
     # ------------------------------------------------------------------ whole requests
     def generate(self, prompts: Seq[Seq[int]], params=None, **param_options) -> List[RequestOutput]:
         """Generate for every prompt (token ids); returns outputs in the order given.

@@ -120,6 +120,7 @@ class Scheduler:
         chunk_cap = cfg.prefill_chunk_size or (1 << 30)
         free = self.cache.min_free_pages()
         planned: List[Scheduled] = []
+        planned_new: List[Sequence] = []                # admitted in this step (each takes a state slot)
 
         def fits_or_preempt(seq: Sequence, n: int) -> bool:
             """Make room for n tokens of seq by preempting later-admitted sequences
@@ -163,7 +164,9 @@ class Scheduler:
             if n > 0 and fits_or_preempt(seq, n):
                 planned.append(Scheduled(seq, n))
                 budget -= n
-        # 3. new requests, strictly in arrival order
+        # 3. new requests in arrival order; one that does not fit blocks the rest (strict_fcfs)
+        #    or is passed over
+        skipped: List[Sequence] = []
         while self.waiting and len(planned) < cfg.max_batch_size and budget > 0:
             seq = self.waiting[0]
             if any(seq is p for p in out.preempted):
@@ -171,15 +174,21 @@ class Scheduler:
             n = min(seq.remaining, chunk_cap, budget)
             need = -(-n // self.cache.page_size)
             reserve = len(self.running)                 # one more page for everyone who is running
-            if need + reserve > free or self.cache.slots.num_free == 0:
-                break
+            if need + reserve > free or self.cache.slots.num_free <= len(planned_new):
+                if cfg.strict_fcfs:
+                    break
+                skipped.append(self.waiting.popleft())
+                continue
             self.waiting.popleft()
             seq.transition(SeqState.PREFILLING)
             self.running[seq.id] = seq
             self.admit_order.append(seq.id)
+            planned_new.append(seq)
             free -= need
             planned.append(Scheduled(seq, n))
             budget -= n
+        for seq in reversed(skipped):
+            self.waiting.appendleft(seq)
         for s in planned:
             if s.seq.state is SeqState.DECODING:
                 out.decode_tokens += s.num_tokens

@@ -209,3 +209,10 @@ def test_command_line_generate_and_bench(models):
     assert p.returncode == 0, p.stderr
     res = json.loads(p.stdout)
     assert res["num_prompts"] == 6 and res["tokens_per_second"] > 0 and res["error_count"] == 0
+    for mode, extra in (("decode", ["--batch", "3", "--context", "20", "--output-len", "8"]),
+                        ("prefill", ["--prompt-len", "40"])):
+        args = [a for a in common if a not in ("--num-blocks", "32")]
+        p = subprocess.run(base + ["bench", *args, "--mode", mode, *extra], capture_output=True, text=True, cwd=root)
+        assert p.returncode == 0, p.stderr
+        res = json.loads(p.stdout)
+        assert res["mode"] == mode and res["tokens_per_second"] > 0

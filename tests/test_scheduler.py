@@ -188,3 +188,16 @@ def test_state_machine_refuses_wrong_transitions():
     s.transition(SeqState.FINISHED)
     with pytest.raises(InvalidTransition):
         s.transition(SeqState.WAITING)
+
+
+def test_without_strict_fcfs_a_request_that_does_not_fit_is_passed_over():
+    sched, cache = make(num_pages=6, page=4, prefill_chunk_size=0, strict_fcfs=False)
+    sched.add(seq(0, 12, max_tokens=3))
+    run_step(sched, cache)
+    sched.add(seq(1, 12, max_tokens=2))          # does not fit beside request 0
+    sched.add(seq(2, 2, max_tokens=2))           # fits: goes ahead of request 1
+    out = run_step(sched, cache)
+    assert [s.seq.id for s in out.scheduled] == [0, 2]
+    assert [s.id for s in sched.waiting] == [1]
+    drain(sched, cache)
+    assert cache.free_pages() == 6
