@@ -100,6 +100,9 @@ class Attention:
         kc, vc, group = cache
         qkv = ws.get("qkv", T, self.qkv_width)
         linear(x, self.w_qkv, qkv)
+        if hasattr(self.position, "apply"):
+            # a position encoding that is not a rotation table: it rewrites q and k itself
+            self.position.apply(qkv, batch, self.nh, self.nkv, self.d)
         ops.rope_kv_write(qkv, batch.positions, batch.slot_mapping[group], self.position.rope_table(),
                           kc, vc, self.nh, self.nkv, self.d, self.ctx.page_size,
                           self.position.interleaved, writes_cache)

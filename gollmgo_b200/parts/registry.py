@@ -13,7 +13,9 @@ norm            cls(spec, ctx)
 position        cls(spec, ctx)
                   .rope_table() -> float64 tensor [rot/2] or None   (fused in the cache-write kernel)
                   .interleaved: bool
-                  .apply(qkv_q, qkv_k, positions)             only if rope_table() is None and it is not "none"
+                  .apply(qkv, batch, nh, nkv, d)              optional: rewrite the q and k heads of
+                                                              qkv [T, (nh+2nkv)*d] in place (positions in
+                                                              batch.positions) before k, v go to the cache
 mixer           cls(spec, ctx)
                   .cache_need() -> PagedKVNeed | FixedStateNeed | None
                   .weights(), .load(get)
