@@ -83,6 +83,68 @@ __global__ void rope_kv_write_kernel(TA* __restrict__ qkv, const int* __restrict
   }
 }
 
+// The common case at full width: bfloat16, half-split pairs, the whole head rotated, head size a
+// multiple of 16.  One CTA per token; a thread takes eight pairs of one head with two 16-byte
+// loads (columns p..p+7 and p+d/2..p+d/2+7), or eight values of a v head, and stores in kind.
+__global__ void __launch_bounds__(256)
+rope_kv_write_vec_kernel(__nv_bfloat16* __restrict__ qkv, const int* __restrict__ positions,
+                         const int* __restrict__ slot_mapping, const double* __restrict__ inv_freq,
+                         __nv_bfloat16* __restrict__ kcache, __nv_bfloat16* __restrict__ vcache, int nh, int nkv,
+                         int d, int page_size, int write_cache) {
+  extern __shared__ float cs[];        // cos[d/2], sin[d/2]
+  pdl_trigger();
+  pdl_wait();
+  const int t = blockIdx.x;
+  const int half = d >> 1;
+  {
+    const double pos = (double)positions[t];
+    const double two_pi = 6.283185307179586476925286766559;
+    for (int p = threadIdx.x; p < half; p += blockDim.x) {
+      const double ang = pos * inv_freq[p];
+      const float r = (float)(ang - two_pi * rint(ang * (1.0 / two_pi)));
+      float s, c;
+      sincosf(r, &s, &c);
+      cs[p] = c;
+      cs[half + p] = s;
+    }
+  }
+  __syncthreads();
+  const int slot = (write_cache && slot_mapping) ? slot_mapping[t] : -1;
+  const int page = slot >= 0 ? slot / page_size : 0;
+  const int off = slot >= 0 ? slot - page * page_size : 0;
+  __nv_bfloat16* row = qkv + (size_t)t * (nh + 2 * nkv) * d;
+  const int per_head = half >> 3;                       // groups of eight pairs per head
+  const int rot_items = (nh + nkv) * per_head, v_items = nkv * (d >> 3);
+  for (int e = threadIdx.x; e < rot_items + v_items; e += blockDim.x) {
+    if (e < rot_items) {
+      const int h = e / per_head, p0 = (e - h * per_head) << 3;
+      __nv_bfloat16* x = row + (size_t)h * d;
+      uint4 lo = *reinterpret_cast<const uint4*>(x + p0), hi = *reinterpret_cast<const uint4*>(x + half + p0);
+      __nv_bfloat162* a2 = reinterpret_cast<__nv_bfloat162*>(&lo);
+      __nv_bfloat162* b2 = reinterpret_cast<__nv_bfloat162*>(&hi);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const float2 a = __bfloat1622float2(a2[i]), b = __bfloat1622float2(b2[i]);
+        const float c0 = cs[p0 + 2 * i], s0 = cs[half + p0 + 2 * i], c1 = cs[p0 + 2 * i + 1], s1 = cs[half + p0 + 2 * i + 1];
+        a2[i] = __floats2bfloat162_rn(a.x * c0 - b.x * s0, a.y * c1 - b.y * s1);
+        b2[i] = __floats2bfloat162_rn(a.x * s0 + b.x * c0, a.y * s1 + b.y * c1);
+      }
+      *reinterpret_cast<uint4*>(x + p0) = lo;
+      *reinterpret_cast<uint4*>(x + half + p0) = hi;
+      if (h >= nh && slot >= 0) {
+        __nv_bfloat16* kc = kcache + (((size_t)page * nkv + (h - nh)) * page_size + off) * d;
+        *reinterpret_cast<uint4*>(kc + p0) = lo;
+        *reinterpret_cast<uint4*>(kc + half + p0) = hi;
+      }
+    } else if (slot >= 0) {
+      const int ev = e - rot_items;
+      const int h = ev / (d >> 3), c = (ev - h * (d >> 3)) << 3;
+      *reinterpret_cast<uint4*>(vcache + (((size_t)page * nkv + h) * page_size + off) * d + c) =
+          *reinterpret_cast<const uint4*>(row + (size_t)(nh + nkv + h) * d + c);
+    }
+  }
+}
+
 extern "C" int gg_rope_kv_write(void* qkv, int act_dtype, const int* positions,
                                 const int* slot_mapping, const double* inv_freq, void* kcache,
                                 void* vcache, int T, int nh, int nkv, int d, int rot,
@@ -96,6 +158,12 @@ extern "C" int gg_rope_kv_write(void* qkv, int act_dtype, const int* positions,
   if (rot == 0) inv_freq = nullptr;
   const size_t smem = (size_t)rot * sizeof(float);
   GG_REQUIRE(smem <= 48 * 1024, "rope_kv_write: rotary width %d too large", rot);
+  if (act_dtype == GG_BF16 && inv_freq && rot == d && d % 16 == 0 && !interleaved &&
+      ((size_t)qkv % 16) == 0 && (!write_cache || (((size_t)kcache % 16) == 0 && ((size_t)vcache % 16) == 0))) {
+    gg_launch(rope_kv_write_vec_kernel, dim3(T), dim3(256), smem, stream, (__nv_bfloat16*)qkv, positions, slot_mapping,
+              inv_freq, (__nv_bfloat16*)kcache, (__nv_bfloat16*)vcache, nh, nkv, d, page_size, write_cache);
+    return gg_check_launch("rope_kv_write");
+  }
   const int threads = d >= 256 ? 128 : 64;
   const dim3 grid(T, (nh + 2 * nkv + ROPE_HEADS_PER_CTA - 1) / ROPE_HEADS_PER_CTA);
   GG_REQUIRE(grid.y <= 65535, "rope_kv_write: too many heads");

@@ -101,7 +101,8 @@ def ref_rope(x, pos, inv_freq, interleaved):
 
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("nh,nkv,d,rot,interleaved,page", [
-    (4, 2, 16, 16, False, 16), (5, 5, 48, 48, True, 8), (8, 1, 80, 32, False, 32), (3, 3, 128, 0, False, 16)])
+    (4, 2, 16, 16, False, 16), (5, 5, 48, 48, True, 8), (8, 1, 80, 32, False, 32), (3, 3, 128, 0, False, 16),
+    (32, 8, 128, 128, False, 16), (6, 2, 64, 64, False, 8), (3, 1, 48, 48, False, 16)])
 def test_rope_kv_write(ops, cuda_device, dtype, nh, nkv, d, rot, interleaved, page):
     g = torch.Generator(device="cuda").manual_seed(3)
     T, pages = 11, 9
