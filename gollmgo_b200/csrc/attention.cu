@@ -359,10 +359,18 @@ extern "C" int gg_attn_decode(const void* q, long long q_stride, const void* kca
   GG_REQUIRE(n_dec >= 0 && num_splits >= 1 && num_splits <= 65535, "attn_decode: bad n_dec %d or splits %d", n_dec, num_splits);
   GG_REQUIRE(part_o && part_ml, "attn_decode: no scratch given");
   if (n_dec == 0) return GG_OK;
+  bool merged = false;
   if (allow_mma && attn_mma_supported(dtype, d) && q_stride % 2 == 0)
-    rc = attn_decode_mma(a, n_dec, stream);
+    rc = attn_decode_mma(a, n_dec, stream, &merged);
   else
     rc = attn_decode_general(a, dtype, n_dec, stream);
-  if (rc) return rc;
+  if (rc || merged) return rc;
   return attn_merge_launch(a, dtype, n_dec, stream);
+}
+
+// Clusters of `splits` decode CTAs that the device holds at once for head size d in
+// bfloat16; 0 where gg_attn_decode would not use clusters for that count.
+extern "C" int gg_attn_decode_cluster_capacity(int dtype, int d, int splits) {
+  if (!attn_mma_supported(dtype, d)) return 0;
+  return attn_decode_cluster_capacity(d, splits);
 }

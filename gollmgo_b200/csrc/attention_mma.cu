@@ -160,12 +160,31 @@ __device__ __forceinline__ void load_q_frags(unsigned (*qf)[4], F qrow) {
 }
 
 // ---------------------------------------------------------------- decoded tokens
-template <int D, int STAGES>
+// CLUSTER: the slices of one (token, kv head) are the CTAs of a thread-block cluster
+// (1, 1, slices) and merge their results through distributed shared memory, every CTA
+// writing its share of the output; otherwise a CTA leaves its slice's result in part_o /
+// part_ml for the merge kernel.
+__device__ __forceinline__ void cluster_barrier() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ float ld_cluster_f32(unsigned local_addr, unsigned rank) {
+  float v;
+  asm volatile(
+      "{\n\t.reg .b32 ra;\n\t"
+      "mapa.shared::cluster.u32 ra, %1, %2;\n\t"
+      "ld.shared::cluster.f32 %0, [ra];\n\t}"
+      : "=f"(v) : "r"(local_addr), "r"(rank) : "memory");
+  return v;
+}
+
+template <int D, int STAGES, bool CLUSTER>
 __global__ void __launch_bounds__(MMA_THREADS, D == 128 ? 3 : 4) attn_decode_mma_kernel(AttnArgs a) {
   extern __shared__ __align__(128) unsigned char smem_raw[];
   constexpr int TILE_BYTES = MMA_BK * D * 2;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, c2 = (lane & 3) * 2;
-  pdl_wait();
+  // The lists that say what this CTA works on were copied in before the step began, and
+  // keys of earlier steps are in the cache already: only the newest key and the queries
+  // come from the kernels just before this one.
   const int ps_log2 = 31 - __clz(a.page_size);
   const int G = a.nh / a.nkv, gchunks = (G + 15) / 16;
   const int b = a.dec_seqs[blockIdx.x];
@@ -186,6 +205,10 @@ __global__ void __launch_bounds__(MMA_THREADS, D == 128 ? 3 : 4) attn_decode_mma
 #pragma unroll
   for (int nt = 0; nt < D / 8; ++nt) { o[nt][0] = o[nt][1] = o[nt][2] = o[nt][3] = 0.f; }
 
+  // the first tiles can be fetched before the kernels ahead have finished, unless they
+  // hold the key this step wrote (position ctx - 1)
+  const bool early = lo < hi && lo + (STAGES - 1) * MMA_BK <= ctx - 1;
+  if (!early) pdl_wait();
   if (lo < hi) {
     const int* bt = a.block_tables + (size_t)b * a.bt_stride;
     const unsigned base = smem_u32(smem_raw);
@@ -195,6 +218,7 @@ __global__ void __launch_bounds__(MMA_THREADS, D == 128 ? 3 : 4) attn_decode_mma
       if (s < ntiles) load_kv_tile<D>(a, bt, kvh, lo + s * MMA_BK, lo, hi, base + s * 2 * TILE_BYTES, base + s * 2 * TILE_BYTES + TILE_BYTES, ps_log2);
       cp_async_commit();
     }
+    if (early) pdl_wait();
     unsigned qf[D / 16][4];
     const __nv_bfloat16* qbase = (const __nv_bfloat16*)a.q + (size_t)t * a.q_stride + (size_t)head0 * D;
     load_q_frags<D>(qf, [&](int r) { return r < nrows ? qbase + (size_t)r * D : nullptr; });
@@ -240,6 +264,9 @@ __global__ void __launch_bounds__(MMA_THREADS, D == 128 ? 3 : 4) attn_decode_mma
   float* cm = reinterpret_cast<float*>(smem_raw);          // [4][16]
   float* cl = cm + 64;                                     // [4][16]
   float* co = cl + 64;                                     // [4][16][D]
+  float* fm = co + 4 * 16 * D;                             // the slice's result: [16] maxima,
+  float* fl = fm + 16;                                     // [16] sums,
+  float* fo = fl + 16;                                     // [16][D] weighted values
   __syncthreads();
   if ((lane & 3) == 0) {
     cm[warp * 16 + g] = m[0]; cm[warp * 16 + g + 8] = m[1];
@@ -266,13 +293,46 @@ __global__ void __launch_bounds__(MMA_THREADS, D == 128 ? 3 : 4) attn_decode_mma
         acc += f * co[((size_t)w * 16 + r) * D + col];
       }
     }
-    const size_t row = ((size_t)blockIdx.x * a.nh + head0 + r) * S + split;
-    a.part_o[row * D + col] = acc;
-    if (col == 0) {
-      // the merge kernel works with natural exponentials: hand it m in that base
-      a.part_ml[row * 2] = M == -INFINITY ? -INFINITY : M * (1.0f / LOG2E);
-      a.part_ml[row * 2 + 1] = L;
+    if (CLUSTER) {
+      fo[r * D + col] = acc;
+      if (col == 0) { fm[r] = M; fl[r] = L; }
+    } else {
+      const size_t row = ((size_t)blockIdx.x * a.nh + head0 + r) * S + split;
+      a.part_o[row * D + col] = acc;
+      if (col == 0) {
+        // the merge kernel works with natural exponentials: hand it m in that base
+        a.part_ml[row * 2] = M == -INFINITY ? -INFINITY : M * (1.0f / LOG2E);
+        a.part_ml[row * 2 + 1] = L;
+      }
     }
+  }
+  if (CLUSTER) {
+    // every CTA of the cluster merges its share of the (row, column pair)s from all slices
+    cluster_barrier();
+    if (b >= 0) {
+      const int pairs = nrows * D / 2, per = (pairs + S - 1) / S;
+      const unsigned fm_a = smem_u32(fm), fl_a = smem_u32(fl), fo_a = smem_u32(fo);
+      __nv_bfloat16* out = (__nv_bfloat16*)a.out + (size_t)t * a.nh * D + (size_t)head0 * D;
+      for (int p = split * per + threadIdx.x; p < min(pairs, (split + 1) * per); p += MMA_THREADS) {
+        const int r = (2 * p) / D, col = 2 * p - r * D;
+        float M = -INFINITY;
+        for (int s = 0; s < S; ++s) M = fmaxf(M, ld_cluster_f32(fm_a + r * 4, s));
+        float L = 0.f, o0 = 0.f, o1 = 0.f;
+        for (int s = 0; s < S; ++s) {
+          const float ms = ld_cluster_f32(fm_a + r * 4, s);
+          if (ms != -INFINITY) {
+            const float f = fast_exp2(ms - M);
+            L += f * ld_cluster_f32(fl_a + r * 4, s);
+            o0 += f * ld_cluster_f32(fo_a + (r * D + col) * 4, s);
+            o1 += f * ld_cluster_f32(fo_a + (r * D + col + 1) * 4, s);
+          }
+        }
+        const float inv = L > 0.f ? 1.f / L : 0.f;
+        *reinterpret_cast<unsigned*>(out + (size_t)r * D + col) = pack_bf16(o0 * inv, o1 * inv);
+      }
+    }
+    // nobody leaves while a neighbour may still read its shared memory
+    cluster_barrier();
   }
 }
 
@@ -384,22 +444,80 @@ template <typename K> static int opt_in_smem(K kernel, size_t bytes, const char*
   return GG_OK;
 }
 
-int attn_decode_mma(const AttnArgs& a, int n_dec, cudaStream_t stream) {
+// Launch with the slices of a (token, kv head) as one cluster, where the device can hold
+// such clusters; the PDL attribute as in gg_launch.
+template <typename K>
+static cudaError_t launch_clustered(K kernel, dim3 grid, size_t smem, int cluster_z, cudaStream_t stream,
+                                    const AttnArgs& a, int* max_clusters) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = dim3(MMA_THREADS);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[2];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 1;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = (unsigned)cluster_z;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  if (max_clusters) {
+    cfg.numAttrs = 1;
+    return cudaOccupancyMaxActiveClusters(max_clusters, kernel, &cfg);
+  }
+  cfg.numAttrs = gg_pdl_enabled() ? 2 : 1;
+  return cudaLaunchKernelEx(&cfg, kernel, a);
+}
+
+#define DECODE_STAGES 2
+static size_t decode_smem(int d) { return (size_t)DECODE_STAGES * 2 * MMA_BK * d * 2; }   // 64 KB at d = 128: 3 CTAs per SM
+
+// How many clusters of `splits` decode CTAs the device holds at once (0: such clusters
+// cannot be launched).  Asked once per head size and cluster size.
+int attn_decode_cluster_capacity(int d, int splits) {
+  static int cache[2][ATTN_MAX_CLUSTER + 1];
+  static bool known[2][ATTN_MAX_CLUSTER + 1];
+  if ((d != 64 && d != 128) || splits < 1 || splits > ATTN_MAX_CLUSTER) return 0;
+  const int di = d == 128;
+  if (!known[di][splits]) {
+    int n = 0;
+    AttnArgs a = {};
+    cudaError_t e;
+    if (d == 128) {
+      e = cudaFuncSetAttribute(attn_decode_mma_kernel<128, DECODE_STAGES, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)decode_smem(128));
+      if (e == cudaSuccess)
+        e = launch_clustered(attn_decode_mma_kernel<128, DECODE_STAGES, true>, dim3(1, 1, splits), decode_smem(128), splits, 0, a, &n);
+    } else {
+      e = launch_clustered(attn_decode_mma_kernel<64, DECODE_STAGES, true>, dim3(1, 1, splits), decode_smem(64), splits, 0, a, &n);
+    }
+    if (e != cudaSuccess) { cudaGetLastError(); n = 0; }
+    cache[di][splits] = n;
+    known[di][splits] = true;
+  }
+  return cache[di][splits];
+}
+
+// *merged is set when the kernel wrote the final output itself (no merge kernel needed).
+int attn_decode_mma(const AttnArgs& a, int n_dec, cudaStream_t stream, bool* merged) {
   GG_REQUIRE(power_of_two(a.page_size), "attn_decode: page size %d is not a power of two", a.page_size);
   const int G = a.nh / a.nkv, gchunks = (G + 15) / 16;
   GG_REQUIRE(a.nkv * gchunks <= 65535, "attn_decode: too many heads");
   dim3 grid(n_dec, a.nkv * gchunks, a.num_splits);
-  constexpr int STAGES = 2;
+  const size_t smem = decode_smem(a.d);
+  const bool cluster = merged && a.num_splits <= ATTN_MAX_CLUSTER && attn_decode_cluster_capacity(a.d, a.num_splits) > 0;
+  if (merged) *merged = cluster;
   int rc;
+  cudaError_t e;
   if (a.d == 128) {
-    const size_t smem = (size_t)STAGES * 2 * MMA_BK * 128 * 2;       // 64 KB (3 CTAs per SM); the combine needs 33 KB of it
-    if ((rc = opt_in_smem(attn_decode_mma_kernel<128, STAGES>, smem, "attn_decode"))) return rc;
-    gg_launch(attn_decode_mma_kernel<128, STAGES>, dim3(grid), dim3(MMA_THREADS), smem, stream, a);
+    if ((rc = opt_in_smem(attn_decode_mma_kernel<128, DECODE_STAGES, false>, smem, "attn_decode"))) return rc;
+    if (cluster) e = launch_clustered(attn_decode_mma_kernel<128, DECODE_STAGES, true>, grid, smem, a.num_splits, stream, a, nullptr);
+    else e = gg_launch(attn_decode_mma_kernel<128, DECODE_STAGES, false>, dim3(grid), dim3(MMA_THREADS), smem, stream, a);
   } else {
-    const size_t smem = (size_t)STAGES * 2 * MMA_BK * 64 * 2;        // 32 KB; the combine needs 17 KB
-    if ((rc = opt_in_smem(attn_decode_mma_kernel<64, STAGES>, smem, "attn_decode"))) return rc;
-    gg_launch(attn_decode_mma_kernel<64, STAGES>, dim3(grid), dim3(MMA_THREADS), smem, stream, a);
+    if (cluster) e = launch_clustered(attn_decode_mma_kernel<64, DECODE_STAGES, true>, grid, smem, a.num_splits, stream, a, nullptr);
+    else e = gg_launch(attn_decode_mma_kernel<64, DECODE_STAGES, false>, dim3(grid), dim3(MMA_THREADS), smem, stream, a);
   }
+  if (e != cudaSuccess) return gg_fail(GG_ERR_CUDA, "attn_decode_mma: launch: %s", cudaGetErrorString(e));
   return gg_check_launch("attn_decode_mma");
 }
 

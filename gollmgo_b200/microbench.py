@@ -104,7 +104,9 @@ def attn_decode(args) -> None:
     out = torch.empty(B, nh * d, device="cuda", dtype=torch.bfloat16)
     bts = [tables[i:i + B].contiguous() for i in range(0, n_seqs, B)]
     sms = torch.cuda.get_device_properties(0).multi_processor_count
-    splits = args.splits or decode_splits(B, nkv * -(-(nh // nkv) // 16), sms)
+    cap = [0] + [ops.attn_decode_cluster_capacity(torch.bfloat16, d, s) for s in range(1, ops.ATTN_MAX_CLUSTER + 1)]
+    print("clusters of s slices held at once:", cap[1:])
+    splits = args.splits or decode_splits(B, nkv * -(-(nh // nkv) // 16), sms, cap)
     po = torch.empty(B * nh * splits * d, device="cuda")
     pm = torch.empty(B * nh * splits * 2, device="cuda")
     t = _time(lambda i: ops.attn_decode(q, q.shape[1], kc, vc, bts[i % len(bts)], stride, cu, ctxs, dec, B,

@@ -27,20 +27,26 @@ ATTN_POLICY = os.environ.get("GOLLMGO_B200_ATTN", "auto")
 MAX_SPLITS = 16
 CTAS_PER_SM = 3            # decode attention CTAs resident on one SM (csrc/attention_mma.cu)
 ASSUMED_TILES = 32         # context the choice is tuned for: 32 tiles of 64 keys
-SPLIT_OVERHEAD = 4         # fixed cost of one slice (prologue, combine, merge), in tiles
+SPLIT_OVERHEAD = 4         # fixed cost of one slice (prologue, combine, merge kernel), in tiles
+CLUSTER_OVERHEAD = 3       # the same where the slices merge inside a cluster, without a merge kernel
 
 
-def decode_splits(n_dec: int, ctas_per_split: int, num_sms: int) -> int:
+def decode_splits(n_dec: int, ctas_per_split: int, num_sms: int, cluster_capacity=None) -> int:
     """Slices of the context per decoded token.  Picks the count that minimises
     waves x (tiles per slice + fixed cost per slice) for a typical context.  It depends
     only on the batch, never on the actual context lengths, so a captured step stays
-    valid as contexts grow."""
+    valid as contexts grow.  cluster_capacity[s], where given and not 0, is how many
+    clusters of s slices the device holds at once: the decode kernel merges such slices
+    itself (csrc/attention_mma.cu)."""
     slots = CTAS_PER_SM * num_sms
     ctas = max(1, n_dec * ctas_per_split)
     best, best_cost = 1, None
     for s in range(1, MAX_SPLITS + 1):
-        waves = -(-ctas * s // slots)
-        cost = waves * (ASSUMED_TILES / s + SPLIT_OVERHEAD)
+        cap = cluster_capacity[s] if cluster_capacity and s < len(cluster_capacity) else 0
+        if cap > 0:
+            cost = -(-ctas // cap) * (ASSUMED_TILES / s + CLUSTER_OVERHEAD)
+        else:
+            cost = -(-ctas * s // slots) * (ASSUMED_TILES / s + SPLIT_OVERHEAD)
         if best_cost is None or cost < best_cost - 1e-9:
             best, best_cost = s, cost
     return best
@@ -72,7 +78,11 @@ class Attention:
         ws.reserve("mixer_out", T * self.hidden, ctx.act_dtype)
         gchunks = -(-(self.nh // self.nkv) // 16)
         self._ctas_per_split = self.nkv * gchunks
-        rows = max(n * decode_splits(n, self._ctas_per_split, self.num_sms)
+        self._cluster_cap = None
+        if ctx.device.type == "cuda":
+            self._cluster_cap = [0] + [ops.attn_decode_cluster_capacity(ctx.act_dtype, self.d, s)
+                                       for s in range(1, ops.ATTN_MAX_CLUSTER + 1)]
+        rows = max(n * decode_splits(n, self._ctas_per_split, self.num_sms, self._cluster_cap)
                    for n in range(1, ctx.max_seqs + 1))
         ws.reserve("attn_part_o", rows * self.nh * self.d, torch.float32)
         ws.reserve("attn_part_ml", rows * self.nh * 2, torch.float32)
@@ -118,7 +128,7 @@ class Attention:
                              tile128_seq=batch.tile128_seq, tile128_q0=batch.tile128_q0,
                              num_tiles128=batch.num_tiles128, allow_tc=ATTN_POLICY == "auto")
         if batch.num_decode:
-            splits = decode_splits(batch.num_decode, self._ctas_per_split, self.num_sms)
+            splits = decode_splits(batch.num_decode, self._ctas_per_split, self.num_sms, self._cluster_cap)
             ops.attn_decode(qkv, self.qkv_width, kc, vc, bt, batch.bt_stride, batch.cu_q_lens,
                             batch.context_lens, batch.dec_seqs, batch.num_decode, splits,
                             ws.get("attn_part_o", 1, batch.num_decode * self.nh * splits * self.d),
