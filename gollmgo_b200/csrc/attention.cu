@@ -368,6 +368,39 @@ extern "C" int gg_attn_decode(const void* q, long long q_stride, const void* kca
   return attn_merge_launch(a, dtype, n_dec, stream);
 }
 
+// gg_attn_decode with the work of gg_rope_kv_write for the same tokens folded in: q is the raw
+// projection output [T, (nh + 2 nkv) * d] (left as it is), the kernel rotates q and k with
+// half-split pairs over the whole head and writes k and v into the cache at slot_mapping[t]
+// (write_cache = 0: rotates q only).  bfloat16, head sizes 64 and 128, at most 16 heads per
+// kv head; anything else is refused.
+extern "C" int gg_attn_decode_rope(const void* qkv, long long q_stride, void* kcache, void* vcache, int dtype,
+                                   const int* block_tables, int bt_stride, const int* cu_q_lens,
+                                   const int* context_lens, const int* dec_seqs, int n_dec, int num_splits,
+                                   float* part_o, float* part_ml, void* out, int nh, int nkv, int d,
+                                   int page_size, int window, float scale, const int* positions,
+                                   const int* slot_mapping, const double* inv_freq, int write_cache,
+                                   cudaStream_t stream) {
+  AttnArgs a = {};
+  a.q = qkv; a.q_stride = q_stride; a.kcache = kcache; a.vcache = vcache;
+  a.block_tables = block_tables; a.bt_stride = bt_stride; a.cu_q_lens = cu_q_lens;
+  a.context_lens = context_lens; a.out = out; a.nh = nh; a.nkv = nkv; a.d = d;
+  a.page_size = page_size; a.window = window; a.scale = scale;
+  a.dec_seqs = dec_seqs; a.num_splits = num_splits; a.part_o = part_o; a.part_ml = part_ml;
+  a.rope_inv_freq = inv_freq; a.rope_positions = positions; a.slot_mapping = slot_mapping;
+  a.rope_write_cache = write_cache;
+  int rc = check_common(a, "attn_decode_rope");
+  if (rc) return rc;
+  GG_REQUIRE(n_dec >= 0 && num_splits >= 1 && num_splits <= 65535, "attn_decode_rope: bad n_dec %d or splits %d", n_dec, num_splits);
+  GG_REQUIRE(part_o && part_ml, "attn_decode_rope: no scratch given");
+  GG_REQUIRE(inv_freq != nullptr, "attn_decode_rope: no inverse frequencies given");
+  GG_REQUIRE(attn_mma_supported(dtype, d), "attn_decode_rope: only bfloat16 with head size 64 or 128 (got dtype %d, head size %d)", dtype, d);
+  if (n_dec == 0) return GG_OK;
+  bool merged = false;
+  rc = attn_decode_mma(a, n_dec, stream, &merged);
+  if (rc || merged) return rc;
+  return attn_merge_launch(a, dtype, n_dec, stream);
+}
+
 // Clusters of `splits` decode CTAs that the device holds at once for head size d in
 // bfloat16; 0 where gg_attn_decode would not use clusters for that count.
 extern "C" int gg_attn_decode_cluster_capacity(int dtype, int d, int splits) {

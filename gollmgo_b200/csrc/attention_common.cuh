@@ -23,6 +23,12 @@ struct AttnArgs {
   int num_splits;
   float* part_o;            // [n_dec, nh, num_splits, d]
   float* part_ml;           // [n_dec, nh, num_splits, 2]
+  // decode with the rotation fused in (attention_mma.cu): q is then the raw [T, (nh+2nkv)*d]
+  // projection output, and the kernel rotates q and k itself and writes k and v to the cache
+  const double* rope_inv_freq;   // d/2 inverse frequencies, or null: q and the cache are ready
+  const int* rope_positions;     // [T]
+  const int* slot_mapping;       // [T] page * page_size + offset, < 0: no write
+  int rope_write_cache;
 };
 
 // General kernels (attention.cu)

@@ -21,6 +21,7 @@
 
 #define MMA_THREADS 128
 #define MMA_BK 64
+#define DEC_BT_CACHE 512          // block-table entries a decode CTA keeps in shared memory
 #define LOG2E 1.4426950408889634f
 
 bool attn_mma_supported(int dtype, int d) { return dtype == GG_BF16 && (d == 64 || d == 128); }
@@ -34,7 +35,8 @@ template <int D> __device__ __forceinline__ unsigned tile_off(int row, int chunk
 // Bring keys and values of tokens [k0, k0+64) of one sequence and kv head to a stage.
 // Tokens outside [lo, hi) and pages that were given back are zero-filled.  The page size
 // is a power of two (ps_log2), so the page of a token is a shift away.
-template <int D>
+// bt_local: bt points to a copy of the block table in shared memory (plain loads).
+template <int D, bool BT_LOCAL = false>
 __device__ __forceinline__ void load_kv_tile(const AttnArgs& a, const int* bt, int kvh, int k0, int lo,
                                              int hi, unsigned ks, unsigned vs, int ps_log2) {
   constexpr int CPR = D / 8;                       // 16-byte chunks per row
@@ -50,7 +52,7 @@ __device__ __forceinline__ void load_kv_tile(const AttnArgs& a, const int* bt, i
     const int row = r0 + i * ROWS_PER_PASS;
     const int tok = k0 + row;
     int page = -1;
-    if (tok >= lo && tok < hi) page = __ldg(bt + (tok >> ps_log2));
+    if (tok >= lo && tok < hi) page = BT_LOCAL ? bt[tok >> ps_log2] : __ldg(bt + (tok >> ps_log2));
     const size_t src = page >= 0 ? ((size_t)page * page_elems + in_head + (unsigned)(tok & ps_mask)) * D + ch * 8 : 0;
     const int bytes = page >= 0 ? 16 : 0;
     const unsigned off = tile_off<D>(row, ch);
@@ -177,7 +179,65 @@ __device__ __forceinline__ float ld_cluster_f32(unsigned local_addr, unsigned ra
   return v;
 }
 
-template <int D, int STAGES, bool CLUSTER>
+// ROPE: what rope_kv_write does for a decoded token (rope_cache.cu, the same arithmetic),
+// inside this kernel: cosines and sines of the token's position into `scratch`, the CTA's
+// query heads rotated into scratch (bfloat16, [16][D]), and, in the one CTA whose slice holds
+// the token's own position, k rotated and v copied into their place in the cache.  Half-split
+// pairs over the whole head.  Ends with a barrier: the CTA then sees q and the new k and v.
+template <int D>
+__device__ __forceinline__ void decode_rope(const AttnArgs& a, int t, int kvh, int head0, int nrows, bool owner,
+                                            unsigned char* scratch) {
+  float* cs = reinterpret_cast<float*>(scratch);
+  __nv_bfloat16* qs = reinterpret_cast<__nv_bfloat16*>(scratch + D * sizeof(float));
+  constexpr int half = D / 2, per_head = half / 8;
+  {
+    const double pos = (double)a.rope_positions[t];
+    const double two_pi = 6.283185307179586476925286766559;
+    for (int p = threadIdx.x; p < half; p += MMA_THREADS) {
+      const double ang = pos * a.rope_inv_freq[p];
+      const float r = (float)(ang - two_pi * rint(ang * (1.0 / two_pi)));
+      float sn, c;
+      sincosf(r, &sn, &c);
+      cs[p] = c;
+      cs[half + p] = sn;
+    }
+  }
+  __syncthreads();
+  const int slot = (owner && a.rope_write_cache && a.slot_mapping) ? a.slot_mapping[t] : -1;
+  const int page = slot >= 0 ? slot / a.page_size : 0;
+  const int off = slot >= 0 ? slot - page * a.page_size : 0;
+  const __nv_bfloat16* row = (const __nv_bfloat16*)a.q + (size_t)t * a.q_stride;
+  const size_t cache_row = (((size_t)page * a.nkv + kvh) * a.page_size + off) * D;
+  const int q_items = nrows * per_head, k_items = slot >= 0 ? per_head : 0, v_items = slot >= 0 ? D / 8 : 0;
+  for (int e = threadIdx.x; e < q_items + k_items + v_items; e += MMA_THREADS) {
+    if (e < q_items + k_items) {
+      const bool is_k = e >= q_items;
+      const int hh = is_k ? 0 : e / per_head;
+      const int p0 = (is_k ? e - q_items : e - hh * per_head) << 3;
+      const __nv_bfloat16* x = row + (size_t)(is_k ? a.nh + kvh : head0 + hh) * D;
+      uint4 lo = *reinterpret_cast<const uint4*>(x + p0), hi = *reinterpret_cast<const uint4*>(x + half + p0);
+      __nv_bfloat162* a2 = reinterpret_cast<__nv_bfloat162*>(&lo);
+      __nv_bfloat162* b2 = reinterpret_cast<__nv_bfloat162*>(&hi);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const float2 av = __bfloat1622float2(a2[i]), bv = __bfloat1622float2(b2[i]);
+        const float c0 = cs[p0 + 2 * i], s0 = cs[half + p0 + 2 * i], c1 = cs[p0 + 2 * i + 1], s1 = cs[half + p0 + 2 * i + 1];
+        a2[i] = __floats2bfloat162_rn(av.x * c0 - bv.x * s0, av.y * c1 - bv.y * s1);
+        b2[i] = __floats2bfloat162_rn(av.x * s0 + bv.x * c0, av.y * s1 + bv.y * c1);
+      }
+      __nv_bfloat16* dst = is_k ? (__nv_bfloat16*)a.kcache + cache_row : qs + hh * D;
+      *reinterpret_cast<uint4*>(dst + p0) = lo;
+      *reinterpret_cast<uint4*>(dst + half + p0) = hi;
+    } else {
+      const int c = (e - q_items - k_items) << 3;
+      *reinterpret_cast<uint4*>((__nv_bfloat16*)a.vcache + cache_row + c) =
+          *reinterpret_cast<const uint4*>(row + (size_t)(a.nh + a.nkv + kvh) * D + c);
+    }
+  }
+  __syncthreads();
+}
+
+template <int D, int STAGES, bool CLUSTER, bool ROPE>
 __global__ void __launch_bounds__(MMA_THREADS, D == 128 ? 3 : 4) attn_decode_mma_kernel(AttnArgs a) {
   extern __shared__ __align__(128) unsigned char smem_raw[];
   constexpr int TILE_BYTES = MMA_BK * D * 2;
@@ -207,28 +267,50 @@ __global__ void __launch_bounds__(MMA_THREADS, D == 128 ? 3 : 4) attn_decode_mma
 
   // the first tiles can be fetched before the kernels ahead have finished, unless they
   // hold the key this step wrote (position ctx - 1)
+  // the slice's part of the block table, once, into shared memory: a tile's copies then start
+  // without a look-up in global memory first
+  __shared__ int bt_s[DEC_BT_CACHE];
+  const int pg_first = lo >> ps_log2, n_pg = lo < hi ? ((hi - 1) >> ps_log2) - pg_first + 1 : 0;
+  const bool bt_local = n_pg > 0 && n_pg <= DEC_BT_CACHE;
+  if (bt_local) {
+    const int* btg = a.block_tables + (size_t)b * a.bt_stride + pg_first;
+    for (int i = threadIdx.x; i < n_pg; i += MMA_THREADS) bt_s[i] = __ldg(btg + i);
+    __syncthreads();
+  }
   const bool early = lo < hi && lo + (STAGES - 1) * MMA_BK <= ctx - 1;
-  if (!early) pdl_wait();
+  // ROPE: the last stage is free until the main loop starts filling it
+  unsigned char* scratch = smem_raw + (STAGES - 1) * 2 * TILE_BYTES;
+  const bool owner = lo <= ctx - 1 && ctx - 1 < hi;
+  if (!early) {
+    pdl_wait();
+    if (ROPE && lo < hi) decode_rope<D>(a, t, kvh, head0, nrows, owner, scratch);
+  }
   if (lo < hi) {
-    const int* bt = a.block_tables + (size_t)b * a.bt_stride;
+    const int* bt = bt_local ? bt_s - pg_first : a.block_tables + (size_t)b * a.bt_stride;
     const unsigned base = smem_u32(smem_raw);
     const int ntiles = (hi - lo + MMA_BK - 1) / MMA_BK;
+    auto load_tile = [&](int i, int st) {
+      if (bt_local) load_kv_tile<D, true>(a, bt, kvh, lo + i * MMA_BK, lo, hi, base + st * 2 * TILE_BYTES, base + st * 2 * TILE_BYTES + TILE_BYTES, ps_log2);
+      else load_kv_tile<D, false>(a, bt, kvh, lo + i * MMA_BK, lo, hi, base + st * 2 * TILE_BYTES, base + st * 2 * TILE_BYTES + TILE_BYTES, ps_log2);
+    };
 #pragma unroll
     for (int s = 0; s < STAGES - 1; ++s) {
-      if (s < ntiles) load_kv_tile<D>(a, bt, kvh, lo + s * MMA_BK, lo, hi, base + s * 2 * TILE_BYTES, base + s * 2 * TILE_BYTES + TILE_BYTES, ps_log2);
+      if (s < ntiles) load_tile(s, s);
       cp_async_commit();
     }
-    if (early) pdl_wait();
+    if (early) {
+      pdl_wait();
+      if (ROPE) decode_rope<D>(a, t, kvh, head0, nrows, owner, scratch);
+    }
     unsigned qf[D / 16][4];
-    const __nv_bfloat16* qbase = (const __nv_bfloat16*)a.q + (size_t)t * a.q_stride + (size_t)head0 * D;
+    const __nv_bfloat16* qbase = ROPE ? reinterpret_cast<const __nv_bfloat16*>(scratch + D * sizeof(float))
+                                      : (const __nv_bfloat16*)a.q + (size_t)t * a.q_stride + (size_t)head0 * D;
     load_q_frags<D>(qf, [&](int r) { return r < nrows ? qbase + (size_t)r * D : nullptr; });
+    if (ROPE) __syncthreads();           // the loop's first copy lands where q was
     const float sc = a.scale * LOG2E;
     for (int it = 0; it < ntiles; ++it) {
       const int nx = it + STAGES - 1;
-      if (nx < ntiles) {
-        const int st = nx % STAGES;
-        load_kv_tile<D>(a, bt, kvh, lo + nx * MMA_BK, lo, hi, base + st * 2 * TILE_BYTES, base + st * 2 * TILE_BYTES + TILE_BYTES, ps_log2);
-      }
+      if (nx < ntiles) load_tile(nx, nx % STAGES);
       cp_async_commit();
       cp_async_wait<STAGES - 1>();
       __syncthreads();
@@ -485,11 +567,11 @@ int attn_decode_cluster_capacity(int d, int splits) {
     AttnArgs a = {};
     cudaError_t e;
     if (d == 128) {
-      e = cudaFuncSetAttribute(attn_decode_mma_kernel<128, DECODE_STAGES, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)decode_smem(128));
+      e = cudaFuncSetAttribute(attn_decode_mma_kernel<128, DECODE_STAGES, true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)decode_smem(128));
       if (e == cudaSuccess)
-        e = launch_clustered(attn_decode_mma_kernel<128, DECODE_STAGES, true>, dim3(1, 1, splits), decode_smem(128), splits, 0, a, &n);
+        e = launch_clustered(attn_decode_mma_kernel<128, DECODE_STAGES, true, false>, dim3(1, 1, splits), decode_smem(128), splits, 0, a, &n);
     } else {
-      e = launch_clustered(attn_decode_mma_kernel<64, DECODE_STAGES, true>, dim3(1, 1, splits), decode_smem(64), splits, 0, a, &n);
+      e = launch_clustered(attn_decode_mma_kernel<64, DECODE_STAGES, true, false>, dim3(1, 1, splits), decode_smem(64), splits, 0, a, &n);
     }
     if (e != cudaSuccess) { cudaGetLastError(); n = 0; }
     cache[di][splits] = n;
@@ -507,16 +589,29 @@ int attn_decode_mma(const AttnArgs& a, int n_dec, cudaStream_t stream, bool* mer
   const size_t smem = decode_smem(a.d);
   const bool cluster = merged && a.num_splits <= ATTN_MAX_CLUSTER && attn_decode_cluster_capacity(a.d, a.num_splits) > 0;
   if (merged) *merged = cluster;
+  const bool rope = a.rope_inv_freq != nullptr;
+  if (rope) {
+    GG_REQUIRE(gchunks == 1, "attn_decode: the fused rotation takes at most 16 heads per kv head, not %d", G);
+    GG_REQUIRE(a.rope_positions && (!a.rope_write_cache || a.slot_mapping), "attn_decode: fused rotation without positions or slots");
+    GG_REQUIRE(a.q_stride % 8 == 0 && ((size_t)a.q % 16) == 0 && ((size_t)a.kcache % 16) == 0 && ((size_t)a.vcache % 16) == 0,
+               "attn_decode: the fused rotation needs 16-byte aligned rows");
+  }
   int rc;
   cudaError_t e;
+#define DECODE_LAUNCH(D_, CL_, RP_)                                                                          \
+  do {                                                                                                       \
+    if ((rc = opt_in_smem(attn_decode_mma_kernel<D_, DECODE_STAGES, CL_, RP_>, smem, "attn_decode"))) return rc; \
+    if (CL_) e = launch_clustered(attn_decode_mma_kernel<D_, DECODE_STAGES, CL_, RP_>, grid, smem, a.num_splits, stream, a, nullptr); \
+    else e = gg_launch(attn_decode_mma_kernel<D_, DECODE_STAGES, CL_, RP_>, dim3(grid), dim3(MMA_THREADS), smem, stream, a); \
+  } while (0)
   if (a.d == 128) {
-    if ((rc = opt_in_smem(attn_decode_mma_kernel<128, DECODE_STAGES, false>, smem, "attn_decode"))) return rc;
-    if (cluster) e = launch_clustered(attn_decode_mma_kernel<128, DECODE_STAGES, true>, grid, smem, a.num_splits, stream, a, nullptr);
-    else e = gg_launch(attn_decode_mma_kernel<128, DECODE_STAGES, false>, dim3(grid), dim3(MMA_THREADS), smem, stream, a);
+    if (cluster) { if (rope) DECODE_LAUNCH(128, true, true); else DECODE_LAUNCH(128, true, false); }
+    else { if (rope) DECODE_LAUNCH(128, false, true); else DECODE_LAUNCH(128, false, false); }
   } else {
-    if (cluster) e = launch_clustered(attn_decode_mma_kernel<64, DECODE_STAGES, true>, grid, smem, a.num_splits, stream, a, nullptr);
-    else e = gg_launch(attn_decode_mma_kernel<64, DECODE_STAGES, false>, dim3(grid), dim3(MMA_THREADS), smem, stream, a);
+    if (cluster) { if (rope) DECODE_LAUNCH(64, true, true); else DECODE_LAUNCH(64, true, false); }
+    else { if (rope) DECODE_LAUNCH(64, false, true); else DECODE_LAUNCH(64, false, false); }
   }
+#undef DECODE_LAUNCH
   if (e != cudaSuccess) return gg_fail(GG_ERR_CUDA, "attn_decode_mma: launch: %s", cudaGetErrorString(e));
   return gg_check_launch("attn_decode_mma");
 }

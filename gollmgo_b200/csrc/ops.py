@@ -177,6 +177,40 @@ def attn_decode(q: torch.Tensor, q_stride: int, kcache: torch.Tensor, vcache: to
                                 ctypes.c_float(scale), int(allow_mma), _stream()), 2)
 
 
+def attn_decode_rope_ok(dtype: torch.dtype, nh: int, nkv: int, d: int, inv_freq: Optional[torch.Tensor],
+                        interleaved: bool) -> bool:
+    """Whether attn_decode_rope takes this shape: bfloat16, head size 64 or 128, at most 16
+    heads per kv head, half-split rotation over the whole head."""
+    return (dtype == torch.bfloat16 and d in (64, 128) and nh // nkv <= 16 and inv_freq is not None
+            and inv_freq.dtype == torch.float64 and 2 * inv_freq.numel() == d and not interleaved)
+
+
+def attn_decode_rope(qkv: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor,
+                     block_tables: torch.Tensor, bt_stride: int, cu_q_lens: torch.Tensor,
+                     context_lens: torch.Tensor, dec_seqs: torch.Tensor, n_dec: int, num_splits: int,
+                     part_o: torch.Tensor, part_ml: torch.Tensor, out: torch.Tensor, nh: int, nkv: int,
+                     d: int, page_size: int, window: int, scale: float, positions: torch.Tensor,
+                     slot_mapping: Optional[torch.Tensor], inv_freq: torch.Tensor,
+                     write_cache: bool = True) -> None:
+    """rope_kv_write and attn_decode of single decoded tokens in one kernel: qkv is the raw
+    projection output and stays as it is; k (rotated) and v land in the cache."""
+    _cuda(qkv, positions, slot_mapping, inv_freq, kcache, vcache)
+    if not attn_decode_rope_ok(qkv.dtype, nh, nkv, d, inv_freq, False) or kcache.dtype != qkv.dtype:
+        raise KernelError("attn_decode_rope: shape or dtype not taken (see attn_decode_rope_ok)")
+    if qkv.shape[1] != (nh + 2 * nkv) * d or qkv.stride(0) != qkv.shape[1]:
+        raise KernelError("attn_decode_rope: qkv must be contiguous [T, (nh + 2 nkv) * d]")
+    if part_o.numel() < n_dec * nh * num_splits * d or part_ml.numel() < n_dec * nh * num_splits * 2:
+        raise KernelError("attn_decode_rope: scratch too small")
+    if write_cache and slot_mapping is None:
+        raise KernelError("attn_decode_rope: cache write without slots")
+    _check(lib().gg_attn_decode_rope(_p(qkv), ctypes.c_longlong(qkv.shape[1]), _p(kcache), _p(vcache),
+                                     dtype_code(kcache.dtype), _p(block_tables), bt_stride,
+                                     _p(cu_q_lens), _p(context_lens), _p(dec_seqs), n_dec, num_splits,
+                                     _p(part_o), _p(part_ml), _p(out), nh, nkv, d, page_size, window,
+                                     ctypes.c_float(scale), _p(positions), _p(slot_mapping), _p(inv_freq),
+                                     int(write_cache), _stream()), 2)
+
+
 ATTN_MAX_CLUSTER = 8  # largest count of slices that the decode kernel merges inside a cluster
 
 

@@ -24,11 +24,13 @@ from .registry import build_position, register_mixer
 # takes the sizes (tcgen05 for head sizes 64 and 128 in prompt portions, mma.sync for decode), "mma" = no tcgen05 kernel,
 # "general" = only the general kernel.
 ATTN_POLICY = os.environ.get("GOLLMGO_B200_ATTN", "auto")
+# Steps of decoded tokens only: rotation and cache write inside the decode attention kernel.
+FUSE_DECODE_ROPE = os.environ.get("GOLLMGO_B200_FUSE_ROPE", "1") != "0"
 MAX_SPLITS = 16
 CTAS_PER_SM = 3            # decode attention CTAs resident on one SM (csrc/attention_mma.cu)
 ASSUMED_TILES = 32         # context the choice is tuned for: 32 tiles of 64 keys
 SPLIT_OVERHEAD = 4         # fixed cost of one slice (prologue, combine, merge kernel), in tiles
-CLUSTER_OVERHEAD = 3       # the same where the slices merge inside a cluster, without a merge kernel
+CLUSTER_OVERHEAD = 2       # the same where the slices merge inside a cluster, without a merge kernel
 
 
 def decode_splits(n_dec: int, ctas_per_split: int, num_sms: int, cluster_capacity=None) -> int:
@@ -113,9 +115,15 @@ class Attention:
         if hasattr(self.position, "apply"):
             # a position encoding that is not a rotation table: it rewrites q and k itself
             self.position.apply(qkv, batch, self.nh, self.nkv, self.d)
-        ops.rope_kv_write(qkv, batch.positions, batch.slot_mapping[group], self.position.rope_table(),
-                          kc, vc, self.nh, self.nkv, self.d, self.ctx.page_size,
-                          self.position.interleaved, writes_cache)
+        # a step of decoded tokens only: the decode kernel rotates and writes the cache itself
+        table = self.position.rope_table()
+        fused = (FUSE_DECODE_ROPE and batch.num_decode > 0 and not batch.num_tiles and ATTN_POLICY != "general"
+                 and not hasattr(self.position, "apply")
+                 and ops.attn_decode_rope_ok(qkv.dtype, self.nh, self.nkv, self.d, table, self.position.interleaved))
+        if not fused:
+            ops.rope_kv_write(qkv, batch.positions, batch.slot_mapping[group], table,
+                              kc, vc, self.nh, self.nkv, self.d, self.ctx.page_size,
+                              self.position.interleaved, writes_cache)
         out = ws.get("attn_out", T, self.nh * self.d)
         window = int(self.window or 0)
         bt = batch.block_tables[group]
@@ -129,11 +137,17 @@ class Attention:
                              num_tiles128=batch.num_tiles128, allow_tc=ATTN_POLICY == "auto")
         if batch.num_decode:
             splits = decode_splits(batch.num_decode, self._ctas_per_split, self.num_sms, self._cluster_cap)
+            part_o = ws.get("attn_part_o", 1, batch.num_decode * self.nh * splits * self.d)
+            part_ml = ws.get("attn_part_ml", 1, batch.num_decode * self.nh * splits * 2)
+        if batch.num_decode and fused:
+            ops.attn_decode_rope(qkv, kc, vc, bt, batch.bt_stride, batch.cu_q_lens, batch.context_lens,
+                                 batch.dec_seqs, batch.num_decode, splits, part_o, part_ml, out, self.nh,
+                                 self.nkv, self.d, self.ctx.page_size, window, self.scale, batch.positions,
+                                 batch.slot_mapping[group], table, writes_cache)
+        elif batch.num_decode:
             ops.attn_decode(qkv, self.qkv_width, kc, vc, bt, batch.bt_stride, batch.cu_q_lens,
                             batch.context_lens, batch.dec_seqs, batch.num_decode, splits,
-                            ws.get("attn_part_o", 1, batch.num_decode * self.nh * splits * self.d),
-                            ws.get("attn_part_ml", 1, batch.num_decode * self.nh * splits * 2),
-                            out, self.nh, self.nkv, self.d, self.ctx.page_size, window, self.scale)
+                            part_o, part_ml, out, self.nh, self.nkv, self.d, self.ctx.page_size, window, self.scale)
         y = ws.get("mixer_out", T, self.hidden)
         linear(out, self.w_o, y)
         return y

@@ -212,7 +212,7 @@ def test_attn_decode(ops, cuda_device, dtype, nh, nkv, d, page, window, allow_mm
     order = list(range(B))
     random.Random(2).shuffle(order)
     dec = torch.tensor(order + [-1, -1], dtype=torch.int32, device="cuda")       # two padded entries
-    for splits in (1, 3, 8):
+    for splits in (1, 3, 8, 11):                                       # up to 8 merge inside a cluster
         n_dec = B + 2
         part_o = torch.full((n_dec * nh * splits * d,), float("nan"), device="cuda")
         part_ml = torch.full((n_dec * nh * splits * 2,), float("nan"), device="cuda")
@@ -221,6 +221,75 @@ def test_attn_decode(ops, cuda_device, dtype, nh, nkv, d, page, window, allow_mm
                         out, nh, nkv, d, page, window, 1 / math.sqrt(d), allow_mma=allow_mma)
         ref = torch.cat(refs).reshape(B, nh * d)
         torch.testing.assert_close(out.double(), ref, **tol(dtype))
+
+
+@pytest.mark.parametrize("nh,nkv,d,page,window", [
+    (32, 8, 128, 16, 0), (24, 2, 64, 16, 0), (6, 2, 64, 8, 70), (16, 1, 128, 32, 0), (3, 3, 128, 16, 33)])
+def test_attn_decode_with_rotation_inside(ops, cuda_device, nh, nkv, d, page, window):
+    """The decode kernel that rotates q and k and writes the cache itself gives, bit for bit,
+    what rope_kv_write followed by attn_decode gives: outputs and cache."""
+    dtype = torch.bfloat16
+    torch.manual_seed(5)
+    ctxs = [1, 2, page, page + 1, 64, 65, 128, 129, 300, 777, 3000]
+    B = len(ctxs)
+    seqs = [(torch.randn(c, nkv, d, device="cuda").to(dtype), torch.randn(c, nkv, d, device="cuda").to(dtype))
+            for c in ctxs]
+    kc, vc, bt, stride = paged(seqs, page, sum(-(-c // page) for c in ctxs) + 5, nkv, d, dtype, 7)
+    W = (nh + 2 * nkv) * d
+    qkv = torch.randn(B + 2, W, device="cuda").to(dtype)                  # two rows of padding at the end
+    order = list(range(B))
+    random.Random(3).shuffle(order)                                       # token t belongs to sequence order[t]
+    cu = torch.zeros(B + 1, dtype=torch.int32)
+    pos = torch.zeros(B + 2, dtype=torch.int32)
+    slots = torch.full((B + 2,), -1, dtype=torch.int32)
+    # sequence b has its one token in row t where order[t] == b; cu_q_lens is by sequence, so rows follow it
+    rows = torch.empty(B + 2, W, device="cuda", dtype=dtype)
+    for b in range(B):
+        cu[b + 1] = b + 1
+        pos[b] = ctxs[b] - 1
+        slots[b] = int(bt[b, (ctxs[b] - 1) // page]) * page + (ctxs[b] - 1) % page
+        rows[b] = qkv[b]
+    rows[B:] = qkv[B:]
+    cu, pos, slots = cu.cuda(), pos.cuda(), slots.cuda()
+    ctx_t = torch.tensor(ctxs, dtype=torch.int32, device="cuda")
+    dec = torch.tensor(order + [-1, -1], dtype=torch.int32, device="cuda")
+    inv = (1.0 / (500000.0 ** (torch.arange(0, d, 2, dtype=torch.float64) / d))).cuda()
+    for splits in (1, 4, 8, 11):
+        n_dec = B + 2
+        part_o = torch.empty(n_dec * nh * splits * d, device="cuda")
+        part_ml = torch.empty(n_dec * nh * splits * 2, device="cuda")
+        for write in (True, False):
+            x1, k1, v1 = rows.clone(), kc.clone(), vc.clone()
+            out1 = torch.zeros(B + 2, nh * d, device="cuda", dtype=dtype)
+            ops.rope_kv_write(x1, pos, slots, inv, k1, v1, nh, nkv, d, page, False, write)
+            ops.attn_decode(x1, W, k1, v1, bt, stride, cu, ctx_t, dec, n_dec, splits, part_o, part_ml, out1,
+                            nh, nkv, d, page, window, 1 / math.sqrt(d))
+            x2, k2, v2 = rows.clone(), kc.clone(), vc.clone()
+            out2 = torch.zeros(B + 2, nh * d, device="cuda", dtype=dtype)
+            ops.attn_decode_rope(x2, k2, v2, bt, stride, cu, ctx_t, dec, n_dec, splits, part_o, part_ml, out2,
+                                 nh, nkv, d, page, window, 1 / math.sqrt(d), pos, slots, inv, write)
+            assert torch.equal(out1, out2), (splits, write)
+            assert torch.equal(k1, k2) and torch.equal(v1, v2), (splits, write)
+            assert torch.equal(x2, rows)                                  # the projection output is left alone
+            if write:
+                assert not torch.equal(k1, kc)
+
+
+def test_attn_decode_rope_refuses_what_it_cannot_do(ops, cuda_device):
+    from gollmgo_b200.csrc.ops import KernelError
+    assert not ops.attn_decode_rope_ok(torch.float32, 8, 2, 128, torch.ones(64, dtype=torch.float64), False)
+    assert not ops.attn_decode_rope_ok(torch.bfloat16, 8, 2, 80, torch.ones(40, dtype=torch.float64), False)
+    assert not ops.attn_decode_rope_ok(torch.bfloat16, 34, 2, 128, torch.ones(64, dtype=torch.float64), False)
+    assert not ops.attn_decode_rope_ok(torch.bfloat16, 8, 2, 128, torch.ones(32, dtype=torch.float64), False)
+    assert not ops.attn_decode_rope_ok(torch.bfloat16, 8, 2, 128, torch.ones(64, dtype=torch.float64), True)
+    assert ops.attn_decode_rope_ok(torch.bfloat16, 8, 2, 128, torch.ones(64, dtype=torch.float64), False)
+    x = torch.zeros(1, 12 * 80, device="cuda", dtype=torch.bfloat16)
+    c = torch.zeros(2, 2, 16, 80, device="cuda", dtype=torch.bfloat16)
+    i = torch.zeros(4, dtype=torch.int32, device="cuda")
+    with pytest.raises(KernelError):
+        ops.attn_decode_rope(x, c, c, i, 1, i, i, i, 1, 1, torch.empty(4000, device="cuda"),
+                             torch.empty(100, device="cuda"), torch.empty(1, 8 * 80, device="cuda", dtype=torch.bfloat16),
+                             8, 2, 80, 16, 0, 0.1, i, i, torch.ones(40, dtype=torch.float64, device="cuda"))
 
 
 @pytest.mark.parametrize("allow_mma", [False, True, "tc"])
