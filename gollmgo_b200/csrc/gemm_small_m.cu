@@ -66,13 +66,17 @@ gemm_small_m_kernel(const __nv_bfloat16* __restrict__ x, long long ldx,
   const int my_tiles = blockIdx.x < num_tiles ? (num_tiles - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
   const unsigned ring_base = smem_u32(ring) + (unsigned)((warp * GSM_STAGES * 4 * 32 + lane) * 16);
 
+  // CTAs start at different places of K and wrap around, so that at any moment they ask L2
+  // for different lines of x (every CTA reads all of x; in step they would all hit one line)
+  const int rot = iters > 0 ? (int)(blockIdx.x % (unsigned)iters) : 0;
   // producer position: tile index within my tiles (group start + offset), k step, ring stage
   int p_g0 = 0, p_ki = 0, p_tj = 0, p_stage = 0;
   auto issue = [&]() {
     if (iters > 0 && p_g0 < my_tiles) {
       int n_a, n_b;
       tile_rows<MODE>(blockIdx.x + (p_g0 + p_tj) * gridDim.x, g, N, n_a, n_b);
-      const int k0 = (p_ki * GSM_WARPS + warp) * GSM_SPAN + c * 8, k1 = k0 + 32;
+      const int kk = p_ki + rot < iters ? p_ki + rot : p_ki + rot - iters;
+      const int k0 = (kk * GSM_WARPS + warp) * GSM_SPAN + c * 8, k1 = k0 + 32;
       const unsigned dst = ring_base + (unsigned)(p_stage * 4 * 32 * 16);
       const __nv_bfloat16* wa = W + (size_t)max(n_a, 0) * K;
       const __nv_bfloat16* wb = W + (size_t)max(n_b, 0) * K;
@@ -110,7 +114,8 @@ gemm_small_m_kernel(const __nv_bfloat16* __restrict__ x, long long ldx,
 #pragma unroll
       for (int j = 0; j < NT; ++j) { acc[t][j][0] = acc[t][j][1] = acc[t][j][2] = acc[t][j][3] = 0.f; }
     for (int ki = 0; ki < iters; ++ki) {
-      const int k0 = (ki * GSM_WARPS + warp) * GSM_SPAN + c * 8, k1 = k0 + 32;
+      const int kk = ki + rot < iters ? ki + rot : ki + rot - iters;
+      const int k0 = (kk * GSM_WARPS + warp) * GSM_SPAN + c * 8, k1 = k0 + 32;
       uint4 x0[NT], x1[NT];
 #pragma unroll
       for (int j = 0; j < NT; ++j) {
