@@ -29,26 +29,37 @@ FUSE_DECODE_ROPE = os.environ.get("GOLLMGO_B200_FUSE_ROPE", "1") != "0"
 MAX_SPLITS = 16
 CTAS_PER_SM = 3            # decode attention CTAs resident on one SM (csrc/attention_mma.cu)
 ASSUMED_TILES = 32         # context the choice is tuned for: 32 tiles of 64 keys
-SPLIT_OVERHEAD = 4         # fixed cost of one slice (prologue, combine, merge kernel), in tiles
-CLUSTER_OVERHEAD = 2       # the same where the slices merge inside a cluster, without a merge kernel
+# The cost of a count of slices, in units of the time a CTA takes for one tile when it does
+# not have to share the memory bandwidth (about 1.6 us):
+SPLIT_OVERHEAD = 4         # fixed cost with a merge kernel (prologue, combine, merge launch)
+CLUSTER_OVERHEAD = 2       # fixed cost where the slices merge inside a cluster instead
+PER_SLICE = 0.3            # what every further slice adds (barriers, partial results to merge)
+WAVE_PENALTY = 4           # every further round of CTAs or clusters, beyond its tiles
+BANDWIDTH_TILE = 0.003     # a tile's share of the memory bandwidth: no count of slices gets below
+                           # tiles x this, however many CTAs work at once
+CLUSTER_FILL = 0.9         # share of the cluster capacity to count on: clusters are placed while the kernel
+                           # before still drains, and a launch that needs every last place often waits for a
+                           # second round (measured: a quarter of the launches, 11 us each)
 
 
 def decode_splits(n_dec: int, ctas_per_split: int, num_sms: int, cluster_capacity=None) -> int:
-    """Slices of the context per decoded token.  Picks the count that minimises
-    waves x (tiles per slice + fixed cost per slice) for a typical context.  It depends
-    only on the batch, never on the actual context lengths, so a captured step stays
-    valid as contexts grow.  cluster_capacity[s], where given and not 0, is how many
+    """Slices of the context per decoded token: the count with the least estimated time
+    max(bandwidth floor, rounds x tiles per slice) + overheads for a typical context.  It
+    depends only on the batch, never on the actual context lengths, so a captured step
+    stays valid as contexts grow.  cluster_capacity[s], where given and not 0, is how many
     clusters of s slices the device holds at once: the decode kernel merges such slices
-    itself (csrc/attention_mma.cu)."""
+    itself (csrc/attention_mma.cu).  Tuned on measured step times at batches 1 to 64."""
     slots = CTAS_PER_SM * num_sms
     ctas = max(1, n_dec * ctas_per_split)
+    floor = ctas * ASSUMED_TILES * BANDWIDTH_TILE
     best, best_cost = 1, None
     for s in range(1, MAX_SPLITS + 1):
         cap = cluster_capacity[s] if cluster_capacity and s < len(cluster_capacity) else 0
         if cap > 0:
-            cost = -(-ctas // cap) * (ASSUMED_TILES / s + CLUSTER_OVERHEAD)
+            rounds, fixed = -(-ctas // max(1, int(cap * CLUSTER_FILL))), CLUSTER_OVERHEAD
         else:
-            cost = -(-ctas * s // slots) * (ASSUMED_TILES / s + SPLIT_OVERHEAD)
+            rounds, fixed = -(-ctas * s // slots), SPLIT_OVERHEAD
+        cost = max(floor, rounds * -(-ASSUMED_TILES // s)) + fixed + PER_SLICE * s + WAVE_PENALTY * (rounds - 1)
         if best_cost is None or cost < best_cost - 1e-9:
             best, best_cost = s, cost
     return best
