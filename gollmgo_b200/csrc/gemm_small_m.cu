@@ -24,7 +24,24 @@
 #define GSM_THREADS (GSM_WARPS * 32)
 #define GSM_SPAN 64               // k per warp per iteration
 
-enum { GSM_OUT_BF16 = 0, GSM_OUT_F32 = 1, GSM_OUT_SILU = 2 };
+enum { GSM_OUT_BF16 = 0, GSM_OUT_F32 = 1, GSM_OUT_SILU = 2, GSM_OUT_RESNORM = 3 };
+
+// Two ways to keep an RMSNorm out of the chain of kernels (rms = sqrt(mean(h^2) + eps)):
+//   * the product that ends a mixer or feed-forward (mode GSM_OUT_RESNORM) adds its result to
+//     the float32 residual stream h in place, writes h * w (w the next norm's weight) in
+//     bfloat16 where the norm's output would go, and leaves, per row tile and token, the
+//     sum of h^2 over the tile's 16 columns in out_partials[tile * 16 + token];
+//   * the product that follows takes that h * w as its x and multiplies row t of its result
+//     by 1 / rms_t, which it gets from in_partials: the same as x = h * w / rms_t, since the
+//     factor is one per token.  Sums run in a fixed order: no atomics, same result each run.
+struct GsmFuse {
+  const float* in_partials;   // [in_tiles, 16] sums of squares of this product's (unnormalised) x, or null
+  int in_tiles;
+  float inv_h, eps;           // 1 / hidden size, the norm's eps
+  float* resid;               // GSM_OUT_RESNORM: [M, N] float32 residual stream, updated in place
+  const float* norm_w;        // [N] weight of the norm that follows
+  float* out_partials;        // [tiles of 16 columns, 16]
+};
 
 #define GSM_STAGES 6
 
@@ -55,8 +72,9 @@ template <int NT, int MODE>
 __global__ void __launch_bounds__(GSM_THREADS)
 gemm_small_m_kernel(const __nv_bfloat16* __restrict__ x, long long ldx,
                     const __nv_bfloat16* __restrict__ W, void* __restrict__ out, int M, int N, int K,
-                    int num_tiles) {
+                    int num_tiles, const GsmFuse fuse) {
   constexpr int GROUP = NT == 1 ? 8 : 4;
+  __shared__ float row_scale[16];
   extern __shared__ __align__(16) unsigned char gsm_smem[];
   uint4* ring = reinterpret_cast<uint4*>(gsm_smem);                       // [warps][stages][4][32]
   float (*red)[16][8 * NT + 1] =
@@ -105,6 +123,23 @@ gemm_small_m_kernel(const __nv_bfloat16* __restrict__ x, long long ldx,
   for (int s = 0; s < GSM_STAGES - 1; ++s) issue();
   pdl_trigger();
   pdl_wait();
+  if (fuse.in_partials) {
+    // 1 / rms of every token from the partial sums: thread (tl, tok) adds tiles tl, tl + 16, ...,
+    // then thread tok adds the 16 results, in that order
+    float (*sc)[17] = reinterpret_cast<float (*)[17]>(&red[0][0][0]);
+    const int tl = threadIdx.x >> 4, tok = threadIdx.x & 15;
+    float v = 0.f;
+    for (int tile = tl; tile < fuse.in_tiles; tile += GSM_THREADS / 16) v += fuse.in_partials[tile * 16 + tok];
+    sc[tl][tok] = v;
+    __syncthreads();
+    if (threadIdx.x < 16) {
+      float sum = 0.f;
+#pragma unroll
+      for (int i = 0; i < GSM_THREADS / 16; ++i) sum += sc[i][threadIdx.x];
+      row_scale[threadIdx.x] = rsqrtf(sum * fuse.inv_h + fuse.eps);
+    }
+    __syncthreads();
+  }
   int c_stage = 0;
   for (int g0 = 0; g0 < my_tiles; g0 += GROUP) {
     const int gsize = min(GROUP, my_tiles - g0);
@@ -168,9 +203,32 @@ gemm_small_m_kernel(const __nv_bfloat16* __restrict__ x, long long ldx,
               float gate = 0.f, up = 0.f;
 #pragma unroll
               for (int wv = 0; wv < GSM_WARPS; ++wv) { gate += red[wv][r][tok]; up += red[wv][r + 8][tok]; }
+              if (fuse.in_partials) { gate *= row_scale[tok]; up *= row_scale[tok]; }
               const float v = gate / (1.f + expf(-gate)) * up;
               reinterpret_cast<__nv_bfloat16*>(out)[(size_t)tok * N + f] = __float2bfloat16_rn(v);
             }
+          }
+        } else if (MODE == GSM_OUT_RESNORM) {
+          // 16 neighbouring lanes hold the 16 columns of one token
+          for (int e = threadIdx.x; e < 8 * NT * 16; e += GSM_THREADS) {
+            const int tok = e >> 4, r = e & 15;
+            const int n = tile * 16 + r;
+            float h = 0.f;
+            if (tok < M && n < N) {
+              float v = 0.f;
+#pragma unroll
+              for (int wv = 0; wv < GSM_WARPS; ++wv) v += red[wv][r][tok];
+              if (fuse.in_partials) v *= row_scale[tok];
+              h = fuse.resid[(size_t)tok * N + n] + v;
+              fuse.resid[(size_t)tok * N + n] = h;
+              reinterpret_cast<__nv_bfloat16*>(out)[(size_t)tok * N + n] = __float2bfloat16_rn(h * fuse.norm_w[n]);
+            }
+            float sq = h * h;
+            sq += __shfl_xor_sync(0xffffffffu, sq, 8);
+            sq += __shfl_xor_sync(0xffffffffu, sq, 4);
+            sq += __shfl_xor_sync(0xffffffffu, sq, 2);
+            sq += __shfl_xor_sync(0xffffffffu, sq, 1);
+            if (r == 0) fuse.out_partials[tile * 16 + tok] = sq;
           }
         } else {
           for (int e = threadIdx.x; e < 8 * NT * 16; e += GSM_THREADS) {
@@ -180,6 +238,7 @@ gemm_small_m_kernel(const __nv_bfloat16* __restrict__ x, long long ldx,
               float v = 0.f;
 #pragma unroll
               for (int wv = 0; wv < GSM_WARPS; ++wv) v += red[wv][r][tok];
+              if (fuse.in_partials) v *= row_scale[tok];
               if (MODE == GSM_OUT_F32) reinterpret_cast<float*>(out)[(size_t)tok * N + n] = v;
               else reinterpret_cast<__nv_bfloat16*>(out)[(size_t)tok * N + n] = __float2bfloat16_rn(v);
             }
@@ -193,15 +252,25 @@ gemm_small_m_kernel(const __nv_bfloat16* __restrict__ x, long long ldx,
 }
 
 // mode: 0 = bfloat16 out [M, N]; 1 = float32 out [M, N]; 2 = W is [2N, K] (gate rows then
-// up rows) and out is bfloat16 [M, N] = silu(x Wg^T) * (x Wu^T).
-extern "C" int gg_gemm_small_m(const void* x, long long ldx, const void* W, void* out, int M, int N,
-                               int K, int mode, cudaStream_t stream) {
+// up rows) and out is bfloat16 [M, N] = silu(x Wg^T) * (x Wu^T); 3 = out is the bfloat16
+// input of the next norm and resid / norm_w / out_partials are used (see GsmFuse).
+// in_partials (or null) with in_tiles, hidden and eps: x is an unnormalised norm input.
+extern "C" int gg_gemm_small_m_fused(const void* x, long long ldx, const void* W, void* out, int M, int N,
+                                     int K, int mode, const float* in_partials, int in_tiles, int hidden,
+                                     float eps, float* resid, const float* norm_w, float* out_partials,
+                                     cudaStream_t stream) {
   GG_REQUIRE(M >= 0 && N > 0 && K > 0, "gemm_small_m: bad sizes M=%d N=%d K=%d", M, N, K);
   GG_REQUIRE(M <= 16, "gemm_small_m: %d tokens; this kernel takes at most 16", M);
   GG_REQUIRE(K % 8 == 0 && ldx % 8 == 0, "gemm_small_m: K=%d and the row stride %lld of x must be multiples of 8", K, ldx);
   GG_REQUIRE(((size_t)x % 16) == 0 && ((size_t)W % 16) == 0, "gemm_small_m: x and W must be 16-byte aligned");
-  GG_REQUIRE(mode >= 0 && mode <= 2, "gemm_small_m: unknown mode %d", mode);
+  GG_REQUIRE(mode >= 0 && mode <= 3, "gemm_small_m: unknown mode %d", mode);
+  GG_REQUIRE(!in_partials || (in_tiles > 0 && hidden > 0), "gemm_small_m: partial sums without their sizes");
+  GG_REQUIRE(mode != GSM_OUT_RESNORM || (resid && norm_w && out_partials), "gemm_small_m: mode 3 needs resid, norm_w and out_partials");
   if (M == 0) return GG_OK;
+  GsmFuse fuse = {};
+  fuse.in_partials = in_partials; fuse.in_tiles = in_tiles;
+  fuse.inv_h = hidden > 0 ? 1.0f / (float)hidden : 0.f; fuse.eps = eps;
+  fuse.resid = resid; fuse.norm_w = norm_w; fuse.out_partials = out_partials;
   const __nv_bfloat16* xp = (const __nv_bfloat16*)x;
   const __nv_bfloat16* wp = (const __nv_bfloat16*)W;
   const int num_tiles = mode == GSM_OUT_SILU ? (N + 7) / 8 : (N + 15) / 16;
@@ -223,13 +292,23 @@ extern "C" int gg_gemm_small_m(const void* x, long long ldx, const void* W, void
       if (e != cudaSuccess) return gg_fail(GG_ERR_CUDA, "gemm_small_m: %s", cudaGetErrorString(e));   \
       set = true;                                                                                     \
     }                                                                                                 \
-    gg_launch(gemm_small_m_kernel<NT, MODE>, dim3(grid), dim3(GSM_THREADS), smem, stream, xp, ldx, wp, out, M, N, K, num_tiles); \
+    gg_launch(gemm_small_m_kernel<NT, MODE>, dim3(grid), dim3(GSM_THREADS), smem, stream, xp, ldx, wp, out, M, N, K, num_tiles, fuse); \
   } while (0)
-  if (M <= 8) {
-    if (mode == 0) GSM_LAUNCH(1, GSM_OUT_BF16); else if (mode == 1) GSM_LAUNCH(1, GSM_OUT_F32); else GSM_LAUNCH(1, GSM_OUT_SILU);
-  } else {
-    if (mode == 0) GSM_LAUNCH(2, GSM_OUT_BF16); else if (mode == 1) GSM_LAUNCH(2, GSM_OUT_F32); else GSM_LAUNCH(2, GSM_OUT_SILU);
-  }
+#define GSM_MODES(NT)                                                  \
+  do {                                                                 \
+    if (mode == 0) GSM_LAUNCH(NT, GSM_OUT_BF16);                       \
+    else if (mode == 1) GSM_LAUNCH(NT, GSM_OUT_F32);                   \
+    else if (mode == 2) GSM_LAUNCH(NT, GSM_OUT_SILU);                  \
+    else GSM_LAUNCH(NT, GSM_OUT_RESNORM);                              \
+  } while (0)
+  if (M <= 8) GSM_MODES(1); else GSM_MODES(2);
+#undef GSM_MODES
 #undef GSM_LAUNCH
   return gg_check_launch("gemm_small_m");
+}
+
+extern "C" int gg_gemm_small_m(const void* x, long long ldx, const void* W, void* out, int M, int N,
+                               int K, int mode, cudaStream_t stream) {
+  GG_REQUIRE(mode >= 0 && mode <= 2, "gemm_small_m: unknown mode %d", mode);
+  return gg_gemm_small_m_fused(x, ldx, W, out, M, N, K, mode, nullptr, 0, 0, 0.f, nullptr, nullptr, nullptr, stream);
 }

@@ -232,10 +232,20 @@ def small_m_ok(x: torch.Tensor, w: torch.Tensor) -> bool:
             and x.stride(0) % 8 == 0 and w.is_contiguous())
 
 
-def gemm_small_m(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, gated: bool = False) -> None:
+def gemm_small_m(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, gated: bool = False,
+                 in_partials: Optional[torch.Tensor] = None, hidden: int = 0, eps: float = 0.0,
+                 resid: Optional[torch.Tensor] = None, norm_w: Optional[torch.Tensor] = None,
+                 out_partials: Optional[torch.Tensor] = None) -> None:
     """out[M, N] = x[M, K] @ w[N, K]^T for M <= 16 (bfloat16 in, float32 accumulate); out is
     bfloat16 or float32.  ``gated``: w is [2N, K] (gate rows, then up rows) and
-    out = silu(x Wg^T) * (x Wu^T) in bfloat16."""
+    out = silu(x Wg^T) * (x Wu^T) in bfloat16.
+
+    RMSNorm folded in on either side (rms_t = sqrt(mean_k h[t, k]^2 + eps)):
+    ``resid``, ``norm_w``, ``out_partials``: the product is added to the float32 residual
+    stream ``resid`` [M, N] in place, ``out`` (bfloat16) becomes resid * norm_w, and
+    out_partials [ceil(N / 16), 16] float32 gets the sums of resid^2 over each 16 columns.
+    ``in_partials`` (+ ``hidden``, ``eps``): x is such an unnormalised resid * norm_w and
+    in_partials its partial sums; row t of the result is divided by rms_t."""
     M, K = x.shape
     N = out.shape[1]
     if w.shape != ((2 * N, K) if gated else (N, K)) or out.shape[0] != M or not out.is_contiguous():
@@ -248,8 +258,29 @@ def gemm_small_m(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, gated: boo
         mode = 1 if out.dtype == torch.float32 else 0
         if out.dtype not in (torch.float32, torch.bfloat16):
             raise KernelError("gemm_small_m: out must be bfloat16 or float32")
-    _check(lib().gg_gemm_small_m(_p(x), ctypes.c_longlong(x.stride(0)), _p(w), _p(out), M, N, K, mode,
-                                 _stream()))
+    in_tiles = 0
+    if in_partials is not None:
+        if in_partials.dtype != torch.float32 or in_partials.dim() != 2 or in_partials.shape[1] != 16 \
+                or not in_partials.is_contiguous() or hidden <= 0:
+            raise KernelError("gemm_small_m: in_partials must be contiguous float32 [tiles, 16] with the hidden size given")
+        in_tiles = in_partials.shape[0]
+    if resid is not None or norm_w is not None or out_partials is not None:
+        if gated or out.dtype != torch.bfloat16:
+            raise KernelError("gemm_small_m: the residual epilogue writes bfloat16 and is not gated")
+        if resid is None or norm_w is None or out_partials is None:
+            raise KernelError("gemm_small_m: resid, norm_w and out_partials go together")
+        if resid.dtype != torch.float32 or resid.shape != (M, N) or not resid.is_contiguous():
+            raise KernelError("gemm_small_m: resid must be contiguous float32 [M, N]")
+        if norm_w.dtype != torch.float32 or norm_w.numel() != N or not norm_w.is_contiguous():
+            raise KernelError("gemm_small_m: norm_w must be contiguous float32 [N]")
+        if out_partials.dtype != torch.float32 or not out_partials.is_contiguous() \
+                or out_partials.numel() < -(-N // 16) * 16:
+            raise KernelError("gemm_small_m: out_partials must be contiguous float32 [ceil(N / 16), 16]")
+        mode = 3
+    _cuda(w, out, in_partials, resid, norm_w, out_partials)
+    _check(lib().gg_gemm_small_m_fused(_p(x), ctypes.c_longlong(x.stride(0)), _p(w), _p(out), M, N, K, mode,
+                                       _p(in_partials), in_tiles, int(hidden), ctypes.c_float(eps),
+                                       _p(resid), _p(norm_w), _p(out_partials), _stream()))
 
 
 _TC_STATUS = {}

@@ -17,7 +17,7 @@ import torch
 from ..cache import PagedKVNeed
 from ..csrc import ops
 from ..weights import WeightSpec
-from .linear import linear
+from .linear import fuses_norms, linear
 from .registry import build_position, register_mixer
 
 # Which prompt-attention kernel the bfloat16 mode uses: "auto" = the most specialised one that
@@ -117,7 +117,14 @@ class Attention:
         self.w_qkv = torch.cat([q.to(dt), k.to(dt), v.to(dt)], dim=0).contiguous()
         self.w_o = get("o_proj.weight").contiguous()
 
-    def forward(self, x, batch, cache, writes_cache=True):
+    # the optional protocol of parts/linear.py
+    def takes_normed_rows(self, num_tokens):
+        return fuses_norms(num_tokens, self.w_qkv, self.ctx.act_dtype)
+
+    def fuses_next_norm(self, num_tokens):
+        return fuses_norms(num_tokens, self.w_o, self.ctx.act_dtype)
+
+    def forward(self, x, batch, cache, writes_cache=True, then=None):
         T = x.shape[0]
         ws = self.ctx.workspace
         kc, vc, group = cache
@@ -160,8 +167,7 @@ class Attention:
                             batch.context_lens, batch.dec_seqs, batch.num_decode, splits,
                             part_o, part_ml, out, self.nh, self.nkv, self.d, self.ctx.page_size, window, self.scale)
         y = ws.get("mixer_out", T, self.hidden)
-        linear(out, self.w_o, y)
-        return y
+        return linear(out, self.w_o, y, then)
 
 
 register_mixer("attention", Attention)

@@ -8,7 +8,7 @@ import torch
 
 from ..csrc import ops
 from ..weights import WeightSpec
-from .linear import linear, use_tc
+from .linear import NormedRows, fuses_norms, linear, use_tc
 from .registry import register_feed_forward
 
 
@@ -40,11 +40,22 @@ class GatedMLP:
         self.w_gate_up = torch.cat([g.to(dt), u.to(dt)], dim=0).contiguous()
         self.w_down = get("down_proj.weight").contiguous()
 
-    def forward(self, x, batch):
+    # the optional protocol of parts/linear.py: the first product can take a norm's unnormalised
+    # input, the last one can do the residual add and prepare the next norm
+    def takes_normed_rows(self, num_tokens):
+        return fuses_norms(num_tokens, self.w_gate_up, self.ctx.act_dtype)
+
+    def fuses_next_norm(self, num_tokens):
+        return fuses_norms(num_tokens, self.w_down, self.ctx.act_dtype)
+
+    def forward(self, x, batch, then=None):
         T = x.shape[0]
         ws = self.ctx.workspace
         a = ws.get("ffn_act", T, self.inter)
-        if ops.small_m_ok(x, self.w_gate_up):
+        if isinstance(x, NormedRows):
+            ops.gemm_small_m(x.scaled, self.w_gate_up, a, gated=True, in_partials=x.partials,
+                             hidden=x.hidden, eps=x.eps)
+        elif ops.small_m_ok(x, self.w_gate_up):
             ops.gemm_small_m(x, self.w_gate_up, a, gated=True)       # product and activation in one
         elif use_tc(x, self.w_gate_up, self.inter, True):
             ops.gemm_tc(x, self.w_gate_up, a, gated=True, pair=True)  # the same, on tcgen05 (CTA pairs)
@@ -53,8 +64,7 @@ class GatedMLP:
             linear(x, self.w_gate_up, gu)
             ops.silu_mul(gu, a)
         y = ws.get("ffn_out", T, self.hidden)
-        linear(a, self.w_down, y)
-        return y
+        return linear(a, self.w_down, y, then)
 
 
 register_feed_forward("gated_mlp", GatedMLP)

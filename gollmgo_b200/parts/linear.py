@@ -44,9 +44,58 @@ def use_tc(x: torch.Tensor, w: torch.Tensor, out_cols: int, gated: bool) -> bool
     return GEMM_POLICY == "tc" or (gated and x.shape[0] >= TC_MIN_TOKENS)
 
 
-def linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+# Steps of a few tokens: the residual add and the RMSNorm between two products are done by
+# the products themselves (csrc/gemm_small_m.cu) instead of by a kernel between them.
+FUSE_NORMS = os.environ.get("GOLLMGO_B200_FUSE_NORM", "1") != "0"
+
+
+class NextNorm:
+    """What the last product of a mixer or feed-forward is asked to do with its result y
+    instead of returning it: resid += y, and leave the input of the norm (weight, eps) that
+    follows as NormedRows in the buffers ``scaled`` [T, hidden] and ``partials``."""
+
+    def __init__(self, resid, weight, eps, scaled, partials):
+        self.resid, self.weight, self.eps = resid, weight, eps
+        self.scaled, self.partials = scaled, partials
+
+
+class NormedRows:
+    """A norm's output that is not divided by the root mean square yet: ``scaled`` is
+    resid * weight in bfloat16, ``partials[tile, t]`` the sums of resid[t]^2 over slices of
+    the hidden size.  The product that takes it as x multiplies row t of its result by
+    rsqrt(sum(partials[:, t]) / hidden + eps): one factor per token, so the same as
+    normalising x first."""
+
+    def __init__(self, scaled, partials, hidden, eps):
+        self.scaled, self.partials, self.hidden, self.eps = scaled, partials, hidden, eps
+
+    @property
+    def shape(self):
+        return self.scaled.shape
+
+
+def fuses_norms(num_tokens: int, w: torch.Tensor, act_dtype: torch.dtype) -> bool:
+    """Whether a product with weight w of a step of num_tokens tokens can take NormedRows
+    as x, or do what a NextNorm asks."""
+    return (FUSE_NORMS and w is not None and w.is_cuda and 0 < num_tokens <= ops.SMALL_M
+            and act_dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and w.is_contiguous()
+            and w.shape[1] % 8 == 0)
+
+
+def linear(x, w: torch.Tensor, out: torch.Tensor, then: Optional[NextNorm] = None):
     """out[T, N] = x[T, K] @ w[N, K]^T, rounded to out's dtype.  A weight stored in
-    float32 is multiplied in float32 even when the activations are bfloat16."""
+    float32 is multiplied in float32 even when the activations are bfloat16.
+    x may be NormedRows and ``then`` a NextNorm where fuses_norms() holds (the caller
+    checks); with ``then`` the result is the NormedRows of the next norm, not out."""
+    if isinstance(x, NormedRows) or then is not None:
+        rows = x if isinstance(x, NormedRows) else None
+        xt = rows.scaled if rows else x
+        kw = dict(in_partials=rows.partials, hidden=rows.hidden, eps=rows.eps) if rows else {}
+        if then is None:
+            ops.gemm_small_m(xt, w, out, **kw)
+            return out
+        ops.gemm_small_m(xt, w, then.scaled, resid=then.resid, norm_w=then.weight, out_partials=then.partials, **kw)
+        return NormedRows(then.scaled, then.partials, then.scaled.shape[1], then.eps)
     if ops.small_m_ok(x, w) and out.is_contiguous():
         ops.gemm_small_m(x, w, out)          # a few tokens: the weight-streaming kernel
     elif out.is_contiguous() and use_tc(x, w, out.shape[1], False):

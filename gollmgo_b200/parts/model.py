@@ -112,8 +112,15 @@ class DecoderModel:
         ops.embed_gather(batch.token_ids, self.embed, resid, self.bad_id,
                          getattr(batch, "token_src", None), getattr(batch, "prev_tokens", None))
         delta = None
-        for e in self.spec.run_order:
-            delta = self.blocks[e.layer].forward(resid, delta, batch, caches[e.cache], e.writes_cache)
+        order = self.spec.run_order
+        for i, e in enumerate(order):
+            block = self.blocks[e.layer]
+            if getattr(block, "chains_norms", False):
+                # such a block may fold the first norm of the block that runs next into its last product
+                nxt = self.blocks[order[i + 1].layer] if i + 1 < len(order) else None
+                delta = block.forward(resid, delta, batch, caches[e.cache], e.writes_cache, next_block=nxt)
+            else:
+                delta = block.forward(resid, delta, batch, caches[e.cache], e.writes_cache)
         R = batch.num_logit_rows
         logits = torch.empty(R, self.spec.vocab_size, dtype=torch.float32, device=self.ctx.device)
         if R == 0:

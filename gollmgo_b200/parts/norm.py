@@ -26,6 +26,11 @@ class RMSNorm:
     def load(self, get):
         self.weight = get("").to(torch.float32).contiguous()
 
+    def rms_weight_eps(self):
+        """(weight, eps) for a product that folds this norm in (parts/linear.py): only a norm
+        that is exactly x * rsqrt(mean(x^2) + eps) * weight may offer this."""
+        return self.weight, self.eps
+
     def add_norm(self, resid, delta, out, rows=None, write_back=True):
         """resid (+= delta); out = norm(resid) * weight.  With ``rows`` only those rows
         are normed (out[i] from resid[rows[i]])."""

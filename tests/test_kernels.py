@@ -456,6 +456,49 @@ def test_gemm_small_m_gated(ops, cuda_device, M, I, K):
     torch.testing.assert_close(out.float(), ref.to(torch.bfloat16).float(), rtol=1e-2, atol=1e-2)
 
 
+@pytest.mark.parametrize("M", [1, 8, 11])
+@pytest.mark.parametrize("H,I", [(48, 104), (4096, 1024), (1000, 264)])
+def test_gemm_small_m_with_norms_folded_in(ops, cuda_device, M, H, I):
+    """A product that adds to the residual and prepares the next norm, then a (gated) product
+    that takes the unnormalised input: together the same as add, RMSNorm, product."""
+    g = torch.Generator(device="cuda").manual_seed(M + H)
+    eps = 3e-6
+    a = torch.randn(M, I, device="cuda", generator=g).to(torch.bfloat16)
+    w_down = (torch.randn(H, I, device="cuda", generator=g) / math.sqrt(I)).to(torch.bfloat16)
+    resid0 = torch.randn(M, H, device="cuda", generator=g) * 3
+    norm_w = 1 + 0.2 * torch.randn(H, device="cuda", generator=g)
+    w_gu = (torch.randn(2 * I, H, device="cuda", generator=g) * (2.0 / math.sqrt(H))).to(torch.bfloat16)
+    w_q = (torch.randn(I, H, device="cuda", generator=g) / math.sqrt(H)).to(torch.bfloat16)
+    # reference in float64
+    h = resid0.double() + a.double() @ w_down.double().T
+    xn = h * torch.rsqrt((h * h).mean(-1, keepdim=True) + eps) * norm_w.double()
+    gu = xn @ w_gu.double().T
+    ref_gated = gu[:, :I] / (1 + torch.exp(-gu[:, :I])) * gu[:, I:]
+    ref_q = xn @ w_q.double().T
+    # the kernels
+    resid = resid0.clone()
+    scaled = torch.empty(M, H, device="cuda", dtype=torch.bfloat16)
+    partials = torch.full((-(-H // 16), 16), float("nan"), device="cuda")
+    ops.gemm_small_m(a, w_down, scaled, resid=resid, norm_w=norm_w, out_partials=partials)
+    torch.testing.assert_close(resid.double(), h, rtol=1e-5, atol=1e-5)
+    torch.testing.assert_close(scaled.double(), (h * norm_w.double()), rtol=1e-2, atol=1e-2)
+    torch.testing.assert_close(partials[:, :M].sum(0).double(), (h * h).sum(-1), rtol=1e-5, atol=1e-5)
+    out_g = torch.empty(M, I, device="cuda", dtype=torch.bfloat16)
+    ops.gemm_small_m(scaled, w_gu, out_g, gated=True, in_partials=partials, hidden=H, eps=eps)
+    out_q = torch.empty(M, I, device="cuda", dtype=torch.bfloat16)
+    ops.gemm_small_m(scaled, w_q, out_q, in_partials=partials, hidden=H, eps=eps)
+    out_f = torch.empty(M, I, device="cuda", dtype=torch.float32)
+    ops.gemm_small_m(scaled, w_q, out_f, in_partials=partials, hidden=H, eps=eps)
+    scale = ref_q.abs().max().item()
+    assert (out_q.double() - ref_q).abs().max().item() <= 2e-2 * scale
+    assert (out_f.double() - ref_q).abs().max().item() <= 1e-2 * scale        # only x is rounded to bfloat16
+    assert (out_g.double() - ref_gated).abs().max().item() <= 2e-2 * ref_gated.abs().max().item()
+    # twice the same: no atomics anywhere
+    resid2, scaled2, partials2 = resid0.clone(), torch.empty_like(scaled), torch.empty_like(partials)
+    ops.gemm_small_m(a, w_down, scaled2, resid=resid2, norm_w=norm_w, out_partials=partials2)
+    assert torch.equal(resid, resid2) and torch.equal(scaled, scaled2) and torch.equal(partials[:, :M], partials2[:, :M])
+
+
 def test_gemm_small_m_refuses_what_it_cannot_do(ops, cuda_device):
     x = torch.zeros(17, 64, device="cuda", dtype=torch.bfloat16)
     w = torch.zeros(32, 64, device="cuda", dtype=torch.bfloat16)

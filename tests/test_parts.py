@@ -172,3 +172,58 @@ def test_block_is_the_plain_decoder_layer(kit, dtype):
     delta = block.forward(resid, None, batch, cm.layer_cache(0))
     got = resid.cpu().double() + delta.cpu().double()            # the block still owes its last delta
     close(got, want, dtype)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("fuse", [True, False])
+def test_two_blocks_of_a_short_step_with_norms_inside_the_products(kit, cuda_device, monkeypatch, fuse):
+    """Steps of up to 16 tokens in bfloat16: the residual adds and norms between the products
+    are done by the products (parts/linear.py).  Two chained blocks give the plain result
+    either way, and the fused way really hands NormedRows from block to block."""
+    import importlib
+    L = importlib.import_module("gollmgo_b200.parts.linear")     # the package also exports a function of that name
+    monkeypatch.setattr(L, "FUSE_NORMS", fuse)
+    dtype = torch.bfloat16
+    torch.manual_seed(11)
+    Hd, nh, nkv, d, I = 64, 4, 2, 16, 104
+    cfg = {"hidden_size": Hd, "num_attention_heads": nh, "num_key_value_heads": nkv, "head_dim": d,
+           "intermediate_size": I, "rms_norm_eps": 2e-6, "rope_theta": 10000.0, "num_hidden_layers": 2}
+    ctx = ctx_for(kit, dtype)
+    S = kit.parts.PartSpec
+    pos = S("rope", {"head_dim": d, "theta": 10000.0, "scaling": None})
+    blocks, w = [], {}
+    for l in range(2):
+        mixer = kit.parts.build_mixer(S("attention", {"hidden_size": Hd, "num_heads": nh, "num_kv_heads": nkv,
+                                                      "head_dim": d, "window": None, "position": pos}), ctx)
+        ff = kit.parts.build_feed_forward(S("gated_mlp", {"hidden_size": Hd, "intermediate_size": I}), ctx)
+        n1 = kit.parts.build_norm(S("rmsnorm", {"size": Hd, "eps": 2e-6}), ctx)
+        n2 = kit.parts.build_norm(S("rmsnorm", {"size": Hd, "eps": 2e-6}), ctx)
+        p = f"model.layers.{l}."
+        for pre, part in ((p + "self_attn.", mixer), (p + "mlp.", ff)):
+            for n, s in part.weights().items():
+                w[pre + n] = (torch.randn(s.shape) * 0.2).to(dtype)
+        w[p + "input_layernorm.weight"] = (1 + 0.1 * torch.randn(Hd)).to(dtype)
+        w[p + "post_attention_layernorm.weight"] = (1 + 0.1 * torch.randn(Hd)).to(dtype)
+        mixer.load(lambda n, p=p: w[p + "self_attn." + n].cuda())
+        ff.load(lambda n, p=p: w[p + "mlp." + n].cuda())
+        n1.load(lambda n, p=p: w[p + "input_layernorm.weight"].cuda())
+        n2.load(lambda n, p=p: w[p + "post_attention_layernorm.weight"].cuda())
+        blocks.append((kit.parts.build_block(kit.parts.LayerSpec(S("pre_norm"), None, None, None, None),
+                                             mixer, ff, n1, n2, ctx), mixer))
+    T = 7                                                            # one portion of 7 tokens
+    x0 = torch.randn(T, Hd)
+    inv = P.rope_inv_freq(d, 10000.0, None)
+    want = x0.double()
+    for l in range(2):
+        want = P.decoder_layer(want, w, l, cfg, torch.arange(T), inv, None)
+    cm = kit.CacheManager([blocks[0][1].cache_need(), blocks[1][1].cache_need()], 16, 16, 2, dtype=dtype, device="cuda")
+    bb = kit.BatchBuilder(cm, "cuda")
+    cm.admit("s")
+    batch = bb.build([kit.StepEntry("s", [0] * T, [])])
+    resid = x0.cuda().clone()
+    d0 = blocks[0][0].forward(resid, None, batch, cm.layer_cache(0), next_block=blocks[1][0])
+    assert isinstance(d0, L.NormedRows) == fuse
+    d1 = blocks[1][0].forward(resid, d0, batch, cm.layer_cache(1), next_block=None)
+    assert isinstance(d1, torch.Tensor)                              # nothing runs next: a plain delta
+    got = resid.cpu().double() + d1.cpu().double()
+    close(got, want, dtype)
