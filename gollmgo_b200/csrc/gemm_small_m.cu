@@ -68,12 +68,15 @@ __device__ __forceinline__ void tile_rows(int tile, int g, int N, int& n_a, int&
 // boundaries, so about five chunks of weights per lane (10 KB per warp) are in
 // flight at any time; the lane that copies a chunk is the lane that consumes it, so
 // waiting on its own copy groups is all the synchronisation the ring needs.
-template <int NT, int MODE>
+// GROUP x XB is the same for every shape, so the unrolled loop body keeps its size (a body
+// several times larger measurably stalls on instruction fetch): CTAs with many row tiles
+// share one fetch of x among GROUP tiles; CTAs with one or two tiles fetch the x chunks of
+// XB K steps together instead, so that the latencies of those loads overlap.
+template <int NT, int MODE, int GROUP, int XB>
 __global__ void __launch_bounds__(GSM_THREADS)
 gemm_small_m_kernel(const __nv_bfloat16* __restrict__ x, long long ldx,
                     const __nv_bfloat16* __restrict__ W, void* __restrict__ out, int M, int N, int K,
                     int num_tiles, const GsmFuse fuse) {
-  constexpr int GROUP = NT == 1 ? 8 : 4;
   __shared__ float row_scale[16];
   extern __shared__ __align__(16) unsigned char gsm_smem[];
   uint4* ring = reinterpret_cast<uint4*>(gsm_smem);                       // [warps][stages][4][32]
@@ -148,34 +151,46 @@ gemm_small_m_kernel(const __nv_bfloat16* __restrict__ x, long long ldx,
     for (int t = 0; t < GROUP; ++t)
 #pragma unroll
       for (int j = 0; j < NT; ++j) { acc[t][j][0] = acc[t][j][1] = acc[t][j][2] = acc[t][j][3] = 0.f; }
-    for (int ki = 0; ki < iters; ++ki) {
-      const int kk = ki + rot < iters ? ki + rot : ki + rot - iters;
-      const int k0 = (kk * GSM_WARPS + warp) * GSM_SPAN + c * 8, k1 = k0 + 32;
-      uint4 x0[NT], x1[NT];
+    // x comes from L2 and a K step is short: a lane asks for its chunks of XB steps at once,
+    // so that their latencies overlap
+    for (int kb = 0; kb < iters; kb += XB) {
+      uint4 xb[XB][2 * NT];
 #pragma unroll
-      for (int j = 0; j < NT; ++j) {
-        x0[j] = (xr[j] && k0 < K) ? __ldg(reinterpret_cast<const uint4*>(xr[j] + k0)) : zero;
-        x1[j] = (xr[j] && k1 < K) ? __ldg(reinterpret_cast<const uint4*>(xr[j] + k1)) : zero;
+      for (int u = 0; u < XB; ++u) {
+        const int ki = kb + u;
+        const int kk = ki + rot < iters ? ki + rot : ki + rot - iters;
+        const int k0 = (kk * GSM_WARPS + warp) * GSM_SPAN + c * 8, k1 = k0 + 32;
+#pragma unroll
+        for (int j = 0; j < NT; ++j) {
+          xb[u][2 * j] = (xr[j] && ki < iters && k0 < K) ? __ldg(reinterpret_cast<const uint4*>(xr[j] + k0)) : zero;
+          xb[u][2 * j + 1] = (xr[j] && ki < iters && k1 < K) ? __ldg(reinterpret_cast<const uint4*>(xr[j] + k1)) : zero;
+        }
       }
 #pragma unroll
-      for (int t = 0; t < GROUP; ++t) {
-        if (t < gsize) {
-          issue();
-          cp_async_wait<GSM_STAGES - 1>();
-          const uint4* st = ring + ((size_t)(warp * GSM_STAGES + c_stage) * 4) * 32 + lane;
-          const uint4 w0 = st[0], w1 = st[32], w2 = st[64], w3 = st[96];
-          c_stage = c_stage + 1 == GSM_STAGES ? 0 : c_stage + 1;
+      for (int u = 0; u < XB; ++u) {
+        if (kb + u < iters) {
 #pragma unroll
-          for (int j = 0; j < NT; ++j) {
-            unsigned a[4];
-            a[0] = w0.x; a[1] = w1.x; a[2] = w0.y; a[3] = w1.y;
-            mma_bf16(acc[t][j], a, x0[j].x, x0[j].y);
-            a[0] = w0.z; a[1] = w1.z; a[2] = w0.w; a[3] = w1.w;
-            mma_bf16(acc[t][j], a, x0[j].z, x0[j].w);
-            a[0] = w2.x; a[1] = w3.x; a[2] = w2.y; a[3] = w3.y;
-            mma_bf16(acc[t][j], a, x1[j].x, x1[j].y);
-            a[0] = w2.z; a[1] = w3.z; a[2] = w2.w; a[3] = w3.w;
-            mma_bf16(acc[t][j], a, x1[j].z, x1[j].w);
+          for (int t = 0; t < GROUP; ++t) {
+            if (t < gsize) {
+              issue();
+              cp_async_wait<GSM_STAGES - 1>();
+              const uint4* st = ring + ((size_t)(warp * GSM_STAGES + c_stage) * 4) * 32 + lane;
+              const uint4 w0 = st[0], w1 = st[32], w2 = st[64], w3 = st[96];
+              c_stage = c_stage + 1 == GSM_STAGES ? 0 : c_stage + 1;
+#pragma unroll
+              for (int j = 0; j < NT; ++j) {
+                const uint4 x0 = xb[u][2 * j], x1 = xb[u][2 * j + 1];
+                unsigned a[4];
+                a[0] = w0.x; a[1] = w1.x; a[2] = w0.y; a[3] = w1.y;
+                mma_bf16(acc[t][j], a, x0.x, x0.y);
+                a[0] = w0.z; a[1] = w1.z; a[2] = w0.w; a[3] = w1.w;
+                mma_bf16(acc[t][j], a, x0.z, x0.w);
+                a[0] = w2.x; a[1] = w3.x; a[2] = w2.y; a[3] = w3.y;
+                mma_bf16(acc[t][j], a, x1.x, x1.y);
+                a[0] = w2.z; a[1] = w3.z; a[2] = w2.w; a[3] = w3.w;
+                mma_bf16(acc[t][j], a, x1.z, x1.w);
+              }
+            }
           }
         }
       }
@@ -283,25 +298,30 @@ extern "C" int gg_gemm_small_m_fused(const void* x, long long ldx, const void* W
   }
   const int grid = num_tiles < 2 * num_sms ? num_tiles : 2 * num_sms;
   const size_t ring_bytes = (size_t)GSM_WARPS * GSM_STAGES * 4 * 32 * 16;
-#define GSM_LAUNCH(NT, MODE)                                                                          \
+#define GSM_LAUNCH(NT, MODE, GROUP, XB)                                                               \
   do {                                                                                                \
     const size_t smem = ring_bytes + sizeof(float) * GSM_WARPS * 16 * (8 * NT + 1);                   \
     static bool set = false;                                                                          \
     if (!set) {                                                                                       \
-      cudaError_t e = cudaFuncSetAttribute(gemm_small_m_kernel<NT, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+      cudaError_t e = cudaFuncSetAttribute(gemm_small_m_kernel<NT, MODE, GROUP, XB>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
       if (e != cudaSuccess) return gg_fail(GG_ERR_CUDA, "gemm_small_m: %s", cudaGetErrorString(e));   \
       set = true;                                                                                     \
     }                                                                                                 \
-    gg_launch(gemm_small_m_kernel<NT, MODE>, dim3(grid), dim3(GSM_THREADS), smem, stream, xp, ldx, wp, out, M, N, K, num_tiles, fuse); \
+    gg_launch(gemm_small_m_kernel<NT, MODE, GROUP, XB>, dim3(grid), dim3(GSM_THREADS), smem, stream, xp, ldx, wp, out, M, N, K, num_tiles, fuse); \
   } while (0)
-#define GSM_MODES(NT)                                                  \
+#define GSM_MODES(NT, GROUP, XB)                                       \
   do {                                                                 \
-    if (mode == 0) GSM_LAUNCH(NT, GSM_OUT_BF16);                       \
-    else if (mode == 1) GSM_LAUNCH(NT, GSM_OUT_F32);                   \
-    else if (mode == 2) GSM_LAUNCH(NT, GSM_OUT_SILU);                  \
-    else GSM_LAUNCH(NT, GSM_OUT_RESNORM);                              \
+    if (mode == 0) GSM_LAUNCH(NT, GSM_OUT_BF16, GROUP, XB);            \
+    else if (mode == 1) GSM_LAUNCH(NT, GSM_OUT_F32, GROUP, XB);        \
+    else if (mode == 2) GSM_LAUNCH(NT, GSM_OUT_SILU, GROUP, XB);       \
+    else GSM_LAUNCH(NT, GSM_OUT_RESNORM, GROUP, XB);                   \
   } while (0)
-  if (M <= 8) GSM_MODES(1); else GSM_MODES(2);
+  const int per_cta = (num_tiles + grid - 1) / grid;      // most row tiles one CTA gets
+  if (M <= 8) {
+    if (per_cta == 1) GSM_MODES(1, 1, 8); else if (per_cta == 2) GSM_MODES(1, 2, 4); else GSM_MODES(1, 8, 1);
+  } else {
+    if (per_cta == 1) GSM_MODES(2, 1, 4); else if (per_cta == 2) GSM_MODES(2, 2, 2); else GSM_MODES(2, 4, 1);
+  }
 #undef GSM_MODES
 #undef GSM_LAUNCH
   return gg_check_launch("gemm_small_m");
