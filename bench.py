@@ -207,7 +207,8 @@ def main() -> int:
     value = B / (ms_step / 1e3)
 
     # ---- end to end through the Python entry point: host tokens in, sampled tokens out, every step
-    params = SamplingParams(max_tokens=W + K + 4, ignore_eos=True)
+    # no sequence ends inside the timed steps (the first ones decode while the last prompts are still read)
+    params = SamplingParams(max_tokens=W + K + 64, ignore_eos=True)
     for j in range(B):
         eng.enqueue(rand_prompt(CONTEXT), params)
     while any(s.state.value != "DECODING" for s in eng.scheduler.running.values()) or eng.scheduler.waiting:

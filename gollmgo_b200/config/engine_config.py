@@ -22,6 +22,7 @@ class EngineConfig:
                                            # request that does not fit is passed over, as in the
                                            # reference (internal/scheduler/fcfs.go:130-161)
     cuda_graphs: bool = True               # capture decode-only steps
+    capture_at_start: bool = True          # capture every batch bucket when the engine is built, not at first use
     device: int = 0
 
     def validate(self) -> None:

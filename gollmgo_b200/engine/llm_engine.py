@@ -80,6 +80,8 @@ class Engine:
         self._next_id = 0
         self._seed_rng = random.Random()
         self._stopped = False
+        if ecfg.cuda_graphs and ecfg.capture_at_start:
+            self.runner.capture_graphs()
 
     # ------------------------------------------------------------------ requests
     def enqueue(self, token_ids: Seq[int], params: Optional[SamplingParams] = None,

@@ -21,7 +21,7 @@ from typing import Dict, List, Optional, Sequence
 import torch
 
 from .. import architectures  # noqa: F401  (registers the architectures)
-from ..cache import CacheManager, PagedKVNeed
+from ..cache import CacheManager, OutOfPages, PagedKVNeed
 from ..config import EngineConfig, read_config_json
 from ..csrc import ops
 from ..parts import BuildContext, build_model, set_matmul_precision
@@ -184,6 +184,35 @@ class ModelRunner:
         ops.launches += cs.launches
         self.steps += 1
         return cs.logits[:len(entries)]
+
+    def capture_graphs(self, up_to: Optional[int] = None) -> int:
+        """Capture the decode step of every batch bucket up to ``up_to`` sequences (default:
+        the largest batch) now, so that no request meets the tens of milliseconds of a
+        capture in the middle of its generation when the batch grows or shrinks into a bucket
+        for the first time.  Uses a request of its own of a few tokens and gives its page
+        back.  Returns the number of buckets captured."""
+        if not self.ecfg.cuda_graphs or self.device.type != "cuda":
+            return 0
+        rid = "__capture__"
+        limit = min(up_to or self.ctx.max_seqs, self.ctx.max_seqs)
+        todo = [b for b in GRAPH_BUCKETS if b <= limit and (b not in self._graphs or self._graphs[b].graph is None)]
+        if not todo or len(todo) + 1 > self.max_model_len:
+            return 0
+        marks = [g.pool.high_water for g in self.cache.groups]
+        self.cache.admit(rid)
+        done = 0
+        try:
+            for b in todo:
+                self._graph_step([StepEntry(rid, [0], [0])], b)
+                done += 1
+            torch.cuda.synchronize(self.device)
+        except OutOfPages:
+            pass                                   # a pool too small even for this: capture at first use instead
+        finally:
+            self.cache.free(rid)
+            for g, m in zip(self.cache.groups, marks):
+                g.pool.high_water = m
+        return done
 
     # ------------------------------------------------------------------ facts
     def memory_report(self) -> dict:

@@ -163,6 +163,34 @@ def test_first_tokens_and_long_decoding(models, dtype, tol):
         assert rows.shape[0] >= 230
 
 
+def test_decode_steps_of_every_batch_size_are_captured_when_the_engine_is_built(models):
+    """No capture happens in the middle of generation, whatever batch sizes the requests pass
+    through as they end one by one; an engine that captures at first use gives the same."""
+    from gollmgo_b200 import Engine, SamplingParams
+    from gollmgo_b200.engine.runner import GRAPH_BUCKETS
+    d, cfg, page, w = models["tiny_a"]
+    reqs = list(tt.random_requests(cfg["vocab_size"], [5, 9, 3, 11, 6], seed=9).values())
+    eng = Engine(d, dtype="bfloat16", block_size=page, num_blocks=32, max_batch_size=6, max_token_budget=64)
+    want = {b for b in GRAPH_BUCKETS if b <= 6}
+    assert {b for b, c in eng.runner._graphs.items() if c.graph is not None} == want
+    assert eng.runner.cache.free_pages() == 32 and not eng.runner.cache.requests
+    graphs = {b: c.graph for b, c in eng.runner._graphs.items()}
+    for i, r in enumerate(reqs):                               # different lengths: the batch shrinks step by step
+        eng.enqueue(r, SamplingParams(max_tokens=4 + 3 * i, ignore_eos=True), request_id=f"r{i}")
+    while eng.has_unfinished():
+        eng.step()
+    assert {b: c.graph for b, c in eng.runner._graphs.items()} == graphs
+    lazy = Engine(d, dtype="bfloat16", block_size=page, num_blocks=32, max_batch_size=6, max_token_budget=64,
+                  capture_at_start=False)
+    assert not lazy.runner._graphs
+    for i, r in enumerate(reqs):
+        lazy.enqueue(r, SamplingParams(max_tokens=4 + 3 * i, ignore_eos=True), request_id=f"r{i}")
+    while lazy.has_unfinished():
+        lazy.step()
+    for i in range(len(reqs)):
+        assert lazy.output_of(f"r{i}").token_ids == eng.output_of(f"r{i}").token_ids
+
+
 def test_small_pool_preempts_and_results_do_not_change(models):
     from gollmgo_b200 import Engine, SamplingParams
     d, cfg, page, w = models["tiny_a"]
