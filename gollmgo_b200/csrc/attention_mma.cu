@@ -184,25 +184,31 @@ __device__ __forceinline__ float ld_cluster_f32(unsigned local_addr, unsigned ra
 // query heads rotated into scratch (bfloat16, [16][D]), and, in the one CTA whose slice holds
 // the token's own position, k rotated and v copied into their place in the cache.  Half-split
 // pairs over the whole head.  Ends with a barrier: the CTA then sees q and the new k and v.
+// The table of cosines and sines depends only on the token's position (known before the
+// step began): decode_rope_table may run before the wait on the kernels ahead.
+template <int D>
+__device__ __forceinline__ void decode_rope_table(const AttnArgs& a, int t, unsigned char* scratch) {
+  float* cs = reinterpret_cast<float*>(scratch);
+  constexpr int half = D / 2;
+  const double pos = (double)a.rope_positions[t];
+  const double two_pi = 6.283185307179586476925286766559;
+  for (int p = threadIdx.x; p < half; p += MMA_THREADS) {
+    const double ang = pos * a.rope_inv_freq[p];
+    const float r = (float)(ang - two_pi * rint(ang * (1.0 / two_pi)));
+    float sn, c;
+    sincosf(r, &sn, &c);
+    cs[p] = c;
+    cs[half + p] = sn;
+  }
+}
+
 template <int D>
 __device__ __forceinline__ void decode_rope(const AttnArgs& a, int t, int kvh, int head0, int nrows, bool owner,
                                             unsigned char* scratch) {
   float* cs = reinterpret_cast<float*>(scratch);
   __nv_bfloat16* qs = reinterpret_cast<__nv_bfloat16*>(scratch + D * sizeof(float));
   constexpr int half = D / 2, per_head = half / 8;
-  {
-    const double pos = (double)a.rope_positions[t];
-    const double two_pi = 6.283185307179586476925286766559;
-    for (int p = threadIdx.x; p < half; p += MMA_THREADS) {
-      const double ang = pos * a.rope_inv_freq[p];
-      const float r = (float)(ang - two_pi * rint(ang * (1.0 / two_pi)));
-      float sn, c;
-      sincosf(r, &sn, &c);
-      cs[p] = c;
-      cs[half + p] = sn;
-    }
-  }
-  __syncthreads();
+  __syncthreads();                       // the table is complete
   const int slot = (owner && a.rope_write_cache && a.slot_mapping) ? a.slot_mapping[t] : -1;
   const int page = slot >= 0 ? slot / a.page_size : 0;
   const int off = slot >= 0 ? slot - page * a.page_size : 0;
@@ -281,6 +287,7 @@ __global__ void __launch_bounds__(MMA_THREADS, D == 128 ? 3 : 4) attn_decode_mma
   // ROPE: the last stage is free until the main loop starts filling it
   unsigned char* scratch = smem_raw + (STAGES - 1) * 2 * TILE_BYTES;
   const bool owner = lo <= ctx - 1 && ctx - 1 < hi;
+  if (ROPE && lo < hi) decode_rope_table<D>(a, t, scratch);
   if (!early) {
     pdl_wait();
     if (ROPE && lo < hi) decode_rope<D>(a, t, kvh, head0, nrows, owner, scratch);
