@@ -328,9 +328,13 @@ extern "C" int gg_attn_prefill(const void* q, long long q_stride, const void* kc
   a.page_size = page_size; a.window = window; a.scale = scale;
   int rc = check_common(a, "attn_prefill");
   if (rc) return rc;
-  if (allow_tc && tile128_seq && status && attn_tc_supported(dtype, d, page_size) && q_stride % 8 == 0) {
+  if (allow_tc && tile128_seq && status && q_stride % 8 == 0) {
     a.tile_seq = tile128_seq; a.tile_q0 = tile128_q0;
-    return attn_prefill_tc(a, num_tiles128, T, num_pages, status, stream);
+    // allow_tc: 1 = the best tcgen05 kernel for the shape, 2 = the one-head-per-CTA kernel only
+    if (allow_tc != 2 && attn_tc2_supported(dtype, d, page_size, nh, nkv))
+      return attn_prefill_tc2(a, num_tiles128, T, num_pages, status, stream);
+    if (attn_tc_supported(dtype, d, page_size))
+      return attn_prefill_tc(a, num_tiles128, T, num_pages, status, stream);
   }
   if (allow_mma && tile64_seq && attn_mma_supported(dtype, d) && q_stride % 8 == 0) {
     a.tile_seq = tile64_seq; a.tile_q0 = tile64_q0;

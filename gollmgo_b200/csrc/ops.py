@@ -147,7 +147,8 @@ def attn_prefill(q: torch.Tensor, q_stride: int, kcache: torch.Tensor, vcache: t
     """Causal attention of prompt portions over the paged cache.  ``tile_*`` list tiles
     of 16 queries (general kernel), ``tile64_*`` of 64 (mma.sync kernel: bfloat16, head
     size 64 or 128), ``tile128_*`` of 128 (tcgen05 kernel: bfloat16, head size 64 or 128); the
-    most specialised kernel whose list is given and that is allowed runs."""
+    most specialised kernel whose list is given and that is allowed runs.  ``allow_tc``: 2 =
+    only the tcgen05 kernel with one head per CTA, not the one with two heads of a kv head."""
     global tc_launched
     use_tc = allow_tc and tile128_seq is not None and kcache.dtype == torch.bfloat16 and d in (64, 128)
     if use_tc:
