@@ -405,6 +405,33 @@ extern "C" int gg_attn_decode_rope(const void* qkv, long long q_stride, void* kc
   return attn_merge_launch(a, dtype, n_dec, stream);
 }
 
+// Decode attention for large batches (bfloat16, head size 64 or 128): the work is cut into
+// equal ranges of tiles instead of whole slices (attention_mma.cu).  Scratch the caller
+// provides: pieces = n_dec * nkv * ceil((nh / nkv) / 16) + gg_attn_decode_flat_ctas(d);
+// part_o float[pieces * 16 * d], part_ml float[pieces * 16 * 2], prefix int[n_dec + 1].
+extern "C" int gg_attn_decode_flat(const void* q, long long q_stride, const void* kcache, const void* vcache,
+                                   int dtype, const int* block_tables, int bt_stride, const int* cu_q_lens,
+                                   const int* context_lens, const int* dec_seqs, int n_dec, float* part_o,
+                                   float* part_ml, int* prefix, void* out, int nh, int nkv, int d,
+                                   int page_size, int window, float scale, cudaStream_t stream) {
+  AttnArgs a = {};
+  a.q = q; a.q_stride = q_stride; a.kcache = kcache; a.vcache = vcache;
+  a.block_tables = block_tables; a.bt_stride = bt_stride; a.cu_q_lens = cu_q_lens;
+  a.context_lens = context_lens; a.out = out; a.nh = nh; a.nkv = nkv; a.d = d;
+  a.page_size = page_size; a.window = window; a.scale = scale;
+  a.dec_seqs = dec_seqs; a.num_splits = 0; a.part_o = part_o; a.part_ml = part_ml;
+  int rc = check_common(a, "attn_decode_flat");
+  if (rc) return rc;
+  GG_REQUIRE(n_dec >= 0, "attn_decode_flat: bad n_dec %d", n_dec);
+  GG_REQUIRE(part_o && part_ml && prefix, "attn_decode_flat: no scratch given");
+  GG_REQUIRE(attn_mma_supported(dtype, d) && q_stride % 2 == 0,
+             "attn_decode_flat: only bfloat16 with head size 64 or 128 (got dtype %d, head size %d)", dtype, d);
+  if (n_dec == 0) return GG_OK;
+  return attn_decode_flat(a, n_dec, prefix, stream);
+}
+
+extern "C" int gg_attn_decode_flat_ctas(int d) { return attn_decode_flat_ctas(d); }
+
 // Clusters of `splits` decode CTAs that the device holds at once for head size d in
 // bfloat16; 0 where gg_attn_decode would not use clusters for that count.
 extern "C" int gg_attn_decode_cluster_capacity(int dtype, int d, int splits) {

@@ -41,6 +41,9 @@ int attn_prefill_mma(const AttnArgs& a, int num_tiles, cudaStream_t stream);   /
 #define ATTN_MAX_CLUSTER 8       // slices of one token and kv head that can be one (portable) cluster
 int attn_decode_mma(const AttnArgs& a, int n_dec, cudaStream_t stream, bool* merged);
 int attn_decode_cluster_capacity(int d, int splits);
+// large batches: the tiles of all (token, kv head) pairs cut into equal ranges, one per CTA
+int attn_decode_flat_ctas(int d);
+int attn_decode_flat(const AttnArgs& a, int n_dec, int* prefix, cudaStream_t stream);
 // bfloat16 tcgen05 kernel for prompt portions, head size 128 (attention_tc.cu); tiles of 128 queries
 bool attn_tc_supported(int dtype, int d, int page_size);
 int attn_prefill_tc(const AttnArgs& a, int num_tiles, int T, int num_pages, int* status, cudaStream_t stream);

@@ -425,6 +425,260 @@ __global__ void __launch_bounds__(MMA_THREADS, D == 128 ? 3 : 4) attn_decode_mma
   }
 }
 
+// ---------------------------------------------------------------- decoded tokens, large batches
+// With more (token, kv head) pairs than CTAs fit at once, whole slices per CTA leave the
+// last round of CTAs mostly empty.  Here the tiles of 64 keys of all pairs form one sequence
+// (kv head chunk r outermost, then token, then tile), which is cut into gridDim.x equal
+// ranges; a CTA walks its range with one ring of stages that runs on across the borders
+// between pairs, and leaves one partial result (m, l, o of up to 16 heads) per pair it
+// touched.  Piece number = (r * n_dec + token index) + CTA index: both only grow along the
+// sequence, so the sum is unique, and attn_merge_flat_kernel finds a pair's pieces from the
+// same arithmetic.  part_o [pieces, 16, D], part_ml [pieces, 16, 2] (m in base 2);
+// prefix_out [n_dec + 1]: tiles before each token, written by CTA 0 for the merge kernel.
+#define FLAT_MAX_SEQS 1024
+
+struct FlatPos { int r, i, tt; };       // kv head chunk, decode entry, tile within the entry
+
+template <int D>
+__global__ void __launch_bounds__(MMA_THREADS, D == 128 ? 3 : 4)
+attn_decode_flat_kernel(AttnArgs a, int n_dec, int* __restrict__ prefix_out) {
+  extern __shared__ __align__(128) unsigned char smem_raw[];
+  __shared__ int pre[FLAT_MAX_SEQS + 1];
+  __shared__ float cm[64], cl[64];
+  constexpr int TILE_BYTES = MMA_BK * D * 2;
+  constexpr int STAGES = 2;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, c2 = (lane & 3) * 2;
+  const int ps_log2 = 31 - __clz(a.page_size);
+  const int G = a.nh / a.nkv, gchunks = (G + 15) / 16, R = a.nkv * gchunks;
+
+  // tiles of every entry (from the lists copied in before the step), then their prefix sums
+  for (int i = threadIdx.x; i < n_dec; i += MMA_THREADS) {
+    const int b = a.dec_seqs[i];
+    const int ctx = b >= 0 ? a.context_lens[b] : 0;
+    const int lo0 = a.window > 0 ? max(0, ctx - a.window) : 0;
+    pre[i + 1] = (ctx - lo0 + MMA_BK - 1) / MMA_BK;
+  }
+  if (threadIdx.x == 0) pre[0] = 0;
+  __syncthreads();
+  if (warp == 0) {
+    const int chunk = (n_dec + 31) / 32, s0 = lane * chunk, s1 = min(n_dec, s0 + chunk);
+    int sum = 0;
+    for (int i = s0; i < s1; ++i) sum += pre[i + 1];
+    int incl = sum;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int v = __shfl_up_sync(0xffffffffu, incl, o);
+      if (lane >= o) incl += v;
+    }
+    int run = incl - sum;
+    for (int i = s0; i < s1; ++i) { run += pre[i + 1]; pre[i + 1] = run; }
+  }
+  __syncthreads();
+  const int T_total = pre[n_dec];
+  const long long U = (long long)R * T_total;
+  const long long u_lo = (long long)blockIdx.x * U / gridDim.x, u_hi = (long long)(blockIdx.x + 1) * U / gridDim.x;
+  const int ntiles = (int)(u_hi - u_lo);
+  pdl_wait();
+  if (blockIdx.x == 0)
+    for (int i = threadIdx.x; i <= n_dec; i += MMA_THREADS) prefix_out[i] = pre[i];
+  if (ntiles > 0) {
+    auto advance = [&](FlatPos& p) {
+      if (++p.tt == pre[p.i + 1] - pre[p.i]) {
+        p.tt = 0;
+        do {
+          if (++p.i == n_dec) { p.i = 0; ++p.r; }
+        } while (pre[p.i + 1] == pre[p.i] && p.r < R);
+      }
+    };
+    FlatPos pp;                                            // where the range starts
+    {
+      pp.r = (int)(u_lo / T_total);
+      const int f = (int)(u_lo - (long long)pp.r * T_total);
+      int lo = 0, hi = n_dec;
+      while (hi - lo > 1) {
+        const int mid = (lo + hi) >> 1;
+        if (pre[mid] <= f) lo = mid; else hi = mid;
+      }
+      pp.i = lo;
+      pp.tt = f - pre[lo];
+    }
+    FlatPos cp = pp;
+    const unsigned base = smem_u32(smem_raw);
+    // what the producer knows about the entry it is in (looked up once per entry, not per tile)
+    int p_i = -1, p_ctx = 0, p_lo0 = 0;
+    const int* p_bt = nullptr;
+    auto load_tile = [&](const FlatPos& p, int st) {
+      if (p.i != p_i) {
+        const int b = a.dec_seqs[p.i];
+        p_i = p.i;
+        p_ctx = a.context_lens[b];
+        p_lo0 = a.window > 0 ? max(0, p_ctx - a.window) : 0;
+        p_bt = a.block_tables + (size_t)b * a.bt_stride;
+      }
+      load_kv_tile<D>(a, p_bt, p.r / gchunks, p_lo0 + p.tt * MMA_BK, p_lo0, p_ctx, base + st * 2 * TILE_BYTES,
+                      base + st * 2 * TILE_BYTES + TILE_BYTES, ps_log2);
+    };
+    load_tile(pp, 0);
+    cp_async_commit();
+    advance(pp);
+
+    float m[2], l[2];
+    float o[D / 8][4];
+    unsigned qf[D / 16][4];
+    int hi = 0, lo0 = 0, nrows = 0;
+    bool fresh = true;
+    const float sc = a.scale * LOG2E;
+    for (int it = 0; it < ntiles; ++it) {
+      if (it + 1 < ntiles) { load_tile(pp, (it + 1) % STAGES); advance(pp); }
+      cp_async_commit();
+      if (fresh) {
+        // a new (token, kv head chunk): its queries, an empty softmax state
+        const int b = a.dec_seqs[cp.i];
+        const int t = a.cu_q_lens[b];
+        hi = a.context_lens[b];
+        lo0 = a.window > 0 ? max(0, hi - a.window) : 0;
+        const int g0 = (cp.r % gchunks) * 16;
+        nrows = min(16, G - g0);
+        const __nv_bfloat16* qbase = (const __nv_bfloat16*)a.q + (size_t)t * a.q_stride + (size_t)((cp.r / gchunks) * G + g0) * D;
+        const int nr = nrows;
+        load_q_frags<D>(qf, [&](int r) { return r < nr ? qbase + (size_t)r * D : nullptr; });
+        m[0] = m[1] = -INFINITY;
+        l[0] = l[1] = 0.f;
+#pragma unroll
+        for (int nt = 0; nt < D / 8; ++nt) { o[nt][0] = o[nt][1] = o[nt][2] = o[nt][3] = 0.f; }
+        fresh = false;
+      }
+      cp_async_wait<STAGES - 1>();
+      __syncthreads();
+      const int st = it % STAGES;
+      const unsigned ks = base + st * 2 * TILE_BYTES, vs = ks + TILE_BYTES;
+      const int key0 = warp * 16;                        // this warp's 16 keys of the tile
+      const int tok0 = lo0 + cp.tt * MMA_BK + key0;
+      if (tok0 < hi) {
+        float s[2][4];
+        qk_mma<D, 2>(qf, ks, key0, s);
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+          const int tk = tok0 + j * 8 + c2;
+          s[j][0] = tk < hi ? s[j][0] * sc : -INFINITY;
+          s[j][2] = tk < hi ? s[j][2] * sc : -INFINITY;
+          s[j][1] = tk + 1 < hi ? s[j][1] * sc : -INFINITY;
+          s[j][3] = tk + 1 < hi ? s[j][3] * sc : -INFINITY;
+        }
+        unsigned p[1][4];
+        softmax_update<D, 2>(s, m, l, o, p);
+        pv_mma<D, 2>(p, vs, key0, o);
+      }
+      __syncthreads();
+      const bool last_of_entry = cp.tt + 1 == pre[cp.i + 1] - pre[cp.i];
+      if (last_of_entry || it + 1 == ntiles) {
+        // ---- this CTA's piece of the pair is complete: combine the four warps in the stage
+        // just used and leave the piece in global memory
+        l[0] += __shfl_xor_sync(0xffffffffu, l[0], 1);
+        l[0] += __shfl_xor_sync(0xffffffffu, l[0], 2);
+        l[1] += __shfl_xor_sync(0xffffffffu, l[1], 1);
+        l[1] += __shfl_xor_sync(0xffffffffu, l[1], 2);
+        float* co = reinterpret_cast<float*>(smem_raw + (size_t)st * 2 * TILE_BYTES);     // [4][16][D]
+        if ((lane & 3) == 0) {
+          cm[warp * 16 + g] = m[0]; cm[warp * 16 + g + 8] = m[1];
+          cl[warp * 16 + g] = l[0]; cl[warp * 16 + g + 8] = l[1];
+        }
+#pragma unroll
+        for (int nt = 0; nt < D / 8; ++nt) {
+          float* r0 = co + ((size_t)warp * 16 + g) * D + nt * 8 + c2;
+          float* r1 = co + ((size_t)warp * 16 + g + 8) * D + nt * 8 + c2;
+          r0[0] = o[nt][0]; r0[1] = o[nt][1];
+          r1[0] = o[nt][2]; r1[1] = o[nt][3];
+        }
+        __syncthreads();
+        const size_t piece = (size_t)cp.r * n_dec + cp.i + blockIdx.x;
+        for (int e = threadIdx.x; e < nrows * D; e += MMA_THREADS) {
+          const int r = e / D, col = e - r * D;
+          const float M = fmaxf(fmaxf(cm[r], cm[16 + r]), fmaxf(cm[32 + r], cm[48 + r]));
+          float L = 0.f, acc = 0.f;
+#pragma unroll
+          for (int w = 0; w < 4; ++w) {
+            const float mw = cm[w * 16 + r];
+            if (mw != -INFINITY) {
+              const float f = fast_exp2(mw - M);
+              L += f * cl[w * 16 + r];
+              acc += f * co[((size_t)w * 16 + r) * D + col];
+            }
+          }
+          a.part_o[(piece * 16 + r) * D + col] = acc;
+          if (col == 0) {
+            a.part_ml[(piece * 16 + r) * 2] = M;
+            a.part_ml[(piece * 16 + r) * 2 + 1] = L;
+          }
+        }
+        __syncthreads();
+        fresh = true;
+      }
+      advance(cp);
+    }
+    cp_async_wait<0>();
+  }
+  pdl_trigger();
+}
+
+// Merge of the pieces of attn_decode_flat_kernel: grid (n_dec, kv head chunks), a block merges
+// the up to 16 heads of its chunk.  A pair's tiles are positions [u0, u1) of the sequence; CTA
+// c took [c U / G, (c + 1) U / G), so it holds a piece of the pair iff its range is not empty
+// and c U < (u0 + 1) G ... (only products are compared; one division per block).
+__global__ void __launch_bounds__(128) attn_merge_flat_kernel(AttnArgs a, int n_dec, int num_ctas,
+                                                              const int* __restrict__ prefix) {
+  __shared__ int range_s[2];
+  pdl_trigger();
+  pdl_wait();
+  const int idx = blockIdx.x, r = blockIdx.y;
+  const int b = a.dec_seqs[idx];
+  if (b < 0) return;
+  const int d = a.d, G = a.nh / a.nkv, gchunks = (G + 15) / 16, R = a.nkv * gchunks;
+  const int kvh = r / gchunks, g0 = (r % gchunks) * 16, nrows = min(16, G - g0);
+  const int T_total = prefix[n_dec];
+  const long long U = (long long)R * T_total, Gc = num_ctas;
+  const long long u0 = (long long)r * T_total + prefix[idx], u1 = u0 + (prefix[idx + 1] - prefix[idx]);
+  __nv_bfloat16* out = (__nv_bfloat16*)a.out + (size_t)a.cu_q_lens[b] * a.nh * d + (size_t)(kvh * G + g0) * d;
+  if (u1 <= u0 || U <= 0) {
+    for (int e = threadIdx.x; e < nrows * d; e += blockDim.x) out[e] = __float2bfloat16_rn(0.f);
+    return;
+  }
+  if (threadIdx.x == 0) {
+    // the last CTA whose range starts at or before u: floor(c U / G) <= u  <=>  c U < (u + 1) G
+    auto last_start_le = [&](long long u) {
+      long long c = u * Gc / U;
+      while (c + 1 < Gc && (c + 1) * U < (u + 1) * Gc) ++c;
+      while (c > 0 && c * U >= (u + 1) * Gc) --c;
+      return (int)c;
+    };
+    range_s[0] = last_start_le(u0);
+    range_s[1] = last_start_le(u1 - 1);
+  }
+  __syncthreads();
+  const int c_first = range_s[0], c_last = range_s[1];
+  const size_t q = (size_t)r * n_dec + idx;
+  const bool gaps = U < Gc;           // fewer tiles than CTAs: CTAs in between may have had nothing to do
+  for (int e = threadIdx.x; e < nrows * d; e += blockDim.x) {
+    const int row = e / d, col = e - row * d;
+    float M = -INFINITY;
+    for (int c = c_first; c <= c_last; ++c) {
+      if (gaps && (c + 1) * U / Gc == c * U / Gc) continue;
+      M = fmaxf(M, a.part_ml[((q + c) * 16 + row) * 2]);
+    }
+    float L = 0.f, acc = 0.f;
+    for (int c = c_first; c <= c_last; ++c) {
+      if (gaps && (c + 1) * U / Gc == c * U / Gc) continue;
+      const float mc = a.part_ml[((q + c) * 16 + row) * 2];
+      if (mc != -INFINITY) {
+        const float f = fast_exp2(mc - M);
+        L += f * a.part_ml[((q + c) * 16 + row) * 2 + 1];
+        acc += f * a.part_o[((q + c) * 16 + row) * d + col];
+      }
+    }
+    out[(size_t)row * d + col] = __float2bfloat16_rn(L > 0.f ? acc / L : 0.f);
+  }
+}
+
 // ---------------------------------------------------------------- prompt portions
 template <int D>
 __global__ void __launch_bounds__(MMA_THREADS) attn_prefill_mma_kernel(AttnArgs a) {
@@ -638,4 +892,41 @@ int attn_prefill_mma(const AttnArgs& a, int num_tiles, cudaStream_t stream) {
     gg_launch(attn_prefill_mma_kernel<64>, dim3(grid), dim3(MMA_THREADS), smem, stream, a);
   }
   return gg_check_launch("attn_prefill_mma");
+}
+
+// CTAs the flat decode kernel is launched with (its whole grid is resident at once).
+int attn_decode_flat_ctas(int d) {
+  static int num_sms = 0;
+  if (!num_sms) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess ||
+        cudaDeviceGetAttribute(&num_sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || num_sms <= 0)
+      num_sms = 148;
+  }
+  return (d == 128 ? 3 : 4) * num_sms;
+}
+
+// Scratch: part_o float[(n_dec * nkv * ceil(G / 16) + CTAs) * 16 * d], part_ml float[(same) * 16 * 2],
+// prefix int[n_dec + 1].
+int attn_decode_flat(const AttnArgs& a, int n_dec, int* prefix, cudaStream_t stream) {
+  GG_REQUIRE(power_of_two(a.page_size), "attn_decode: page size %d is not a power of two", a.page_size);
+  GG_REQUIRE(n_dec <= FLAT_MAX_SEQS, "attn_decode: %d decoded tokens; the flat kernel takes at most %d", n_dec, FLAT_MAX_SEQS);
+  GG_REQUIRE(prefix != nullptr, "attn_decode: no prefix scratch given");
+  const int ctas = attn_decode_flat_ctas(a.d);
+  const size_t smem = decode_smem(a.d);
+  int rc;
+  cudaError_t e;
+  if (a.d == 128) {
+    if ((rc = opt_in_smem(attn_decode_flat_kernel<128>, smem, "attn_decode"))) return rc;
+    e = gg_launch(attn_decode_flat_kernel<128>, dim3(ctas), dim3(MMA_THREADS), smem, stream, a, n_dec, prefix);
+  } else {
+    e = gg_launch(attn_decode_flat_kernel<64>, dim3(ctas), dim3(MMA_THREADS), smem, stream, a, n_dec, prefix);
+  }
+  if (e != cudaSuccess) return gg_fail(GG_ERR_CUDA, "attn_decode_flat: launch: %s", cudaGetErrorString(e));
+  if ((rc = gg_check_launch("attn_decode_flat"))) return rc;
+  const int G = a.nh / a.nkv, R = a.nkv * ((G + 15) / 16);
+  GG_REQUIRE(R <= 65535, "attn_decode_flat: too many heads");
+  e = gg_launch(attn_merge_flat_kernel, dim3(n_dec, R), dim3(128), 0, stream, a, n_dec, ctas, (const int*)prefix);
+  if (e != cudaSuccess) return gg_fail(GG_ERR_CUDA, "attn_merge_flat: launch: %s", cudaGetErrorString(e));
+  return gg_check_launch("attn_merge_flat");
 }

@@ -113,6 +113,14 @@ def attn_decode(args) -> None:
                                         splits, po, pm, out, nh, nkv, d, page, 0, 1 / math.sqrt(d)), args.reps)
     print(f"attn_decode+merge B={B} context={ctx} heads={nh}/{nkv} d={d} splits={splits}: {t:7.1f} us "
           f"{B * seq_bytes / t / 1e6:5.2f} TB/s of cache", flush=True)
+    pieces = ops.attn_decode_flat_pieces(B, nh, nkv, d)
+    po = torch.empty(pieces * 16 * d, device="cuda")
+    pm = torch.empty(pieces * 16 * 2, device="cuda")
+    prefix = torch.empty(B + 1, dtype=torch.int32, device="cuda")
+    t = _time(lambda i: ops.attn_decode_flat(q, q.shape[1], kc, vc, bts[i % len(bts)], stride, cu, ctxs, dec, B,
+                                             po, pm, prefix, out, nh, nkv, d, page, 0, 1 / math.sqrt(d)), args.reps)
+    print(f"attn_decode_flat (equal ranges of tiles) B={B} context={ctx}: {t:7.1f} us "
+          f"{B * seq_bytes / t / 1e6:5.2f} TB/s of cache", flush=True)
 
 
 def attn_prefill(args) -> None:

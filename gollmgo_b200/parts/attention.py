@@ -26,6 +26,9 @@ from .registry import build_position, register_mixer
 ATTN_POLICY = os.environ.get("GOLLMGO_B200_ATTN", "auto")
 # Steps of decoded tokens only: rotation and cache write inside the decode attention kernel.
 FUSE_DECODE_ROPE = os.environ.get("GOLLMGO_B200_FUSE_ROPE", "1") != "0"
+# Decode steps with at least this many times more (token, kv head) pairs than CTAs fit at once
+# use the kernel that cuts all tiles into equal ranges (ops.attn_decode_flat); 0 = never.
+FLAT_DECODE_FILL = float(os.environ.get("GOLLMGO_B200_FLAT_DECODE_FILL", "1.0"))
 MAX_SPLITS = 16
 CTAS_PER_SM = 3            # decode attention CTAs resident on one SM (csrc/attention_mma.cu)
 ASSUMED_TILES = 32         # context the choice is tuned for: 32 tiles of 64 keys
@@ -99,6 +102,13 @@ class Attention:
                    for n in range(1, ctx.max_seqs + 1))
         ws.reserve("attn_part_o", rows * self.nh * self.d, torch.float32)
         ws.reserve("attn_part_ml", rows * self.nh * 2, torch.float32)
+        self._flat_ok = (ctx.device.type == "cuda" and ctx.act_dtype == torch.bfloat16 and self.d in (64, 128)
+                         and ATTN_POLICY != "general" and FLAT_DECODE_FILL > 0)
+        if self._flat_ok:
+            pieces = ops.attn_decode_flat_pieces(ctx.max_seqs, self.nh, self.nkv, self.d)
+            ws.reserve("attn_part_o", pieces * 16 * self.d, torch.float32)
+            ws.reserve("attn_part_ml", pieces * 16 * 2, torch.float32)
+            ws.reserve("attn_flat_prefix", ctx.max_seqs + 1, torch.int32)
         self.w_qkv = None
         self.w_o = None
 
@@ -135,7 +145,10 @@ class Attention:
             self.position.apply(qkv, batch, self.nh, self.nkv, self.d)
         # a step of decoded tokens only: the decode kernel rotates and writes the cache itself
         table = self.position.rope_table()
+        flat_step = (self._flat_ok and batch.num_decode * self._ctas_per_split
+                     >= FLAT_DECODE_FILL * CTAS_PER_SM * self.num_sms)
         fused = (FUSE_DECODE_ROPE and batch.num_decode > 0 and not batch.num_tiles and ATTN_POLICY != "general"
+                 and not flat_step
                  and not hasattr(self.position, "apply")
                  and ops.attn_decode_rope_ok(qkv.dtype, self.nh, self.nkv, self.d, table, self.position.interleaved))
         if not fused:
@@ -153,11 +166,23 @@ class Attention:
                              allow_mma=ATTN_POLICY != "general",
                              tile128_seq=batch.tile128_seq, tile128_q0=batch.tile128_q0,
                              num_tiles128=batch.num_tiles128, allow_tc=ATTN_POLICY == "auto")
-        if batch.num_decode:
+        if batch.num_decode and flat_step:
+            # more pairs than CTAs at once: equal ranges of tiles instead of whole slices
+            n = batch.num_decode
+            pieces = ops.attn_decode_flat_pieces(n, self.nh, self.nkv, self.d)
+            ops.attn_decode_flat(qkv, self.qkv_width, kc, vc, bt, batch.bt_stride, batch.cu_q_lens,
+                                 batch.context_lens, batch.dec_seqs, n,
+                                 ws.get("attn_part_o", 1, pieces * 16 * self.d),
+                                 ws.get("attn_part_ml", 1, pieces * 16 * 2),
+                                 ws.get("attn_flat_prefix", 1, n + 1), out, self.nh, self.nkv, self.d,
+                                 self.ctx.page_size, window, self.scale)
+        elif batch.num_decode:
             splits = decode_splits(batch.num_decode, self._ctas_per_split, self.num_sms, self._cluster_cap)
             part_o = ws.get("attn_part_o", 1, batch.num_decode * self.nh * splits * self.d)
             part_ml = ws.get("attn_part_ml", 1, batch.num_decode * self.nh * splits * 2)
-        if batch.num_decode and fused:
+        if batch.num_decode and flat_step:
+            pass
+        elif batch.num_decode and fused:
             ops.attn_decode_rope(qkv, kc, vc, bt, batch.bt_stride, batch.cu_q_lens, batch.context_lens,
                                  batch.dec_seqs, batch.num_decode, splits, part_o, part_ml, out, self.nh,
                                  self.nkv, self.d, self.ctx.page_size, window, self.scale, batch.positions,

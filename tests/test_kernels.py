@@ -224,6 +224,59 @@ def test_attn_decode(ops, cuda_device, dtype, nh, nkv, d, page, window, allow_mm
 
 
 @pytest.mark.parametrize("nh,nkv,d,page,window", [
+    (32, 8, 128, 16, 0), (24, 1, 64, 16, 0), (6, 2, 64, 8, 70), (40, 2, 128, 32, 0), (3, 3, 128, 16, 33)])
+@pytest.mark.parametrize("many", [False, True])
+def test_attn_decode_flat(ops, cuda_device, nh, nkv, d, page, window, many):
+    """The decode kernel for large batches cuts the tiles of all (token, kv head) pairs into
+    equal ranges, so a pair's keys may be spread over several CTAs and a CTA may hold the end
+    of one pair and the start of the next: contexts from one key to thousands, padding
+    entries in between, and (many) more pairs than CTAs."""
+    dtype = torch.bfloat16
+    torch.manual_seed(6)
+    ctxs = [1, 2, page - 1, page, page + 1, 63, 64, 65, 127, 129, 300, 777, 3000, 5001]
+    if many:
+        ctxs = ctxs + [70 + 13 * i for i in range(150)]
+    B = len(ctxs)
+    seqs, qs, refs = [], [], []
+    for i, ctx in enumerate(ctxs):
+        k, v = torch.randn(ctx, nkv, d, device="cuda"), torch.randn(ctx, nkv, d, device="cuda")
+        q = torch.randn(1, nh, d, device="cuda")
+        lo = max(0, ctx - window) if window else 0
+        far = [lo, min(ctx - 1, lo + 1), ctx - 1, (lo + ctx) // 2, max(lo, ctx - 65)][i % 5]
+        if ctx > 2000:
+            far = lo + 3
+        spike(q, k, v, i % nh, (i % nh) // (nh // nkv), far)
+        q, k, v = q.to(dtype), k.to(dtype), v.to(dtype)
+        seqs.append((k, v)), qs.append(q)
+        refs.append(ref_attention(q.float(), k.float(), v.float(), ctx - 1, window))
+    kc, vc, bt, stride = paged(seqs, page, sum(-(-c // page) for c in ctxs) + 5, nkv, d, dtype, 1)
+    q_all = torch.cat(qs).reshape(B, nh * d).contiguous()
+    cu = torch.arange(B + 1, dtype=torch.int32, device="cuda")
+    ctx_t = torch.tensor(ctxs, dtype=torch.int32, device="cuda")
+    order = list(range(B))
+    random.Random(2).shuffle(order)
+    order[3:3] = [-1]                                                   # padding in the middle and at the end
+    dec = torch.tensor(order + [-1, -1], dtype=torch.int32, device="cuda")
+    n_dec = len(order) + 2
+    pieces = ops.attn_decode_flat_pieces(n_dec, nh, nkv, d)
+    part_o = torch.full((pieces * 16 * d,), float("nan"), device="cuda")
+    part_ml = torch.full((pieces * 16 * 2,), float("nan"), device="cuda")
+    prefix = torch.full((n_dec + 1,), -7, dtype=torch.int32, device="cuda")
+    out = torch.zeros(B, nh * d, device="cuda", dtype=dtype)
+    ops.attn_decode_flat(q_all, nh * d, kc, vc, bt, stride, cu, ctx_t, dec, n_dec, part_o, part_ml, prefix,
+                         out, nh, nkv, d, page, window, 1 / math.sqrt(d))
+    ref = torch.cat(refs).reshape(B, nh * d)
+    torch.testing.assert_close(out.double(), ref, **tol(dtype))
+    # the same through the sliced kernel: equal up to the order of the sums
+    out2 = torch.zeros_like(out)
+    po = torch.empty(n_dec * nh * 3 * d, device="cuda")
+    pm = torch.empty(n_dec * nh * 3 * 2, device="cuda")
+    ops.attn_decode(q_all, nh * d, kc, vc, bt, stride, cu, ctx_t, dec, n_dec, 3, po, pm, out2,
+                    nh, nkv, d, page, window, 1 / math.sqrt(d))
+    torch.testing.assert_close(out.float(), out2.float(), rtol=2e-2, atol=2e-2)
+
+
+@pytest.mark.parametrize("nh,nkv,d,page,window", [
     (32, 8, 128, 16, 0), (24, 2, 64, 16, 0), (6, 2, 64, 8, 70), (16, 1, 128, 32, 0), (3, 3, 128, 16, 33)])
 def test_attn_decode_with_rotation_inside(ops, cuda_device, nh, nkv, d, page, window):
     """The decode kernel that rotates q and k and writes the cache itself gives, bit for bit,
