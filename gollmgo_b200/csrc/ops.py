@@ -365,6 +365,36 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, gated: bool = F
               _p(tc_status(x.device)), _stream()))
 
 
+MID_M = 64            # most tokens gemm_mid_m takes
+
+
+def mid_m_ok(x: torch.Tensor, w: torch.Tensor) -> bool:
+    """Whether out = x @ w^T can go through gemm_mid_m."""
+    return (x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.is_cuda
+            and 0 < x.shape[0] <= MID_M and x.shape[1] % 8 == 0 and x.stride(1) == 1
+            and x.stride(0) % 8 == 0 and w.is_contiguous())
+
+
+def gemm_mid_m(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, gated: bool = False) -> None:
+    """out[M, N] = x[M, K] @ w[N, K]^T for M <= 64 on tcgen05 with the operands swapped (rows
+    of w on the M side of the instruction, tokens on its N side) and K split over a
+    thread-block cluster; out bfloat16 or float32.  ``gated``: w is [2N, K] (gate rows, then
+    up rows) and out = silu(x Wg^T) * (x Wu^T) in bfloat16."""
+    M, K = x.shape
+    N = out.shape[1]
+    if w.shape != ((2 * N, K) if gated else (N, K)) or out.shape[0] != M or not out.is_contiguous():
+        raise KernelError("gemm_mid_m: shapes do not fit")
+    if gated and out.dtype != torch.bfloat16:
+        raise KernelError("gemm_mid_m: the gated product writes bfloat16")
+    if out.dtype not in (torch.float32, torch.bfloat16):
+        raise KernelError("gemm_mid_m: out must be bfloat16 or float32")
+    mode = 2 if gated else (1 if out.dtype == torch.float32 else 0)
+    global tc_launched
+    tc_launched = True
+    _check(lib().gg_gemm_mid_m(_p(x), ctypes.c_longlong(x.stride(0)), _p(w), _p(out), M, N, K, mode,
+                               _p(tc_status(x.device)), _stream()))
+
+
 def gemm_tc_withheld(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
     """Self-test of gemm_tc's bounded waits: launches it with its loads withheld.  The kernel
     gives up after about a second, sets the status word and returns (check_tc_status raises)."""

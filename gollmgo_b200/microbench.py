@@ -51,9 +51,15 @@ def gemm_small_m(args) -> None:
         x = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
         out = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
         lib_out = torch.empty(M, rows, device="cuda", dtype=torch.bfloat16)
-        own = _time(lambda i: ops.gemm_small_m(x, ws[i % copies], out, gated=gated), args.reps)
+        if M <= ops.SMALL_M:
+            kern = "gemm_small_m"
+            own = _time(lambda i: ops.gemm_small_m(x, ws[i % copies], out, gated=gated), args.reps)
+        else:
+            kern = "gemm_mid_m"
+            own = _time(lambda i: ops.gemm_mid_m(x, ws[i % copies], out, gated=gated), args.reps)
+            ops.check_tc_status("cuda")
         lib = _time(lambda i: torch.mm(x, ws[i % copies].t(), out=lib_out), args.reps)
-        print(f"gemm_small_m {name:13s} M={M:2d} N={N:6d} K={K:5d}: {own:7.1f} us {nbytes / own / 1e6:5.2f} TB/s"
+        print(f"{kern} {name:13s} M={M:2d} N={N:6d} K={K:5d}: {own:7.1f} us {nbytes / own / 1e6:5.2f} TB/s"
               f"   (vendor library: {lib:7.1f} us {nbytes / lib / 1e6:5.2f} TB/s)", flush=True)
         del ws
 

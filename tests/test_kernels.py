@@ -557,6 +557,42 @@ def test_gemm_small_m_with_norms_folded_in(ops, cuda_device, M, H, I):
     assert torch.equal(resid, resid2) and torch.equal(scaled, scaled2) and torch.equal(partials[:, :M], partials2[:, :M])
 
 
+@pytest.mark.parametrize("M", [1, 17, 32, 33, 50, 64])
+@pytest.mark.parametrize("N,K", [(48, 64), (100, 120), (4096, 4096), (1000, 14336 + 8), (6144, 4096), (130, 72)])
+def test_gemm_mid_m(ops, cuda_device, M, N, K):
+    g = torch.Generator(device="cuda").manual_seed(M * 7 + N)
+    x = torch.randn(M, K, device="cuda", generator=g).to(torch.bfloat16)
+    w = (torch.randn(N, K, device="cuda", generator=g) / math.sqrt(K)).to(torch.bfloat16)
+    ref = x.double() @ w.double().T
+    for dt in (torch.bfloat16, torch.float32):
+        out = torch.full((M, N), float("nan"), device="cuda", dtype=dt)
+        ops.gemm_mid_m(x, w, out)
+        ops.check_tc_status("cuda")
+        t = dict(rtol=1e-2, atol=1e-2) if dt == torch.bfloat16 else dict(rtol=1e-4, atol=1e-4)
+        torch.testing.assert_close(out.double(), ref, **t)
+    # x as rows of a wider buffer, as the engine's workspaces are
+    wide = torch.randn(M, K + 64, device="cuda", generator=g).to(torch.bfloat16)
+    out = torch.empty(M, N, device="cuda", dtype=torch.float32)
+    ops.gemm_mid_m(wide[:, :K], w, out)
+    torch.testing.assert_close(out.double(), wide[:, :K].double() @ w.double().T, rtol=1e-4, atol=1e-4)
+    ops.check_tc_status("cuda")
+
+
+@pytest.mark.parametrize("M", [17, 40, 64])
+@pytest.mark.parametrize("I,K", [(44, 64), (352, 128), (14336, 4096), (200, 72)])
+def test_gemm_mid_m_gated(ops, cuda_device, M, I, K):
+    g = torch.Generator(device="cuda").manual_seed(M + I)
+    x = torch.randn(M, K, device="cuda", generator=g).to(torch.bfloat16)
+    w = (torch.randn(2 * I, K, device="cuda", generator=g) * (2.0 / math.sqrt(K))).to(torch.bfloat16)
+    out = torch.full((M, I), float("nan"), device="cuda", dtype=torch.bfloat16)
+    ops.gemm_mid_m(x, w, out, gated=True)
+    ops.check_tc_status("cuda")
+    gu = x.float() @ w.float().T
+    gate, up = gu[:, :I], gu[:, I:]
+    ref = gate / (1 + torch.exp(-gate)) * up
+    torch.testing.assert_close(out.float(), ref.to(torch.bfloat16).float(), rtol=1e-2, atol=1e-2)
+
+
 def test_gemm_small_m_refuses_what_it_cannot_do(ops, cuda_device):
     x = torch.zeros(17, 64, device="cuda", dtype=torch.bfloat16)
     w = torch.zeros(32, 64, device="cuda", dtype=torch.bfloat16)
