@@ -18,6 +18,8 @@ from __future__ import annotations
 from dataclasses import dataclass, field
 from typing import Dict, List, Optional, Sequence, Tuple
 
+import numpy as np
+
 from .pool import OutOfPages, PagePool
 from .state_slots import StateSlots
 
@@ -69,6 +71,11 @@ class CacheManager:
         self.state_buffers: Dict[int, object] = {}
         self.slots = StateSlots(max_requests)
         self.requests: Dict[object, RequestCache] = {}
+        # flat mirrors for the native step packer (csrc/host_pack.cu): per group a table
+        # [state slot, logical page] of page ids (-1 = none), and the tokens cached per slot
+        self.max_requests = max_requests
+        self.tab: List[np.ndarray] = []
+        self.ntok = np.zeros(max_requests, dtype=np.int32)
         for cid, need in enumerate(needs):
             if need is None:
                 continue
@@ -85,6 +92,8 @@ class CacheManager:
                 self.state_needs[cid] = need
             else:
                 raise TypeError(f"cache need of entry {cid} is {type(need).__name__}")
+        self.tab = [np.full((max_requests, 64), -1, dtype=np.int32) for _ in self.groups]
+        self.any_window = any(g.need.window is not None for g in self.groups)
         if device is not None:
             import torch
             for g in self.groups:
@@ -117,6 +126,9 @@ class CacheManager:
             raise RuntimeError(f"request {req_id!r} is already admitted")
         slot = self.slots.take()
         self.requests[req_id] = RequestCache(slot, 0, [[] for _ in self.groups])
+        for t in self.tab:
+            t[slot, :] = -1
+        self.ntok[slot] = 0
         for buf in self.state_buffers.values():
             buf[slot].zero_()
         return slot
@@ -169,8 +181,34 @@ class CacheManager:
             rc.pages[gi].extend(g.pool.allocate(want - len(rc.pages[gi])))
             table = rc.pages[gi]
             slots.append([table[t // ps] * ps + t % ps for t in range(start, start + n_tokens)])
+            self._mirror(gi, rc)
         rc.num_tokens = start + n_tokens
+        self.ntok[rc.state_slot] = rc.num_tokens
         return Appended(start, slots)
+
+    def _mirror(self, gi: int, rc: RequestCache) -> None:
+        """Bring the flat table of group gi up to date with the request's pages."""
+        pages = rc.pages[gi]
+        t = self.tab[gi]
+        if len(pages) > t.shape[1]:
+            wider = np.full((self.max_requests, max(2 * t.shape[1], len(pages))), -1, dtype=np.int32)
+            wider[:, :t.shape[1]] = t
+            self.tab[gi] = t = wider
+        row = t[rc.state_slot]
+        row[:len(pages)] = pages
+        row[len(pages):] = -1
+
+    def append_one(self, req_id) -> int:
+        """append(req_id, 1) for the step packer: returns the position of the new token.  Where
+        the token lands in a page the request already holds (and no group has a window to
+        slide), nothing but the count changes."""
+        rc = self.requests[req_id]
+        start = rc.num_tokens
+        if self.any_window or start % self.page_size == 0:
+            return self.append(req_id, 1).start
+        rc.num_tokens = start + 1
+        self.ntok[rc.state_slot] = start + 1
+        return start
 
     def rollback(self, req_id, num_tokens: int) -> None:
         """Forget the tokens after the first ``num_tokens`` and give back the pages
@@ -184,7 +222,9 @@ class CacheManager:
                 page = rc.pages[gi].pop()
                 if page >= 0:
                     g.pool.release(page)
+            self._mirror(gi, rc)
         rc.num_tokens = num_tokens
+        self.ntok[rc.state_slot] = num_tokens
 
     def block_table(self, req_id, group: int) -> List[int]:
         return self.requests[req_id].pages[group]
@@ -199,6 +239,9 @@ class CacheManager:
             for page in rc.pages[gi]:
                 if page >= 0:
                     g.pool.release(page)
+        for t in self.tab:
+            t[rc.state_slot, :] = -1
+        self.ntok[rc.state_slot] = 0
         self.slots.give_back(rc.state_slot)
 
     # ------------------------------------------------------------------ checks
@@ -233,3 +276,15 @@ class CacheManager:
         slots = [rc.state_slot for rc in self.requests.values()]
         if len(set(slots)) != len(slots) or sorted(slots) != self.slots.held():
             raise AssertionError("state slots and requests disagree")
+        # the flat mirrors say the same as the requests, and nothing for slots nobody holds
+        for gi in range(len(self.groups)):
+            want = np.full_like(self.tab[gi], -1)
+            for rc in self.requests.values():
+                want[rc.state_slot, :len(rc.pages[gi])] = rc.pages[gi]
+            if not np.array_equal(want, self.tab[gi]):
+                raise AssertionError(f"group {gi}: the flat page table disagrees with the requests")
+        counts = np.zeros_like(self.ntok)
+        for rc in self.requests.values():
+            counts[rc.state_slot] = rc.num_tokens
+        if not np.array_equal(counts, self.ntok):
+            raise AssertionError("the flat token counts disagree with the requests")

@@ -405,6 +405,23 @@ def gemm_tc_withheld(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> Non
                                      _p(tc_status(x.device)), _stream()))
 
 
+def pack_decode_step(host, offsets, G: int, B: int, Bp: int, used: int, page_size: int, tokens, token_src,
+                     state_slots, context_after, tables) -> None:
+    """Fill the packed int32 step buffer ``host`` (a numpy view) for a step of single decoded
+    tokens: native code over flat numpy arrays (csrc/host_pack.cu).  ``offsets``: int32 array
+    of the buffer's array offsets, ``tables``: per group the cache manager's [state slot,
+    logical page] int32 table."""
+    import numpy as np
+    for a in (host, offsets, tokens, token_src, state_slots, context_after, *tables):
+        if a.dtype != np.int32 or not a.flags["C_CONTIGUOUS"]:
+            raise KernelError("pack_decode_step: arguments must be contiguous int32 arrays")
+    ptrs = (ctypes.c_void_p * max(G, 1))(*[t.ctypes.data for t in tables])
+    widths = (ctypes.c_int * max(G, 1))(*[t.shape[1] for t in tables])
+    vp = lambda a: ctypes.c_void_p(a.ctypes.data)
+    _check(lib().gg_pack_decode_step(vp(host), vp(offsets), G, B, Bp, used, page_size, vp(tokens), vp(token_src),
+                                     vp(state_slots), vp(context_after), ptrs, widths), 0)
+
+
 def argmax(logits: torch.Tensor, out: torch.Tensor) -> None:
     """out[r] = first index of the maximum of logits[r, :] (float32 [R, V])."""
     _cuda(logits, out)

@@ -9,6 +9,7 @@ pass; the device gets block tables, not per-token slot lists.
 """
 from __future__ import annotations
 
+import os
 from dataclasses import dataclass, field
 from typing import List, Optional, Sequence
 
@@ -117,6 +118,8 @@ class BatchBuilder:
         self._host = None
         self._dev = None
         self._copied = None
+        # steps of single decoded tokens are packed by native code (GOLLMGO_B200_NATIVE_PACK=0: by the general path)
+        self.native_decode = os.environ.get("GOLLMGO_B200_NATIVE_PACK", "1") != "0"
         self._ensure(capacity_ints)
 
     def _ensure(self, n: int) -> None:
@@ -128,11 +131,98 @@ class BatchBuilder:
         self._dev = torch.empty(n, dtype=torch.int32, device=self.device)
         self._copied = None
 
+    def _build_decode(self, entries, fixed_seqs, fixed_stride, static_dev) -> StepBatch:
+        """build() for a step in which every entry brings one token and wants its logits: the
+        per-sequence arrays are packed by native code (csrc/host_pack.cu) from the cache
+        manager's flat tables; the same layout and the same result as the general path."""
+        from ..csrc import ops
+        cache, ps, G = self.cache, self.cache.page_size, self.G
+        ids = [e.request_id for e in entries]
+        B = len(ids)
+        if len(set(ids)) != B:
+            raise ValueError("a request appears twice in one step")
+        starts: List[int] = []
+        try:
+            for rid in ids:
+                starts.append(cache.append_one(rid))
+        except Exception:
+            for rid, s0 in zip(ids, starts):           # all or nothing
+                cache.rollback(rid, s0)
+            raise
+        reqs = cache.requests
+        rcs = [reqs[rid] for rid in ids]
+        slots = [rc.state_slot for rc in rcs]
+        max_pages = max(len(p) for rc in rcs for p in rc.pages) if G else 1
+        Bp = fixed_seqs if fixed_seqs is not None else B
+        if Bp < B:
+            raise ValueError("more sequences than the fixed layout holds")
+        stride = fixed_stride if fixed_stride is not None else max(1, max_pages)
+        if stride < max_pages:
+            raise ValueError(f"a sequence holds {max_pages} pages, the fixed block table has {stride}")
+        lay = BatchLayout(Bp, Bp, Bp, 0, Bp, G, stride, 0, 0)
+        used = min(stride, max(1, max_pages))
+        hlay = lay if used == stride else BatchLayout(Bp, Bp, Bp, 0, Bp, G, used, 0, 0)
+        cuda = self.device.type == "cuda"
+        if static_dev is None:
+            self._ensure(lay.size)
+            if self._copied is not None:
+                self._copied.synchronize()
+            host = self._host
+        else:
+            host = torch.empty(hlay.size, dtype=torch.int32, pin_memory=cuda)
+        h = host.numpy()
+        h[:hlay.size] = 0
+        offsets = np.array([hlay.token_ids, hlay.token_src, hlay.positions, hlay.cu_q_lens, hlay.context_lens,
+                            hlay.state_slots, hlay.logit_rows, hlay.dec_seqs, *hlay.slot_mapping,
+                            *hlay.block_tables], dtype=np.int32)
+        srcs = [e.token_src for e in entries]
+        ops.pack_decode_step(h, offsets, G, B, Bp, used, ps,
+                             np.array([e.tokens[0] for e in entries], dtype=np.int32),
+                             np.array(srcs, dtype=np.int32), np.array(slots, dtype=np.int32),
+                             np.array([s0 + 1 for s0 in starts], dtype=np.int32), cache.tab)
+        dev = self._dev if static_dev is None else static_dev
+        if dev.numel() < lay.size:
+            raise ValueError("static batch buffer is too small for this layout")
+        if hlay is lay:
+            dev[:lay.size].copy_(host[:lay.size], non_blocking=cuda)
+        else:
+            head = lay.block_tables[0] if G else lay.size
+            dev[:head].copy_(host[:head], non_blocking=cuda)
+            for g in range(G):
+                src = host[hlay.block_tables[g]:hlay.block_tables[g] + Bp * used].view(Bp, used)
+                dev[lay.block_tables[g]:lay.block_tables[g] + Bp * stride].view(Bp, stride)[:, :used] \
+                    .copy_(src, non_blocking=cuda)
+        if cuda and static_dev is None:
+            self._copied = torch.cuda.Event()
+            self._copied.record()
+        sb = StepBatch()
+        sb.num_tokens, sb.num_seqs, sb.num_logit_rows = Bp, Bp, Bp
+        sb.num_tiles, sb.num_decode, sb.bt_stride = 0, Bp, stride
+        v = lambda off, n: dev[off:off + max(n, 1)]
+        sb.token_ids, sb.positions = v(lay.token_ids, Bp), v(lay.positions, Bp)
+        sb.token_src = v(lay.token_src, Bp) if (static_dev is not None or any(x >= 0 for x in srcs)) else None
+        sb.cu_q_lens, sb.context_lens = v(lay.cu_q_lens, Bp + 1), v(lay.context_lens, Bp)
+        sb.state_slots, sb.logit_rows = v(lay.state_slots, Bp), v(lay.logit_rows, Bp)[:Bp]
+        sb.tile_seq, sb.tile_q0 = v(lay.tile_seq, 0), v(lay.tile_q0, 0)
+        sb.tile64_seq, sb.tile64_q0, sb.num_tiles64 = v(lay.tile64_seq, 0), v(lay.tile64_q0, 0), 0
+        sb.tile128_seq, sb.tile128_q0, sb.num_tiles128 = v(lay.tile128_seq, 0), v(lay.tile128_q0, 0), 0
+        sb.dec_seqs = v(lay.dec_seqs, Bp)
+        sb.slot_mapping = [v(o, Bp) for o in lay.slot_mapping]
+        sb.block_tables = [v(o, Bp * stride) for o in lay.block_tables]
+        sb.request_ids, sb.q_lens, sb.q_starts = ids, [1] * B, starts
+        sb.state_slot_list = slots
+        sb.prev_tokens = None
+        sb.layout = lay
+        return sb
+
     def build(self, entries: Sequence[StepEntry], fixed_seqs: Optional[int] = None,
               fixed_stride: Optional[int] = None, static_dev: Optional[torch.Tensor] = None) -> StepBatch:
         cache, ps, G = self.cache, self.cache.page_size, self.G
         if not entries:
             raise ValueError("a step needs at least one entry")
+        if self.native_decode and self.device.type == "cuda" and \
+                all(len(e.tokens) == 1 and len(e.want) == 1 and e.want[0] == 0 for e in entries):
+            return self._build_decode(entries, fixed_seqs, fixed_stride, static_dev)
         ids = [e.request_id for e in entries]
         if len(set(ids)) != len(ids):
             raise ValueError("a request appears twice in one step")
