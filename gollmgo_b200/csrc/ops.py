@@ -212,6 +212,9 @@ def attn_decode_rope(qkv: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tens
                                      int(write_cache), _stream()), 2)
 
 
+ATTN_FLAT_MAX_SEQS = 1024   # decoded tokens attn_decode_flat takes in one launch (FLAT_MAX_SEQS in attention_mma.cu)
+
+
 def attn_decode_flat_ctas(d: int) -> int:
     """CTAs that attn_decode_flat launches for head size d (for sizing its scratch)."""
     return int(lib().gg_attn_decode_flat_ctas(d))

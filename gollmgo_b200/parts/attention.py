@@ -103,7 +103,8 @@ class Attention:
         ws.reserve("attn_part_o", rows * self.nh * self.d, torch.float32)
         ws.reserve("attn_part_ml", rows * self.nh * 2, torch.float32)
         self._flat_ok = (ctx.device.type == "cuda" and ctx.act_dtype == torch.bfloat16 and self.d in (64, 128)
-                         and ATTN_POLICY != "general" and FLAT_DECODE_FILL > 0)
+                         and ATTN_POLICY != "general" and FLAT_DECODE_FILL > 0
+                         and ctx.max_seqs <= ops.ATTN_FLAT_MAX_SEQS)
         if self._flat_ok:
             pieces = ops.attn_decode_flat_pieces(ctx.max_seqs, self.nh, self.nkv, self.d)
             ws.reserve("attn_part_o", pieces * 16 * self.d, torch.float32)
