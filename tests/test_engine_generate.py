@@ -163,6 +163,49 @@ def test_first_tokens_and_long_decoding(models, dtype, tol):
         assert rows.shape[0] >= 230
 
 
+@pytest.mark.parametrize("name", ["tiny_d", "tiny_e"])
+def test_decode_kernel_for_large_batches_inside_the_engine(tmp_path, cuda_device, monkeypatch, name):
+    """The decode attention that cuts all tiles into equal ranges is chosen when a step has more
+    (token, kv head) pairs than CTAs fit at once; with the threshold lowered it runs for every
+    decode step of a tiny model (head sizes 64 and 128, one with a window): every logit row of
+    long decoding against the whole sequence, as with the sliced kernel."""
+    import importlib
+    A = importlib.import_module("gollmgo_b200.parts.attention")
+    monkeypatch.setattr(A, "FLAT_DECODE_FILL", 1e-6)
+    from gollmgo_b200.config import EngineConfig
+    from gollmgo_b200.engine.batch import StepEntry
+    from gollmgo_b200.engine.runner import load_runner
+    cfg, page, std, jitter = tiny_configs.get(name)
+    d = tt.model_folder(str(tmp_path), name, cfg, seed=31, std=std, jitter=jitter, dtype="bfloat16")
+    w = tt.load_weights(d)
+    runner = load_runner(d, EngineConfig(dtype="bfloat16", block_size=page, num_blocks=96, max_batch_size=4,
+                                         max_token_budget=64, max_model_len=256))
+    assert runner.model.blocks[0].mixer._flat_ok
+    seqs = tt.random_requests(cfg["vocab_size"], [150, 97, 131], seed=8)
+    refs = tt.plain_logits(w, cfg, seqs)
+    names = list(seqs)
+    first = {n: 3 + 5 * i for i, n in enumerate(names)}
+    got = {n: [] for n in names}
+    out = runner.step([StepEntry(n, seqs[n][:first[n]], range(first[n])) for n in names]).cpu().double()
+    i = 0
+    for n in names:
+        got[n].append(out[i:i + first[n]])
+        i += first[n]
+    for t in range(1, 150):
+        step = [n for n in names if first[n] + t - 1 < len(seqs[n])]
+        if not step:
+            break
+        out = runner.step([StepEntry(n, [seqs[n][first[n] + t - 1]], [0]) for n in step]).cpu().double()
+        for j, n in enumerate(step):
+            got[n].append(out[j:j + 1])
+    for n in names:
+        rows = torch.cat(got[n])
+        ref = refs[n][:rows.shape[0]]
+        err = ((rows - ref).abs().amax(dim=1) / ref.abs().amax(dim=1)).max()
+        assert float(err) <= 6e-2, f"{n}: worst relative error {float(err):.2e}"
+        assert rows.shape[0] == len(seqs[n])
+
+
 def test_decode_steps_of_every_batch_size_are_captured_when_the_engine_is_built(models):
     """No capture happens in the middle of generation, whatever batch sizes the requests pass
     through as they end one by one; an engine that captures at first use gives the same."""
