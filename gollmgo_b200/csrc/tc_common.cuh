@@ -19,6 +19,16 @@ __device__ __forceinline__ void mbar_expect_tx(unsigned bar, unsigned bytes) {
 }
 // Bounded wait for the phase with the given parity.  False if it ran out.
 __device__ __forceinline__ bool mbar_wait(unsigned bar, unsigned parity) {
+  {
+    // the phase is often complete already: ask once without offering to be suspended
+    unsigned done;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.b32 %0, 1, 0, p;\n\t}"
+        : "=r"(done) : "r"(bar), "r"(parity) : "memory");
+    if (done) return true;
+  }
   for (unsigned spin = 0; spin < TC_SPIN_LIMIT; ++spin) {
     unsigned done;
     asm volatile(
