@@ -91,32 +91,100 @@ __global__ void argmax_kernel(const float* __restrict__ logits, int V, int* __re
 // with key > K weigh less than `target` and those with key >= K weigh at least
 // `target`.  weight(i) = 1 (count mode, the k-th largest) or exp((x_i - m) * invT)
 // (mass mode).  Only elements with key >= floor_key take part.
+// Logits crowd into a few values of the leading byte, so one shared histogram with atomics
+// serialises (a millisecond per row at a vocabulary of 128 k).  Every warp keeps a histogram
+// of its own instead: the lanes that fall into the same bin are found by comparison with a
+// leader's bin, their weights are summed by the warp, and the leader adds the sum without an
+// atomic; the warps' histograms are then added in warp order.  The sums therefore have a
+// fixed order and the result is the same on every run.
 template <bool MASS>
 __device__ unsigned int radix_threshold(const float* row, int V, float m, float invT,
-                                        unsigned int floor_key, float target, float* hist) {
+                                        unsigned int floor_key, float target, float* hist,
+                                        float (*whist)[256]) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
   unsigned int prefix = 0, pmask = 0;
   float above = 0.f;       // weight of keys strictly above the current prefix range
+  // In the first pass every element takes part and the bins of small values hold nearly all of
+  // them, though the threshold is almost always within the three bins at and below the
+  // maximum's.  So the first pass only bins those (`low_bin` = the lowest bin looked at); if
+  // their weight does not reach the target, the pass is repeated over all bins.
+  int low_bin = max(0, (int)(ordered_key(m) >> 24) - 2);
   for (int shift = 24; shift >= 0; shift -= 8) {
-    for (int i = threadIdx.x; i < 256; i += blockDim.x) hist[i] = 0.f;
+    if (shift != 24) low_bin = 0;
+    for (int i = lane; i < 256; i += 32) whist[warp][i] = 0.f;
+    __syncwarp();
+    // one element of every lane: the lanes of a bin are found by comparison with a leader's
+    auto consume = [&](float x, bool valid) {
+      int bin = -1;
+      float w = 0.f;
+      if (valid) {
+        const unsigned int k = ordered_key(x);
+        if (k >= floor_key && (k & pmask) == prefix && (int)((k >> shift) & 255u) >= low_bin) {
+          bin = (int)((k >> shift) & 255u);
+          w = MASS ? expf((x - m) * invT) : 1.f;
+        }
+      }
+      unsigned todo = __ballot_sync(0xffffffffu, bin >= 0);
+      while (todo) {
+        const int leader = __ffs(todo) - 1;
+        const int b = __shfl_sync(0xffffffffu, bin, leader);
+        const bool mine = bin == b;
+        const float sum = warp_sum(mine ? w : 0.f);
+        if (lane == leader) whist[warp][b] += sum;
+        todo &= ~__ballot_sync(0xffffffffu, mine);
+      }
+    };
+    // four values per load where the row allows it: a quarter as many trips to L2 in a loop
+    // whose votes keep the loads from overlapping
+    const int V4 = (((size_t)row) & 15) == 0 ? V >> 2 : 0;
+    const float4* row4 = reinterpret_cast<const float4*>(row);
+    for (int i0 = 0; i0 < V4; i0 += 4 * blockDim.x) {
+      float4 v[4];
+      bool valid[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {            // four loads in flight before the first vote
+        const int i = i0 + u * blockDim.x + threadIdx.x;
+        valid[u] = i < V4;
+        v[u] = valid[u] ? row4[i] : make_float4(0.f, 0.f, 0.f, 0.f);
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        consume(v[u].x, valid[u]);
+        consume(v[u].y, valid[u]);
+        consume(v[u].z, valid[u]);
+        consume(v[u].w, valid[u]);
+      }
+    }
+    for (int i0 = V4 << 2; i0 < V; i0 += blockDim.x) {
+      const int i = i0 + threadIdx.x;
+      consume(i < V ? row[i] : 0.f, i < V);
+    }
     __syncthreads();
-    for (int i = threadIdx.x; i < V; i += blockDim.x) {
-      const float x = row[i];
-      const unsigned int k = ordered_key(x);
-      if (k >= floor_key && (k & pmask) == prefix)
-        atomicAdd(&hist[(k >> shift) & 255u], MASS ? expf((x - m) * invT) : 1.f);
+    for (int i = threadIdx.x; i < 256; i += blockDim.x) {
+      float v = 0.f;
+      for (int wv = 0; wv < nw; ++wv) v += whist[wv][i];
+      hist[i] = v;
     }
     __syncthreads();
     if (threadIdx.x == 0) {
       float cum = above;
       int bin = 255;
-      for (; bin > 0; --bin) {
+      for (; bin > low_bin; --bin) {
         if (cum + hist[bin] >= target) break;
         cum += hist[bin];
       }
+      // stopped at the lowest bin looked at without reaching the target: the bins below count too
+      const bool again = low_bin > 0 && bin == low_bin && cum + hist[bin] < target;
       hist[256] = cum;
-      hist[257] = __int_as_float(bin);
+      hist[257] = __int_as_float(again ? -1 : bin);
     }
     __syncthreads();
+    if (__float_as_int(hist[257]) < 0) {       // the same pass again over all bins
+      __syncthreads();
+      low_bin = 0;
+      shift += 8;
+      continue;
+    }
     above = hist[256];
     const unsigned int bin = (unsigned int)__float_as_int(hist[257]);
     prefix |= bin << shift;
@@ -134,6 +202,7 @@ sample_kernel(const float* __restrict__ logits, int V, const float* __restrict__
   __shared__ float red_f[33];
   __shared__ int red_i[33];
   __shared__ float hist[258];
+  __shared__ float whist[SAMPLE_THREADS / 32][256];       // a histogram per warp (radix_threshold)
   __shared__ float scan[SAMPLE_THREADS / 32 + 1];
   __shared__ int found;
   pdl_trigger();
@@ -150,7 +219,7 @@ sample_kernel(const float* __restrict__ logits, int V, const float* __restrict__
   const float invT = 1.f / T;
   unsigned int floor_key = 0;
   const int k = top_k ? top_k[r] : 0;
-  if (k > 0 && k < V) floor_key = radix_threshold<false>(row, V, m, invT, 0u, (float)k, hist);
+  if (k > 0 && k < V) floor_key = radix_threshold<false>(row, V, m, invT, 0u, (float)k, hist, whist);
   const float p = top_p ? top_p[r] : 0.f;
   if (p > 0.f && p < 1.f) {
     float z = 0.f;
@@ -159,7 +228,7 @@ sample_kernel(const float* __restrict__ logits, int V, const float* __restrict__
       if (ordered_key(x) >= floor_key) z += expf((x - m) * invT);
     }
     z = block_sum(z, red_f);
-    floor_key = radix_threshold<true>(row, V, m, invT, floor_key, p * z, hist);
+    floor_key = radix_threshold<true>(row, V, m, invT, floor_key, p * z, hist, whist);
   }
   // running sum in index order over the kept elements; thread owns a contiguous chunk
   const int chunk = (V + blockDim.x - 1) / blockDim.x;
