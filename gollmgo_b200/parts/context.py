@@ -18,6 +18,7 @@ class Workspace:
         self.device = device
         self._want: Dict[str, Tuple[int, torch.dtype]] = {}
         self._bufs: Dict[str, torch.Tensor] = {}
+        self._views: Dict[Tuple[str, int, int], torch.Tensor] = {}
 
     def reserve(self, name: str, numel: int, dtype: torch.dtype) -> None:
         old = self._want.get(name)
@@ -26,9 +27,15 @@ class Workspace:
         self._want[name] = (max(numel, old[0] if old else 0), dtype)
         if name in self._bufs and self._bufs[name].numel() < self._want[name][0]:
             del self._bufs[name]
+            self._views = {k: v for k, v in self._views.items() if k[0] != name}
 
     def get(self, name: str, rows: int, cols: int) -> torch.Tensor:
-        """View [rows, cols] of the named buffer."""
+        """View [rows, cols] of the named buffer (views are kept: a step asks for the same few
+        again and again, and making one costs microseconds of host time)."""
+        key = (name, rows, cols)
+        view = self._views.get(key)
+        if view is not None:
+            return view
         buf = self._bufs.get(name)
         if buf is None:
             numel, dtype = self._want[name]
@@ -37,7 +44,11 @@ class Workspace:
         n = rows * cols
         if n > buf.numel():
             raise ValueError(f"workspace buffer {name!r} holds {buf.numel()} elements, {n} asked")
-        return buf[:n].view(rows, cols)
+        view = buf[:n].view(rows, cols)
+        if len(self._views) > 4096:
+            self._views.clear()
+        self._views[key] = view
+        return view
 
     def nbytes(self) -> int:
         return sum(n * torch.empty((), dtype=dt).element_size() for n, dt in self._want.values())
