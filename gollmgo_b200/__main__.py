@@ -285,14 +285,34 @@ def cmd_doctor(argv) -> int:
     return 0 if ok else 1
 
 
+def cmd_replay(argv) -> int:
+    """Trace replay (the same as bin/trace_run): steps as JSON lines on standard input, logits at
+    the wanted places to <out>/<step>.f32, `done <step>` after every step."""
+    ap = argparse.ArgumentParser(prog="python -m gollmgo_b200 replay")
+    ap.add_argument("--model", required=True, help="folder with config.json and model.safetensors")
+    ap.add_argument("--dtype", required=True, choices=["bfloat16", "float32"])
+    ap.add_argument("--out", required=True, help="folder for <step>.f32 files")
+    ap.add_argument("--max-tokens", type=int, required=True,
+                    help="most tokens live requests hold at any time (each rounded up to 64)")
+    ap.add_argument("--block-size", type=int, default=16, help="tokens per cache page")
+    ap.add_argument("--no-cuda-graphs", action="store_true")
+    args = ap.parse_args(argv)
+    from .engine.trace import make_trace_runner, replay
+    runner = make_trace_runner(args.model, args.dtype, args.max_tokens, args.block_size,
+                               cuda_graphs=not args.no_cuda_graphs)
+    replay(runner, sys.stdin, args.out)
+    return 0
+
+
 def main(argv=None) -> int:
     argv = list(sys.argv[1:] if argv is None else argv)
-    cmds = {"generate": cmd_generate, "bench": cmd_bench, "doctor": cmd_doctor}
+    cmds = {"generate": cmd_generate, "bench": cmd_bench, "doctor": cmd_doctor, "replay": cmd_replay}
     if not argv or argv[0] in ("-h", "--help") or argv[0] not in cmds:
         print("usage: python -m gollmgo_b200 <command> [flags]\n\ncommands:\n"
               "  generate  generate tokens for prompts given as token ids\n"
               "  bench     run synthetic prompts through the engine and print a result JSON\n"
-              "  doctor    check the toolchain, the device and the kernel library\n",
+              "  doctor    check the toolchain, the device and the kernel library\n"
+              "  replay    feed given token ids step by step (JSON lines on stdin) and write logits\n",
               file=sys.stderr)
         return 0 if argv and argv[0] in ("-h", "--help") else 1
     return cmds[argv[0]](argv[1:])

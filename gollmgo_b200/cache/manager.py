@@ -15,6 +15,7 @@ no state), kernels/gollmgo_kvcache.cu:11-63 (device layout [layer][slot][head][d
 """
 from __future__ import annotations
 
+import os
 from dataclasses import dataclass, field
 from typing import Dict, List, Optional, Sequence, Tuple
 
@@ -74,6 +75,7 @@ class CacheManager:
         # flat mirrors for the native step packer (csrc/host_pack.cu): per group a table
         # [state slot, logical page] of page ids (-1 = none), and the tokens cached per slot
         self.max_requests = max_requests
+        self.poison_freed = os.environ.get("GOLLMGO_B200_POISON_FREED", "0") == "1"
         self.tab: List[np.ndarray] = []
         self.ntok = np.zeros(max_requests, dtype=np.int32)
         for cid, need in enumerate(needs):
@@ -119,6 +121,16 @@ class CacheManager:
         gi, idx = self.group_of[cache_id]
         g = self.groups[gi]
         return g.kv[idx, 0], g.kv[idx, 1], gi
+
+    def _give_back(self, gi: int, page: int) -> None:
+        """Return a page of group gi to its pool.  With GOLLMGO_B200_POISON_FREED=1 its keys and
+        values are overwritten with NaN on the device first (in stream order, so after every
+        step launched so far): a kernel that read a page its request no longer holds would
+        then show up as NaN logits."""
+        g = self.groups[gi]
+        if self.poison_freed and g.kv is not None:
+            g.kv[:, :, page] = float("nan")
+        g.pool.release(page)
 
     # ------------------------------------------------------------------ requests
     def admit(self, req_id) -> int:
@@ -175,7 +187,7 @@ class CacheManager:
         slots = []
         for gi, g in enumerate(self.groups):
             for idx in self._behind_window(rc, gi):
-                g.pool.release(rc.pages[gi][idx])
+                self._give_back(gi, rc.pages[gi][idx])
                 rc.pages[gi][idx] = -1
             want = -(-(start + n_tokens) // ps)
             rc.pages[gi].extend(g.pool.allocate(want - len(rc.pages[gi])))
@@ -221,7 +233,7 @@ class CacheManager:
             while len(rc.pages[gi]) > keep:
                 page = rc.pages[gi].pop()
                 if page >= 0:
-                    g.pool.release(page)
+                    self._give_back(gi, page)
             self._mirror(gi, rc)
         rc.num_tokens = num_tokens
         self.ntok[rc.state_slot] = num_tokens
@@ -238,7 +250,7 @@ class CacheManager:
         for gi, g in enumerate(self.groups):
             for page in rc.pages[gi]:
                 if page >= 0:
-                    g.pool.release(page)
+                    self._give_back(gi, page)
         for t in self.tab:
             t[rc.state_slot, :] = -1
         self.ntok[rc.state_slot] = 0

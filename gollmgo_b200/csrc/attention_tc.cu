@@ -225,6 +225,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     const unsigned tmem_o = lane_addr + 256 + sub * OC;
     const float sc = a.scale * ATC_LOG2E;
     float m_ref = -INFINITY, l = 0.f;
+    const int stale_hi = (hi + ps - 1) / ps * ps;        // end of the last page that is fetched
     bool ok = true;
     for (int j = 0; j < ntiles; ++j) {
       const int s = j & 1;
@@ -286,6 +287,24 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             tc_store32(tmem_o + c, v);
           }
           tc_wait_store();
+        }
+      }
+      // The last page of the last tile may hold rows past the context: whatever the page's
+      // owner before left there.  Their P is zero, but zero times a NaN or an infinity is not:
+      // those rows of V are cleared before the product reads them (the product waits for
+      // every softmax warp's arrival on p_full).
+      if (j == ntiles - 1 && stale_hi > ctx) {
+        ok = softmax_all(mbar_wait(v_full0 + 8 * s, (j >> 1) & 1) && !*(volatile int*)&abort_s);
+        if (!ok) break;
+        const int tile0 = kstart + j * ATC_BK;
+        const int z0 = max(ctx, tile0) - tile0, z1 = min(stale_hi, tile0 + ATC_BK) - tile0;
+        if (r >= z0 && r < z1) {
+          for (int hf = sub; hf < D / 64; hf += 2) {
+            const unsigned row = v_smem + s * ATC_TILE_BYTES + hf * ATC_HALF_BYTES + (unsigned)r * 128;
+#pragma unroll
+            for (int c = 0; c < 128; c += 16)
+              asm volatile("st.shared.v4.b32 [%0], {%1, %1, %1, %1};" ::"r"(row + c), "r"(0u) : "memory");
+          }
         }
       }
       // p = 2^(s - m_ref), row sum, P to shared memory (bf16, swizzled K-major): this thread's

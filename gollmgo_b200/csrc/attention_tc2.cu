@@ -239,6 +239,7 @@ attn_prefill_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
     const unsigned my_p = p_smem + t * AT2_P_BYTES + (unsigned)r * 128;
     const float sc = a.scale * AT2_LOG2E;
     float m_ref = -INFINITY, l = 0.f;
+    const int stale_hi = (hi + ps - 1) / ps * ps;        // end of the last page that is fetched
     bool ok = true;
     for (int j = 0; j < ntiles; ++j) {
       const int s = j & 1;
@@ -299,6 +300,25 @@ attn_prefill_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
             tc_store32(tmem_o + c, v);
           }
           tc_wait_store();
+        }
+      }
+      // The last page of the last tile may hold rows past the context: whatever the page's
+      // owner before left there.  Their P is zero, but zero times a NaN or an infinity is not:
+      // those rows of V are cleared before the product reads them (by each head's own warps,
+      // whose arrival on p_full the product waits for).
+      if (j == ntiles - 1 && stale_hi > ctx) {
+        ok = mbar_wait(v_full0 + 8 * s, (j >> 1) & 1) && !*(volatile int*)&abort_s;
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        const int z0 = max(ctx, kb) - kb, z1 = min(stale_hi, kb + AT2_BK) - kb;
+        if (r >= z0 && r < z1) {
+#pragma unroll
+          for (int hf = 0; hf < HALVES; ++hf) {
+            const unsigned row = v_smem + s * KV_BYTES + hf * AT2_KHALF + (unsigned)r * 128;
+#pragma unroll
+            for (int c = 0; c < 128; c += 16)
+              asm volatile("st.shared.v4.b32 [%0], {%1, %1, %1, %1};" ::"r"(row + c), "r"(0u) : "memory");
+          }
         }
       }
       // The exponentials of the two heads take turns (head 0 first in every step): the special

@@ -37,3 +37,26 @@ def test_replay_matches_plain(tmp_path, cuda_device, name, dtype):
     worst = tt.compare(trace, out, reference, config["vocab_size"], TOL[dtype])
     print(f"{name} {dtype}: {len(trace.steps)} steps, pool {trace.peak} tokens "
           f"(single-request peak {peak_single}), worst relative error {worst:.2e}")
+
+
+@pytest.mark.parametrize("name,dtype", [("tiny_b", "bfloat16"), ("tiny_c", "bfloat16"), ("tiny_e", "bfloat16"),
+                                        ("tiny_c", "float32")])
+def test_pages_given_back_are_never_read(tmp_path, cuda_device, name, dtype):
+    """The mixed trace on a small pool with every page overwritten by NaN the moment it is given
+    back (finished requests, pages behind a window): a kernel that read a page its request no
+    longer holds, or beyond a request's context inside a page, would produce NaN logits."""
+    import os
+    config, page, std, jitter = tiny_configs.get(name)
+    model_dir = tt.model_folder(str(tmp_path), name, config, seed=12, std=std, jitter=jitter,
+                                dtype="float32" if dtype == "float32" else "bfloat16")
+    weights = tt.load_weights(model_dir)
+    requests = tt.random_requests(config["vocab_size"], LENGTHS[name], seed=6)
+    reference = tt.plain_logits(weights, config, requests)
+    trace = tt.Trace()
+    tt.mixed(trace, requests, max_live=4, seed=7)
+    tt.portions(trace, requests)
+    tt.mixed(trace, dict(reversed(list(requests.items()))), max_live=3, seed=8, tag="n")
+    out = str(tmp_path / "out")
+    env = dict(os.environ, GOLLMGO_B200_POISON_FREED="1")
+    tt.run_trace(model_dir, dtype, trace, out, block_size=page, env=env)
+    tt.compare(trace, out, reference, config["vocab_size"], TOL[dtype])
