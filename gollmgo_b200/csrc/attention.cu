@@ -433,8 +433,9 @@ extern "C" int gg_attn_decode_flat(const void* q, long long q_stride, const void
 extern "C" int gg_attn_decode_flat_ctas(int d) { return attn_decode_flat_ctas(d); }
 
 // Clusters of `splits` decode CTAs that the device holds at once for head size d in
-// bfloat16; 0 where gg_attn_decode would not use clusters for that count.
-extern "C" int gg_attn_decode_cluster_capacity(int dtype, int d, int splits) {
+// bfloat16 with `group` query heads to a kv head; 0 where gg_attn_decode would not use
+// clusters for that count.
+extern "C" int gg_attn_decode_cluster_capacity(int dtype, int d, int splits, int group) {
   if (!attn_mma_supported(dtype, d)) return 0;
-  return attn_decode_cluster_capacity(d, splits);
+  return attn_decode_cluster_capacity(d, splits, group);
 }

@@ -40,7 +40,7 @@ bool attn_mma_supported(int dtype, int d);
 int attn_prefill_mma(const AttnArgs& a, int num_tiles, cudaStream_t stream);   // tiles of 64 queries
 #define ATTN_MAX_CLUSTER 8       // slices of one token and kv head that can be one (portable) cluster
 int attn_decode_mma(const AttnArgs& a, int n_dec, cudaStream_t stream, bool* merged);
-int attn_decode_cluster_capacity(int d, int splits);
+int attn_decode_cluster_capacity(int d, int splits, int group);
 // large batches: the tiles of all (token, kv head) pairs cut into equal ranges, one per CTA
 int attn_decode_flat_ctas(int d);
 int attn_decode_flat(const AttnArgs& a, int n_dec, int* prefix, cudaStream_t stream);

@@ -169,6 +169,16 @@ __device__ __forceinline__ void load_q_frags(unsigned (*qf)[4], F qrow) {
 __device__ __forceinline__ void cluster_barrier() {
   asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
+__device__ __forceinline__ void cluster_arrive_relaxed() { asm volatile("barrier.cluster.arrive.relaxed.aligned;" ::: "memory"); }
+__device__ __forceinline__ void cluster_wait() { asm volatile("barrier.cluster.wait.aligned;" ::: "memory"); }
+// v into the same shared-memory address of CTA `rank` of the cluster
+__device__ __forceinline__ void st_cluster_f32(unsigned local_addr, unsigned rank, float v) {
+  asm volatile(
+      "{\n\t.reg .b32 ra;\n\t"
+      "mapa.shared::cluster.u32 ra, %0, %1;\n\t"
+      "st.shared::cluster.f32 [ra], %2;\n\t}"
+      :: "r"(local_addr), "r"(rank), "f"(v) : "memory");
+}
 __device__ __forceinline__ float ld_cluster_f32(unsigned local_addr, unsigned rank) {
   float v;
   asm volatile(
@@ -246,6 +256,17 @@ __device__ __forceinline__ void decode_rope(const AttnArgs& a, int t, int kvh, i
 template <int D, int STAGES, bool CLUSTER, bool ROPE>
 __global__ void __launch_bounds__(MMA_THREADS, D == 128 ? 3 : 4) attn_decode_mma_kernel(AttnArgs a) {
   extern __shared__ __align__(128) unsigned char smem_raw[];
+  // The merge's inbox, behind the ring: every slice of the cluster leaves its share of the
+  // result here (and its row maxima and sums with everybody), so a CTA merges from its own
+  // shared memory.  A place of its own: neighbours write it while this CTA may still be in
+  // its loop.  Sized for the rows there are (decode_inbox_bytes): what a CTA holds in shared
+  // memory decides whether the next kernel's CTAs can settle beside it and fetch their
+  // weights while this one finishes.
+  float* rx_ml = reinterpret_cast<float*>(smem_raw + STAGES * 2 * MMA_BK * D * 2);   // [slices][16][2]
+  float* rx_o = rx_ml + ATTN_MAX_CLUSTER * 32;                                     // [slices][per]
+  // nobody may write a neighbour's shared memory before that neighbour runs: everybody
+  // arrives here, and waits for the others only just before the first such write
+  if (CLUSTER) cluster_arrive_relaxed();
   constexpr int TILE_BYTES = MMA_BK * D * 2;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, c2 = (lane & 3) * 2;
   // The lists that say what this CTA works on were copied in before the step began, and
@@ -283,31 +304,33 @@ __global__ void __launch_bounds__(MMA_THREADS, D == 128 ? 3 : 4) attn_decode_mma
     for (int i = threadIdx.x; i < n_pg; i += MMA_THREADS) bt_s[i] = __ldg(btg + i);
     __syncthreads();
   }
-  const bool early = lo < hi && lo + (STAGES - 1) * MMA_BK <= ctx - 1;
   // ROPE: the last stage is free until the main loop starts filling it
   unsigned char* scratch = smem_raw + (STAGES - 1) * 2 * TILE_BYTES;
   const bool owner = lo <= ctx - 1 && ctx - 1 < hi;
   if (ROPE && lo < hi) decode_rope_table<D>(a, t, scratch);
-  if (!early) {
-    pdl_wait();
-    if (ROPE && lo < hi) decode_rope<D>(a, t, kvh, head0, nrows, owner, scratch);
+  const int* bt = bt_local ? bt_s - pg_first : a.block_tables + (size_t)b * a.bt_stride;
+  const unsigned base = smem_u32(smem_raw);
+  const int ntiles = lo < hi ? (hi - lo + MMA_BK - 1) / MMA_BK : 0;
+  auto load_tile = [&](int i, int st) {
+    if (bt_local) load_kv_tile<D, true>(a, bt, kvh, lo + i * MMA_BK, lo, hi, base + st * 2 * TILE_BYTES, base + st * 2 * TILE_BYTES + TILE_BYTES, ps_log2);
+    else load_kv_tile<D, false>(a, bt, kvh, lo + i * MMA_BK, lo, hi, base + st * 2 * TILE_BYTES, base + st * 2 * TILE_BYTES + TILE_BYTES, ps_log2);
+  };
+  // the tiles that end before the key this step wrote (position ctx - 1) can be fetched
+  // before the kernels ahead have finished: as many of them as the ring holds
+  const int pre = lo < hi ? min(STAGES - 1, (ctx - 1 - lo) / MMA_BK) : 0;
+#pragma unroll
+  for (int s = 0; s < STAGES - 1; ++s) {
+    if (s < pre) { load_tile(s, s); cp_async_commit(); }
   }
+  pdl_wait();
+  if (ROPE && lo < hi) decode_rope<D>(a, t, kvh, head0, nrows, owner, scratch);
   if (lo < hi) {
-    const int* bt = bt_local ? bt_s - pg_first : a.block_tables + (size_t)b * a.bt_stride;
-    const unsigned base = smem_u32(smem_raw);
-    const int ntiles = (hi - lo + MMA_BK - 1) / MMA_BK;
-    auto load_tile = [&](int i, int st) {
-      if (bt_local) load_kv_tile<D, true>(a, bt, kvh, lo + i * MMA_BK, lo, hi, base + st * 2 * TILE_BYTES, base + st * 2 * TILE_BYTES + TILE_BYTES, ps_log2);
-      else load_kv_tile<D, false>(a, bt, kvh, lo + i * MMA_BK, lo, hi, base + st * 2 * TILE_BYTES, base + st * 2 * TILE_BYTES + TILE_BYTES, ps_log2);
-    };
 #pragma unroll
     for (int s = 0; s < STAGES - 1; ++s) {
-      if (s < ntiles) load_tile(s, s);
-      cp_async_commit();
-    }
-    if (early) {
-      pdl_wait();
-      if (ROPE) decode_rope<D>(a, t, kvh, head0, nrows, owner, scratch);
+      if (s >= pre) {
+        if (s < ntiles) load_tile(s, s);
+        cp_async_commit();
+      }
     }
     unsigned qf[D / 16][4];
     const __nv_bfloat16* qbase = ROPE ? reinterpret_cast<const __nv_bfloat16*>(scratch + D * sizeof(float))
@@ -353,9 +376,6 @@ __global__ void __launch_bounds__(MMA_THREADS, D == 128 ? 3 : 4) attn_decode_mma
   float* cm = reinterpret_cast<float*>(smem_raw);          // [4][16]
   float* cl = cm + 64;                                     // [4][16]
   float* co = cl + 64;                                     // [4][16][D]
-  float* fm = co + 4 * 16 * D;                             // the slice's result: [16] maxima,
-  float* fl = fm + 16;                                     // [16] sums,
-  float* fo = fl + 16;                                     // [16][D] weighted values
   __syncthreads();
   if ((lane & 3) == 0) {
     cm[warp * 16 + g] = m[0]; cm[warp * 16 + g + 8] = m[1];
@@ -369,7 +389,12 @@ __global__ void __launch_bounds__(MMA_THREADS, D == 128 ? 3 : 4) attn_decode_mma
     r1[0] = o[nt][2]; r1[1] = o[nt][3];
   }
   __syncthreads();
-  for (int e = threadIdx.x; e < nrows * D; e += MMA_THREADS) {
+  // CLUSTER: CTA s of the cluster merges elements [s * per, (s + 1) * per) of the rows; a
+  // slice sends each of its elements to the CTA that merges it
+  const int elems = nrows * D, per = ((elems / 2 + S - 1) / S) * 2;
+  const unsigned rx_o_a = smem_u32(rx_o), rx_ml_a = smem_u32(rx_ml);
+  if (CLUSTER) cluster_wait();
+  for (int e = threadIdx.x; e < elems; e += MMA_THREADS) {
     const int r = e / D, col = e - r * D;
     float M = fmaxf(fmaxf(cm[r], cm[16 + r]), fmaxf(cm[32 + r], cm[48 + r]));
     float L = 0.f, acc = 0.f;
@@ -383,8 +408,12 @@ __global__ void __launch_bounds__(MMA_THREADS, D == 128 ? 3 : 4) attn_decode_mma
       }
     }
     if (CLUSTER) {
-      fo[r * D + col] = acc;
-      if (col == 0) { fm[r] = M; fl[r] = L; }
+      const int dest = e / per;
+      st_cluster_f32(rx_o_a + (unsigned)(split * per + e - dest * per) * 4, dest, acc);
+      if (col < S) {                     // threads col = 0 .. S-1 of the row: one neighbour each
+        st_cluster_f32(rx_ml_a + (unsigned)(split * 32 + r * 2) * 4, col, M);
+        st_cluster_f32(rx_ml_a + (unsigned)(split * 32 + r * 2 + 1) * 4, col, L);
+      }
     } else {
       const size_t row = ((size_t)blockIdx.x * a.nh + head0 + r) * S + split;
       a.part_o[row * D + col] = acc;
@@ -396,32 +425,35 @@ __global__ void __launch_bounds__(MMA_THREADS, D == 128 ? 3 : 4) attn_decode_mma
     }
   }
   if (CLUSTER) {
-    // every CTA of the cluster merges its share of the (row, column pair)s from all slices
+    // after this barrier every slice's numbers are in the inbox, and nobody touches a
+    // neighbour's shared memory again: a CTA finishes on its own
     cluster_barrier();
     if (b >= 0) {
-      const int pairs = nrows * D / 2, per = (pairs + S - 1) / S;
-      const unsigned fm_a = smem_u32(fm), fl_a = smem_u32(fl), fo_a = smem_u32(fo);
       __nv_bfloat16* out = (__nv_bfloat16*)a.out + (size_t)t * a.nh * D + (size_t)head0 * D;
-      for (int p = split * per + threadIdx.x; p < min(pairs, (split + 1) * per); p += MMA_THREADS) {
-        const int r = (2 * p) / D, col = 2 * p - r * D;
+      for (int i = 2 * threadIdx.x; i < per && split * per + i < elems; i += 2 * MMA_THREADS) {
+        const int e = split * per + i, r = e / D, col = e - r * D;
         float M = -INFINITY;
-        for (int s = 0; s < S; ++s) M = fmaxf(M, ld_cluster_f32(fm_a + r * 4, s));
+#pragma unroll
+        for (int s = 0; s < ATTN_MAX_CLUSTER; ++s)
+          if (s < S) M = fmaxf(M, rx_ml[s * 32 + r * 2]);
         float L = 0.f, o0 = 0.f, o1 = 0.f;
-        for (int s = 0; s < S; ++s) {
-          const float ms = ld_cluster_f32(fm_a + r * 4, s);
-          if (ms != -INFINITY) {
-            const float f = fast_exp2(ms - M);
-            L += f * ld_cluster_f32(fl_a + r * 4, s);
-            o0 += f * ld_cluster_f32(fo_a + (r * D + col) * 4, s);
-            o1 += f * ld_cluster_f32(fo_a + (r * D + col + 1) * 4, s);
+#pragma unroll
+        for (int s = 0; s < ATTN_MAX_CLUSTER; ++s) {
+          if (s < S) {
+            const float ms = rx_ml[s * 32 + r * 2];
+            if (ms != -INFINITY) {
+              const float f = fast_exp2(ms - M);
+              const float2 v = *reinterpret_cast<const float2*>(rx_o + s * per + i);
+              L += f * rx_ml[s * 32 + r * 2 + 1];
+              o0 += f * v.x;
+              o1 += f * v.y;
+            }
           }
         }
         const float inv = L > 0.f ? 1.f / L : 0.f;
         *reinterpret_cast<unsigned*>(out + (size_t)r * D + col) = pack_bf16(o0 * inv, o1 * inv);
       }
     }
-    // nobody leaves while a neighbour may still read its shared memory
-    cluster_barrier();
   }
 }
 
@@ -814,31 +846,41 @@ static cudaError_t launch_clustered(K kernel, dim3 grid, size_t smem, int cluste
 }
 
 #define DECODE_STAGES 2
-static size_t decode_smem(int d) { return (size_t)DECODE_STAGES * 2 * MMA_BK * d * 2; }   // 64 KB at d = 128: 3 CTAs per SM
+// The ring: 64 KB at d = 128, three CTAs per SM.  (A ring of six stages with one CTA per SM
+// for launches that do not fill the device was measured: the attention itself no faster,
+// the step slower, because the next kernel's CTAs found no room beside it.)
+static size_t decode_ring_bytes(int d) { return (size_t)DECODE_STAGES * 2 * MMA_BK * d * 2; }
+// The inbox of the merge through the cluster: maxima and sums of every slice, and this
+// CTA's share of every slice's rows.
+static size_t decode_inbox_bytes(int d, int rows) { return (size_t)(ATTN_MAX_CLUSTER * 32 + rows * d + 2 * ATTN_MAX_CLUSTER) * sizeof(float); }
+
+template <int D>
+static int decode_cluster_capacity_of(int splits, int rows) {
+  int n = 0;
+  AttnArgs a = {};
+  const size_t smem = decode_ring_bytes(D) + decode_inbox_bytes(D, rows);
+  cudaError_t e = cudaSuccess;
+  if (smem > 48 * 1024)
+    e = cudaFuncSetAttribute(attn_decode_mma_kernel<D, DECODE_STAGES, true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  if (e == cudaSuccess)
+    e = launch_clustered(attn_decode_mma_kernel<D, DECODE_STAGES, true, false>, dim3(1, 1, splits), smem, splits, 0, a, &n);
+  if (e != cudaSuccess) { cudaGetLastError(); n = 0; }
+  return n;
+}
 
 // How many clusters of `splits` decode CTAs the device holds at once (0: such clusters
-// cannot be launched).  Asked once per head size and cluster size.
-int attn_decode_cluster_capacity(int d, int splits) {
-  static int cache[2][ATTN_MAX_CLUSTER + 1];
-  static bool known[2][ATTN_MAX_CLUSTER + 1];
-  if ((d != 64 && d != 128) || splits < 1 || splits > ATTN_MAX_CLUSTER) return 0;
-  const int di = d == 128;
-  if (!known[di][splits]) {
-    int n = 0;
-    AttnArgs a = {};
-    cudaError_t e;
-    if (d == 128) {
-      e = cudaFuncSetAttribute(attn_decode_mma_kernel<128, DECODE_STAGES, true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)decode_smem(128));
-      if (e == cudaSuccess)
-        e = launch_clustered(attn_decode_mma_kernel<128, DECODE_STAGES, true, false>, dim3(1, 1, splits), decode_smem(128), splits, 0, a, &n);
-    } else {
-      e = launch_clustered(attn_decode_mma_kernel<64, DECODE_STAGES, true, false>, dim3(1, 1, splits), decode_smem(64), splits, 0, a, &n);
-    }
-    if (e != cudaSuccess) { cudaGetLastError(); n = 0; }
-    cache[di][splits] = n;
-    known[di][splits] = true;
+// cannot be launched), with `group` query heads to a kv head (they size the merge's inbox).
+// Asked once per head size, cluster size and inbox size.
+int attn_decode_cluster_capacity(int d, int splits, int group) {
+  static int cache[2][17][ATTN_MAX_CLUSTER + 1];
+  static bool known[2][17][ATTN_MAX_CLUSTER + 1];
+  if ((d != 64 && d != 128) || splits < 1 || splits > ATTN_MAX_CLUSTER || group < 1) return 0;
+  const int di = d == 128, rows = group < 16 ? group : 16;
+  if (!known[di][rows][splits]) {
+    cache[di][rows][splits] = d == 128 ? decode_cluster_capacity_of<128>(splits, rows) : decode_cluster_capacity_of<64>(splits, rows);
+    known[di][rows][splits] = true;
   }
-  return cache[di][splits];
+  return cache[di][rows][splits];
 }
 
 // *merged is set when the kernel wrote the final output itself (no merge kernel needed).
@@ -847,9 +889,9 @@ int attn_decode_mma(const AttnArgs& a, int n_dec, cudaStream_t stream, bool* mer
   const int G = a.nh / a.nkv, gchunks = (G + 15) / 16;
   GG_REQUIRE(a.nkv * gchunks <= 65535, "attn_decode: too many heads");
   dim3 grid(n_dec, a.nkv * gchunks, a.num_splits);
-  const size_t smem = decode_smem(a.d);
-  const bool cluster = merged && a.num_splits <= ATTN_MAX_CLUSTER && attn_decode_cluster_capacity(a.d, a.num_splits) > 0;
+  const bool cluster = merged && a.num_splits <= ATTN_MAX_CLUSTER && attn_decode_cluster_capacity(a.d, a.num_splits, G) > 0;
   if (merged) *merged = cluster;
+  const size_t smem = decode_ring_bytes(a.d) + (cluster ? decode_inbox_bytes(a.d, G < 16 ? G : 16) : 0);
   const bool rope = a.rope_inv_freq != nullptr;
   if (rope) {
     GG_REQUIRE(gchunks == 1, "attn_decode: the fused rotation takes at most 16 heads per kv head, not %d", G);
@@ -913,7 +955,7 @@ int attn_decode_flat(const AttnArgs& a, int n_dec, int* prefix, cudaStream_t str
   GG_REQUIRE(n_dec <= FLAT_MAX_SEQS, "attn_decode: %d decoded tokens; the flat kernel takes at most %d", n_dec, FLAT_MAX_SEQS);
   GG_REQUIRE(prefix != nullptr, "attn_decode: no prefix scratch given");
   const int ctas = attn_decode_flat_ctas(a.d);
-  const size_t smem = decode_smem(a.d);
+  const size_t smem = decode_ring_bytes(a.d);
   int rc;
   cudaError_t e;
   if (a.d == 128) {

@@ -257,12 +257,12 @@ def attn_decode_flat(q: torch.Tensor, q_stride: int, kcache: torch.Tensor, vcach
 ATTN_MAX_CLUSTER = 8  # largest count of slices that the decode kernel merges inside a cluster
 
 
-def attn_decode_cluster_capacity(dtype: torch.dtype, d: int, splits: int) -> int:
-    """Clusters of `splits` decode CTAs the device holds at once; 0 where attn_decode
-    merges with a kernel of its own instead."""
+def attn_decode_cluster_capacity(dtype: torch.dtype, d: int, splits: int, group: int) -> int:
+    """Clusters of `splits` decode CTAs the device holds at once, with `group` query heads
+    to a kv head; 0 where attn_decode merges with a kernel of its own instead."""
     if dtype not in (torch.bfloat16, torch.float32):
         return 0
-    return int(lib().gg_attn_decode_cluster_capacity(dtype_code(dtype), d, splits))
+    return int(lib().gg_attn_decode_cluster_capacity(dtype_code(dtype), d, splits, group))
 
 
 SMALL_M = 16          # most tokens gemm_small_m takes

@@ -110,7 +110,7 @@ def attn_decode(args) -> None:
     out = torch.empty(B, nh * d, device="cuda", dtype=torch.bfloat16)
     bts = [tables[i:i + B].contiguous() for i in range(0, n_seqs, B)]
     sms = torch.cuda.get_device_properties(0).multi_processor_count
-    cap = [0] + [ops.attn_decode_cluster_capacity(torch.bfloat16, d, s) for s in range(1, ops.ATTN_MAX_CLUSTER + 1)]
+    cap = [0] + [ops.attn_decode_cluster_capacity(torch.bfloat16, d, s, nh // nkv) for s in range(1, ops.ATTN_MAX_CLUSTER + 1)]
     print("clusters of s slices held at once:", cap[1:])
     splits = args.splits or decode_splits(B, nkv * -(-(nh // nkv) // 16), sms, cap)
     po = torch.empty(B * nh * splits * d, device="cuda")

@@ -96,7 +96,7 @@ class Attention:
         self._ctas_per_split = self.nkv * gchunks
         self._cluster_cap = None
         if ctx.device.type == "cuda":
-            self._cluster_cap = [0] + [ops.attn_decode_cluster_capacity(ctx.act_dtype, self.d, s)
+            self._cluster_cap = [0] + [ops.attn_decode_cluster_capacity(ctx.act_dtype, self.d, s, self.nh // self.nkv)
                                        for s in range(1, ops.ATTN_MAX_CLUSTER + 1)]
         rows = max(n * decode_splits(n, self._ctas_per_split, self.num_sms, self._cluster_cap)
                    for n in range(1, ctx.max_seqs + 1))
