@@ -43,10 +43,28 @@ TC_MIN_TOKENS = 1024     # below this the tcgen05 kernel has too few tiles to fi
 # Llama-3.1-8B shape: 2.7 % faster than the vendor library at 24 tokens, level at 32, 3 %
 # slower at 64 (its 224 row slabs of the gated product fill 296 places unevenly).
 MID_M_TOKENS = int(os.environ.get("GOLLMGO_B200_GEMM_MID_TOKENS", "32"))
+# Up to MID_M_SPLIT_TOKENS tokens it still takes the products with so few rows of W that it
+# splits K eight ways over a cluster (the o and down products of that shape: 12.6 and 25.9 us
+# against the library's 15.5 and 27.0 at 64 tokens).
+MID_M_SPLIT_TOKENS = int(os.environ.get("GOLLMGO_B200_GEMM_MID_SPLIT_TOKENS", "64"))
+_NUM_SMS = {}
+
+
+def _num_sms(device) -> int:
+    n = _NUM_SMS.get(device)
+    if n is None:
+        n = _NUM_SMS[device] = torch.cuda.get_device_properties(device).multi_processor_count
+    return n
 
 
 def use_mid_m(x: torch.Tensor, w: torch.Tensor) -> bool:
-    return GEMM_POLICY != "lib" and x.shape[0] <= MID_M_TOKENS and ops.mid_m_ok(x, w)
+    if GEMM_POLICY == "lib":
+        return False
+    T = x.shape[0]
+    if T > MID_M_TOKENS and not (T <= MID_M_SPLIT_TOKENS and x.is_cuda
+                                 and -(-w.shape[0] // 128) * 8 <= 2 * _num_sms(x.device)):
+        return False
+    return ops.mid_m_ok(x, w)
 
 
 def use_tc(x: torch.Tensor, w: torch.Tensor, out_cols: int, gated: bool) -> bool:
