@@ -30,6 +30,7 @@ FUSE_DECODE_ROPE = os.environ.get("GOLLMGO_B200_FUSE_ROPE", "1") != "0"
 # use the kernel that cuts all tiles into equal ranges (ops.attn_decode_flat); 0 = never.
 FLAT_DECODE_FILL = float(os.environ.get("GOLLMGO_B200_FLAT_DECODE_FILL", "1.0"))
 MAX_SPLITS = 16
+FORCED_SPLITS = int(os.environ.get("GOLLMGO_B200_DECODE_SPLITS", "0"))   # for measurements: this count, whatever the batch
 CTAS_PER_SM = 3            # decode attention CTAs resident on one SM (csrc/attention_mma.cu)
 ASSUMED_TILES = 32         # context the choice is tuned for: 32 tiles of 64 keys
 # The cost of a count of slices, in units of the time a CTA takes for one tile when it does
@@ -40,9 +41,11 @@ PER_SLICE = 0.3            # what every further slice adds (barriers, partial re
 WAVE_PENALTY = 4           # every further round of CTAs or clusters, beyond its tiles
 BANDWIDTH_TILE = 0.003     # a tile's share of the memory bandwidth: no count of slices gets below
                            # tiles x this, however many CTAs work at once
-CLUSTER_FILL = 0.9         # share of the cluster capacity to count on: clusters are placed while the kernel
-                           # before still drains, and a launch that needs every last place often waits for a
-                           # second round (measured: a quarter of the launches, 11 us each)
+CLUSTER_FILL = 0.9         # share of the cluster capacity that one round can count on: clusters are placed
+                           # while the kernel before still drains, and a launch that needs every last place
+                           # often waits for a second round (measured: a quarter of the launches, 11 us each).
+                           # A launch of several rounds anyway fills every place (batch 32: three slices in
+                           # two rounds, 52.8 us a layer, against 61.1 for whole contexts on 256 of 444 places)
 
 
 def decode_splits(n_dec: int, ctas_per_split: int, num_sms: int, cluster_capacity=None) -> int:
@@ -52,6 +55,8 @@ def decode_splits(n_dec: int, ctas_per_split: int, num_sms: int, cluster_capacit
     stays valid as contexts grow.  cluster_capacity[s], where given and not 0, is how many
     clusters of s slices the device holds at once: the decode kernel merges such slices
     itself (csrc/attention_mma.cu).  Tuned on measured step times at batches 1 to 64."""
+    if FORCED_SPLITS > 0:
+        return FORCED_SPLITS
     slots = CTAS_PER_SM * num_sms
     ctas = max(1, n_dec * ctas_per_split)
     floor = ctas * ASSUMED_TILES * BANDWIDTH_TILE
@@ -59,7 +64,9 @@ def decode_splits(n_dec: int, ctas_per_split: int, num_sms: int, cluster_capacit
     for s in range(1, MAX_SPLITS + 1):
         cap = cluster_capacity[s] if cluster_capacity and s < len(cluster_capacity) else 0
         if cap > 0:
-            rounds, fixed = -(-ctas // max(1, int(cap * CLUSTER_FILL))), CLUSTER_OVERHEAD
+            rounds, fixed = -(-ctas // cap), CLUSTER_OVERHEAD
+            if rounds == 1 and ctas > cap * CLUSTER_FILL:
+                rounds = 2
         else:
             rounds, fixed = -(-ctas * s // slots), SPLIT_OVERHEAD
         cost = max(floor, rounds * -(-ASSUMED_TILES // s)) + fixed + PER_SLICE * s + WAVE_PENALTY * (rounds - 1)
