@@ -18,6 +18,7 @@
 // Prompt portions: one CTA per (64 queries of a sequence, head); a warp owns 16
 // query rows.
 #include "attention_common.cuh"
+#include <cstdlib>
 
 #define MMA_THREADS 128
 #define MMA_BK 64
@@ -811,8 +812,9 @@ __global__ void __launch_bounds__(MMA_THREADS) attn_prefill_mma_kernel(AttnArgs 
 }
 
 // ---------------------------------------------------------------- launchers
+// (static and dynamic shared memory together count against the 48 KB that need no opt-in)
 template <typename K> static int opt_in_smem(K kernel, size_t bytes, const char* who) {
-  if (bytes > 48 * 1024) {
+  if (bytes > 32 * 1024) {
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
     if (e != cudaSuccess) return gg_fail(GG_ERR_CUDA, "%s: %s", who, cudaGetErrorString(e));
   }
@@ -849,21 +851,22 @@ static cudaError_t launch_clustered(K kernel, dim3 grid, size_t smem, int cluste
 // The ring: 64 KB at d = 128, three CTAs per SM.  (A ring of six stages with one CTA per SM
 // for launches that do not fill the device was measured: the attention itself no faster,
 // the step slower, because the next kernel's CTAs found no room beside it.)
-static size_t decode_ring_bytes(int d) { return (size_t)DECODE_STAGES * 2 * MMA_BK * d * 2; }
+#define DECODE_STAGES_FEW 3       // for launches of at most two CTAs per SM: two tiles in flight per CTA
+static size_t decode_ring_bytes(int d, int stages = DECODE_STAGES) { return (size_t)stages * 2 * MMA_BK * d * 2; }
 // The inbox of the merge through the cluster: maxima and sums of every slice, and this
 // CTA's share of every slice's rows.
 static size_t decode_inbox_bytes(int d, int rows) { return (size_t)(ATTN_MAX_CLUSTER * 32 + rows * d + 2 * ATTN_MAX_CLUSTER) * sizeof(float); }
 
-template <int D>
+template <int D, int STAGES>
 static int decode_cluster_capacity_of(int splits, int rows) {
   int n = 0;
   AttnArgs a = {};
-  const size_t smem = decode_ring_bytes(D) + decode_inbox_bytes(D, rows);
+  const size_t smem = decode_ring_bytes(D, STAGES) + decode_inbox_bytes(D, rows);
   cudaError_t e = cudaSuccess;
-  if (smem > 48 * 1024)
-    e = cudaFuncSetAttribute(attn_decode_mma_kernel<D, DECODE_STAGES, true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  if (smem > 32 * 1024)
+    e = cudaFuncSetAttribute(attn_decode_mma_kernel<D, STAGES, true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e == cudaSuccess)
-    e = launch_clustered(attn_decode_mma_kernel<D, DECODE_STAGES, true, false>, dim3(1, 1, splits), smem, splits, 0, a, &n);
+    e = launch_clustered(attn_decode_mma_kernel<D, STAGES, true, false>, dim3(1, 1, splits), smem, splits, 0, a, &n);
   if (e != cudaSuccess) { cudaGetLastError(); n = 0; }
   return n;
 }
@@ -871,17 +874,22 @@ static int decode_cluster_capacity_of(int splits, int rows) {
 // How many clusters of `splits` decode CTAs the device holds at once (0: such clusters
 // cannot be launched), with `group` query heads to a kv head (they size the merge's inbox).
 // Asked once per head size, cluster size and inbox size.
-int attn_decode_cluster_capacity(int d, int splits, int group) {
-  static int cache[2][17][ATTN_MAX_CLUSTER + 1];
-  static bool known[2][17][ATTN_MAX_CLUSTER + 1];
+static int decode_cluster_capacity(int d, int splits, int group, bool few) {
+  static int cache[2][2][17][ATTN_MAX_CLUSTER + 1];
+  static bool known[2][2][17][ATTN_MAX_CLUSTER + 1];
   if ((d != 64 && d != 128) || splits < 1 || splits > ATTN_MAX_CLUSTER || group < 1) return 0;
   const int di = d == 128, rows = group < 16 ? group : 16;
-  if (!known[di][rows][splits]) {
-    cache[di][rows][splits] = d == 128 ? decode_cluster_capacity_of<128>(splits, rows) : decode_cluster_capacity_of<64>(splits, rows);
-    known[di][rows][splits] = true;
+  if (!known[few][di][rows][splits]) {
+    int n;
+    if (few) n = d == 128 ? decode_cluster_capacity_of<128, DECODE_STAGES_FEW>(splits, rows) : decode_cluster_capacity_of<64, DECODE_STAGES_FEW>(splits, rows);
+    else n = d == 128 ? decode_cluster_capacity_of<128, DECODE_STAGES>(splits, rows) : decode_cluster_capacity_of<64, DECODE_STAGES>(splits, rows);
+    cache[few][di][rows][splits] = n;
+    known[few][di][rows][splits] = true;
   }
-  return cache[di][rows][splits];
+  return cache[few][di][rows][splits];
 }
+
+int attn_decode_cluster_capacity(int d, int splits, int group) { return decode_cluster_capacity(d, splits, group, false); }
 
 // *merged is set when the kernel wrote the final output itself (no merge kernel needed).
 int attn_decode_mma(const AttnArgs& a, int n_dec, cudaStream_t stream, bool* merged) {
@@ -891,7 +899,21 @@ int attn_decode_mma(const AttnArgs& a, int n_dec, cudaStream_t stream, bool* mer
   dim3 grid(n_dec, a.nkv * gchunks, a.num_splits);
   const bool cluster = merged && a.num_splits <= ATTN_MAX_CLUSTER && attn_decode_cluster_capacity(a.d, a.num_splits, G) > 0;
   if (merged) *merged = cluster;
-  const size_t smem = decode_ring_bytes(a.d) + (cluster ? decode_inbox_bytes(a.d, G < 16 ? G : 16) : 0);
+  // A launch that fits with two CTAs per SM gets a ring of three stages: each CTA then has two
+  // tiles on their way, and a launch of so few CTAs is bound by how much is in flight (decode
+  // steps at batch 1 and 16: 1.7 and 2.5 % faster; GOLLMGO_B200_DECODE_FEW=0 turns it off).
+  static int num_sms = 0, few_ok = -1;
+  if (!num_sms) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess ||
+        cudaDeviceGetAttribute(&num_sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || num_sms <= 0)
+      num_sms = 148;
+  }
+  if (few_ok < 0) { const char* ev = getenv("GOLLMGO_B200_DECODE_FEW"); few_ok = ev ? atoi(ev) : 1; }
+  const long long groups = (long long)n_dec * a.nkv * gchunks;
+  const bool few = few_ok && groups * a.num_splits <= 2LL * num_sms &&
+                   (!cluster || groups * 10 <= 9LL * decode_cluster_capacity(a.d, a.num_splits, G, true));
+  const size_t smem = decode_ring_bytes(a.d, few ? DECODE_STAGES_FEW : DECODE_STAGES) + (cluster ? decode_inbox_bytes(a.d, G < 16 ? G : 16) : 0);
   const bool rope = a.rope_inv_freq != nullptr;
   if (rope) {
     GG_REQUIRE(gchunks == 1, "attn_decode: the fused rotation takes at most 16 heads per kv head, not %d", G);
@@ -901,11 +923,16 @@ int attn_decode_mma(const AttnArgs& a, int n_dec, cudaStream_t stream, bool* mer
   }
   int rc;
   cudaError_t e;
+#define DECODE_LAUNCH_ST(D_, ST_, CL_, RP_)                                                                  \
+  do {                                                                                                       \
+    if ((rc = opt_in_smem(attn_decode_mma_kernel<D_, ST_, CL_, RP_>, smem, "attn_decode"))) return rc;       \
+    if (CL_) e = launch_clustered(attn_decode_mma_kernel<D_, ST_, CL_, RP_>, grid, smem, a.num_splits, stream, a, nullptr); \
+    else e = gg_launch(attn_decode_mma_kernel<D_, ST_, CL_, RP_>, dim3(grid), dim3(MMA_THREADS), smem, stream, a); \
+  } while (0)
 #define DECODE_LAUNCH(D_, CL_, RP_)                                                                          \
   do {                                                                                                       \
-    if ((rc = opt_in_smem(attn_decode_mma_kernel<D_, DECODE_STAGES, CL_, RP_>, smem, "attn_decode"))) return rc; \
-    if (CL_) e = launch_clustered(attn_decode_mma_kernel<D_, DECODE_STAGES, CL_, RP_>, grid, smem, a.num_splits, stream, a, nullptr); \
-    else e = gg_launch(attn_decode_mma_kernel<D_, DECODE_STAGES, CL_, RP_>, dim3(grid), dim3(MMA_THREADS), smem, stream, a); \
+    if (few) DECODE_LAUNCH_ST(D_, DECODE_STAGES_FEW, CL_, RP_);                                              \
+    else DECODE_LAUNCH_ST(D_, DECODE_STAGES, CL_, RP_);                                                      \
   } while (0)
   if (a.d == 128) {
     if (cluster) { if (rope) DECODE_LAUNCH(128, true, true); else DECODE_LAUNCH(128, true, false); }
@@ -915,6 +942,7 @@ int attn_decode_mma(const AttnArgs& a, int n_dec, cudaStream_t stream, bool* mer
     else { if (rope) DECODE_LAUNCH(64, false, true); else DECODE_LAUNCH(64, false, false); }
   }
 #undef DECODE_LAUNCH
+#undef DECODE_LAUNCH_ST
   if (e != cudaSuccess) return gg_fail(GG_ERR_CUDA, "attn_decode_mma: launch: %s", cudaGetErrorString(e));
   return gg_check_launch("attn_decode_mma");
 }
