@@ -57,6 +57,7 @@ class StepBatch:
     tile128_q0: torch.Tensor
     num_tiles128: int
     dec_seqs: torch.Tensor
+    long_context: bool = False             # some live request holds a long context (set by the runner)
     slot_mapping: List[torch.Tensor]
     block_tables: List[torch.Tensor]
     # host side

@@ -25,6 +25,7 @@ from ..cache import CacheManager, OutOfPages, PagedKVNeed
 from ..config import EngineConfig, read_config_json
 from ..csrc import ops
 from ..parts import BuildContext, build_model, set_matmul_precision
+from ..parts.context import LONG_CONTEXT
 from ..weights import checkpoint_source, random_source
 from .batch import BatchBuilder, BatchLayout, StepBatch, StepEntry
 
@@ -135,11 +136,15 @@ class ModelRunner:
             if e.request_id not in self.cache.requests:
                 self.cache.admit(e.request_id)
         decode_only = all(len(e.tokens) == 1 and list(e.want) == [0] for e in entries)
+        # a step while some live request holds a long context is a step of its own kind: parts
+        # may choose differently for it (the attention's count of slices), so it has graphs of its own
+        long_context = int(self.cache.ntok.max()) >= LONG_CONTEXT
         if decode_only and self.ecfg.cuda_graphs:
             bucket = next((b for b in GRAPH_BUCKETS if b >= len(entries)), None)
             if bucket is not None and bucket <= self.ctx.max_seqs:
-                return self._graph_step(entries, bucket)
+                return self._graph_step(entries, bucket, long_context)
         batch = self.builder.build(entries)
+        batch.long_context = long_context
         batch.prev_tokens = self.last_tokens if batch.token_src is not None else None
         logits = self.model.forward(batch, self.caches)
         self.steps += 1
@@ -156,14 +161,16 @@ class ModelRunner:
     def _graph_stride(self) -> int:
         return -(-self.max_model_len // self.cache.page_size)
 
-    def _graph_step(self, entries, bucket: int) -> torch.Tensor:
-        cs = self._graphs.get(bucket)
+    def _graph_step(self, entries, bucket: int, long_context: bool = False) -> torch.Tensor:
+        key = (bucket, True) if long_context else bucket
+        cs = self._graphs.get(key)
         stride = self._graph_stride()
         if cs is None:
             lay = BatchLayout(bucket, bucket, bucket, 0, bucket, len(self.cache.groups), stride)
             cs = _CapturedStep(torch.zeros(lay.size, dtype=torch.int32, device=self.device))
-            self._graphs[bucket] = cs
+            self._graphs[key] = cs
         batch = self.builder.build(entries, fixed_seqs=bucket, fixed_stride=stride, static_dev=cs.meta)
+        batch.long_context = long_context
         batch.prev_tokens = self.last_tokens
         if cs.graph is None:
             torch.cuda.synchronize(self.device)

@@ -30,6 +30,13 @@ FUSE_DECODE_ROPE = os.environ.get("GOLLMGO_B200_FUSE_ROPE", "1") != "0"
 # use the kernel that cuts all tiles into equal ranges (ops.attn_decode_flat); 0 = never.
 FLAT_DECODE_FILL = float(os.environ.get("GOLLMGO_B200_FLAT_DECODE_FILL", "1.0"))
 MAX_SPLITS = 16
+# A step whose longest context has reached context.LONG_CONTEXT tokens is a step of its own kind (the
+# runner captures it separately and sets batch.long_context): the count of slices is then
+# chosen for contexts of LONG_TILES tiles, among up to MAX_SPLITS_LONG.  One sequence at
+# 32768 tokens: 8 slices in a cluster are 64 CTAs for 134 MB of cache a layer (87 us); 32
+# slices and a merge kernel are 256 CTAs.
+LONG_TILES = 256
+MAX_SPLITS_LONG = 64
 FORCED_SPLITS = int(os.environ.get("GOLLMGO_B200_DECODE_SPLITS", "0"))   # for measurements: this count, whatever the batch
 CTAS_PER_SM = 3            # decode attention CTAs resident on one SM (csrc/attention_mma.cu)
 ASSUMED_TILES = 32         # context the choice is tuned for: 32 tiles of 64 keys
@@ -48,7 +55,8 @@ CLUSTER_FILL = 0.9         # share of the cluster capacity that one round can co
                            # two rounds, 52.8 us a layer, against 61.1 for whole contexts on 256 of 444 places)
 
 
-def decode_splits(n_dec: int, ctas_per_split: int, num_sms: int, cluster_capacity=None) -> int:
+def decode_splits(n_dec: int, ctas_per_split: int, num_sms: int, cluster_capacity=None,
+                  long_context: bool = False) -> int:
     """Slices of the context per decoded token: the count with the least estimated time
     max(bandwidth floor, rounds x tiles per slice) + overheads for a typical context.  It
     depends only on the batch, never on the actual context lengths, so a captured step
@@ -59,9 +67,13 @@ def decode_splits(n_dec: int, ctas_per_split: int, num_sms: int, cluster_capacit
         return FORCED_SPLITS
     slots = CTAS_PER_SM * num_sms
     ctas = max(1, n_dec * ctas_per_split)
-    floor = ctas * ASSUMED_TILES * BANDWIDTH_TILE
+    # (only where even the largest cluster per pair leaves places empty: larger batches stream
+    # long contexts at 0.8 of the copy bandwidth with the choice made for short ones)
+    long_context = long_context and ctas * 8 < slots
+    tiles = LONG_TILES if long_context else ASSUMED_TILES
+    floor = ctas * tiles * BANDWIDTH_TILE
     best, best_cost = 1, None
-    for s in range(1, MAX_SPLITS + 1):
+    for s in range(1, (MAX_SPLITS_LONG if long_context else MAX_SPLITS) + 1):
         cap = cluster_capacity[s] if cluster_capacity and s < len(cluster_capacity) else 0
         if cap > 0:
             rounds, fixed = -(-ctas // cap), CLUSTER_OVERHEAD
@@ -69,7 +81,7 @@ def decode_splits(n_dec: int, ctas_per_split: int, num_sms: int, cluster_capacit
                 rounds = 2
         else:
             rounds, fixed = -(-ctas * s // slots), SPLIT_OVERHEAD
-        cost = max(floor, rounds * -(-ASSUMED_TILES // s)) + fixed + PER_SLICE * s + WAVE_PENALTY * (rounds - 1)
+        cost = max(floor, rounds * -(-tiles // s)) + fixed + PER_SLICE * s + WAVE_PENALTY * (rounds - 1)
         if best_cost is None or cost < best_cost - 1e-9:
             best, best_cost = s, cost
     return best
@@ -105,8 +117,8 @@ class Attention:
         if ctx.device.type == "cuda":
             self._cluster_cap = [0] + [ops.attn_decode_cluster_capacity(ctx.act_dtype, self.d, s, self.nh // self.nkv)
                                        for s in range(1, ops.ATTN_MAX_CLUSTER + 1)]
-        rows = max(n * decode_splits(n, self._ctas_per_split, self.num_sms, self._cluster_cap)
-                   for n in range(1, ctx.max_seqs + 1))
+        rows = max(n * decode_splits(n, self._ctas_per_split, self.num_sms, self._cluster_cap, lc)
+                   for n in range(1, ctx.max_seqs + 1) for lc in (False, True))
         ws.reserve("attn_part_o", rows * self.nh * self.d, torch.float32)
         ws.reserve("attn_part_ml", rows * self.nh * 2, torch.float32)
         self._flat_ok = (ctx.device.type == "cuda" and ctx.act_dtype == torch.bfloat16 and self.d in (64, 128)
@@ -185,7 +197,8 @@ class Attention:
                                  ws.get("attn_flat_prefix", 1, n + 1), out, self.nh, self.nkv, self.d,
                                  self.ctx.page_size, window, self.scale)
         elif batch.num_decode:
-            splits = decode_splits(batch.num_decode, self._ctas_per_split, self.num_sms, self._cluster_cap)
+            splits = decode_splits(batch.num_decode, self._ctas_per_split, self.num_sms, self._cluster_cap,
+                                   batch.long_context)
             part_o = ws.get("attn_part_o", 1, batch.num_decode * self.nh * splits * self.d)
             part_ml = ws.get("attn_part_ml", 1, batch.num_decode * self.nh * splits * 2)
         if batch.num_decode and flat_step:

@@ -3,9 +3,16 @@ limits, and a workspace of named activation buffers that parts share.
 """
 from __future__ import annotations
 
+import os
 from typing import Dict, Optional, Tuple
 
 import torch
+
+
+# From this many tokens in some live request's cache a step counts as one with a long context:
+# the runner sets batch.long_context and keeps captured steps of their own for it, and a part
+# may choose differently for such steps (the attention: more slices of the context).
+LONG_CONTEXT = int(os.environ.get("GOLLMGO_B200_LONG_CONTEXT", "8192"))
 
 
 class Workspace:

@@ -206,6 +206,52 @@ def test_decode_kernel_for_large_batches_inside_the_engine(tmp_path, cuda_device
         assert rows.shape[0] == len(seqs[n])
 
 
+@pytest.mark.parametrize("name", ["tiny_d", "tiny_e"])
+def test_steps_with_a_long_context_are_steps_of_their_own(tmp_path, cuda_device, monkeypatch, name):
+    """Once some live request's cache has reached the threshold of a long context (lowered here),
+    decode steps are captured separately and the attention cuts contexts into many more slices
+    (merged by a kernel of their own, most of them empty at these lengths): every logit row of
+    long decoding against the whole sequence, before and after the change."""
+    import importlib
+    R = importlib.import_module("gollmgo_b200.engine.runner")
+    monkeypatch.setattr(R, "LONG_CONTEXT", 60)
+    from gollmgo_b200.config import EngineConfig
+    from gollmgo_b200.engine.batch import StepEntry
+    cfg, page, std, jitter = tiny_configs.get(name)
+    d = tt.model_folder(str(tmp_path), name, cfg, seed=32, std=std, jitter=jitter, dtype="bfloat16")
+    w = tt.load_weights(d)
+    runner = R.load_runner(d, EngineConfig(dtype="bfloat16", block_size=page, num_blocks=96, max_batch_size=4,
+                                           max_token_budget=64, max_model_len=256))
+    mixer = runner.model.blocks[0].mixer
+    A = importlib.import_module("gollmgo_b200.parts.attention")
+    assert A.decode_splits(2, mixer._ctas_per_split, mixer.num_sms, mixer._cluster_cap, True) > 8
+    seqs = tt.random_requests(cfg["vocab_size"], [140, 90], seed=9)
+    refs = tt.plain_logits(w, cfg, seqs)
+    names = list(seqs)
+    first = {n: 3 + 5 * i for i, n in enumerate(names)}
+    got = {n: [] for n in names}
+    out = runner.step([StepEntry(n, seqs[n][:first[n]], range(first[n])) for n in names]).cpu().double()
+    i = 0
+    for n in names:
+        got[n].append(out[i:i + first[n]])
+        i += first[n]
+    for t in range(1, 140):
+        step = [n for n in names if first[n] + t - 1 < len(seqs[n])]
+        if not step:
+            break
+        out = runner.step([StepEntry(n, [seqs[n][first[n] + t - 1]], [0]) for n in step]).cpu().double()
+        for j, n in enumerate(step):
+            got[n].append(out[j:j + 1])
+    kinds = set(runner._graphs)
+    assert 2 in kinds and (2, True) in kinds and (1, True) in kinds, kinds
+    for n in names:
+        rows = torch.cat(got[n])
+        ref = refs[n][:rows.shape[0]]
+        err = ((rows - ref).abs().amax(dim=1) / ref.abs().amax(dim=1)).max()
+        assert float(err) <= 6e-2, f"{n}: worst relative error {float(err):.2e}"
+        assert rows.shape[0] == len(seqs[n])
+
+
 def test_decode_steps_of_every_batch_size_are_captured_when_the_engine_is_built(models):
     """No capture happens in the middle of generation, whatever batch sizes the requests pass
     through as they end one by one; an engine that captures at first use gives the same."""
