@@ -9,6 +9,8 @@
 // request's tokens do not depend on what else is in the batch.
 // Elements equal to the top-k or top-p threshold value are all kept.
 #include "common.cuh"
+#include <cstring>
+#include <cstdlib>
 
 #define SAMPLE_THREADS 1024
 
@@ -97,10 +99,46 @@ __global__ void argmax_kernel(const float* __restrict__ logits, int V, int* __re
 // leader's bin, their weights are summed by the warp, and the leader adds the sum without an
 // atomic; the warps' histograms are then added in warp order.  The sums therefore have a
 // fixed order and the result is the same on every run.
-template <bool MASS>
+// ---- a row spread over the CTAs of a thread-block cluster (sample_cluster_kernel): what a
+// CTA shows its neighbours.  Two copies, used in turn: a copy is written again only after a
+// further cluster barrier, which nobody passes before everybody has read the one before.
+struct ClusterPub {
+  float hist[2][256];
+  float f[2];
+  int i[2];
+  int parity;            // which copy the next exchange uses (the same in every CTA)
+};
+__device__ __forceinline__ unsigned sc_rank() {
+  unsigned r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ unsigned sc_size() {
+  unsigned r;
+  asm volatile("mov.u32 %0, %%cluster_nctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ void sc_barrier() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+template <typename T> __device__ __forceinline__ T sc_load(const T* local, unsigned rank) {
+  unsigned v, a = (unsigned)__cvta_generic_to_shared(local);
+  asm volatile(
+      "{\n\t.reg .b32 ra;\n\t"
+      "mapa.shared::cluster.u32 ra, %1, %2;\n\t"
+      "ld.shared::cluster.b32 %0, [ra];\n\t}"
+      : "=r"(v) : "r"(a), "r"(rank) : "memory");
+  T out;
+  memcpy(&out, &v, 4);
+  return out;
+}
+
+// CL: row is this CTA's part of the row and the histogram of a pass is the sum over the
+// cluster's CTAs in rank order, the same in every CTA, so every CTA descends alike.
+template <bool MASS, bool CL>
 __device__ unsigned int radix_threshold(const float* row, int V, float m, float invT,
                                         unsigned int floor_key, float target, float* hist,
-                                        float (*whist)[256]) {
+                                        float (*whist)[256], unsigned long long* h64, ClusterPub* pub = nullptr) {
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
   unsigned int prefix = 0, pmask = 0;
   float above = 0.f;       // weight of keys strictly above the current prefix range
@@ -112,9 +150,27 @@ __device__ unsigned int radix_threshold(const float* row, int V, float m, float 
   for (int shift = 24; shift >= 0; shift -= 8) {
     if (shift != 24) low_bin = 0;
     for (int i = lane; i < 256; i += 32) whist[warp][i] = 0.f;
+    if (shift != 24) {
+      for (int i = threadIdx.x; i < 256; i += blockDim.x) h64[i] = 0ULL;
+      __syncthreads();
+    }
     __syncwarp();
     // one element of every lane: the lanes of a bin are found by comparison with a leader's
     auto consume = [&](float x, bool valid) {
+      if (shift != 24) {
+        // Below the leading byte the elements still in the range spread over many bins: the
+        // vote below would take a round per distinct bin.  Atomic adds on one histogram of
+        // 64-bit integers instead (weights in fixed point, 40 fraction bits): integer sums do
+        // not depend on their order, so the result stays the same on every run.
+        if (valid) {
+          const unsigned int k = ordered_key(x);
+          if (k >= floor_key && (k & pmask) == prefix) {
+            const unsigned long long w = MASS ? (unsigned long long)(expf((x - m) * invT) * 1099511627776.f) : 1ULL;
+            atomicAdd(h64 + ((k >> shift) & 255u), w);
+          }
+        }
+        return;
+      }
       int bin = -1;
       float w = 0.f;
       if (valid) {
@@ -129,9 +185,10 @@ __device__ unsigned int radix_threshold(const float* row, int V, float m, float 
         const int leader = __ffs(todo) - 1;
         const int b = __shfl_sync(0xffffffffu, bin, leader);
         const bool mine = bin == b;
-        const float sum = warp_sum(mine ? w : 0.f);
+        const unsigned same = __ballot_sync(0xffffffffu, mine);
+        const float sum = MASS ? warp_sum(mine ? w : 0.f) : (float)__popc(same);   // counting needs no sum
         if (lane == leader) whist[warp][b] += sum;
-        todo &= ~__ballot_sync(0xffffffffu, mine);
+        todo &= ~same;
       }
     };
     // four values per load where the row allows it: a quarter as many trips to L2 in a loop
@@ -162,8 +219,21 @@ __device__ unsigned int radix_threshold(const float* row, int V, float m, float 
     __syncthreads();
     for (int i = threadIdx.x; i < 256; i += blockDim.x) {
       float v = 0.f;
-      for (int wv = 0; wv < nw; ++wv) v += whist[wv][i];
-      hist[i] = v;
+      if (shift == 24) { for (int wv = 0; wv < nw; ++wv) v += whist[wv][i]; }
+      else v = MASS ? (float)h64[i] * (1.f / 1099511627776.f) : (float)h64[i];
+      if (CL) pub->hist[pub->parity][i] = v; else hist[i] = v;
+    }
+    if (CL) {
+      const int par = pub->parity;
+      sc_barrier();                            // (also a barrier of the CTA)
+      const unsigned C = sc_size();
+      for (int i = threadIdx.x; i < 256; i += blockDim.x) {
+        float v = 0.f;
+        for (unsigned c = 0; c < C; ++c) v += sc_load(&pub->hist[par][i], c);
+        hist[i] = v;
+      }
+      __syncthreads();
+      if (threadIdx.x == 0) pub->parity = par ^ 1;
     }
     __syncthreads();
     if (threadIdx.x == 0) {
@@ -203,6 +273,7 @@ sample_kernel(const float* __restrict__ logits, int V, const float* __restrict__
   __shared__ int red_i[33];
   __shared__ float hist[258];
   __shared__ float whist[SAMPLE_THREADS / 32][256];       // a histogram per warp (radix_threshold)
+  __shared__ unsigned long long h64[256];
   __shared__ float scan[SAMPLE_THREADS / 32 + 1];
   __shared__ int found;
   pdl_trigger();
@@ -219,7 +290,7 @@ sample_kernel(const float* __restrict__ logits, int V, const float* __restrict__
   const float invT = 1.f / T;
   unsigned int floor_key = 0;
   const int k = top_k ? top_k[r] : 0;
-  if (k > 0 && k < V) floor_key = radix_threshold<false>(row, V, m, invT, 0u, (float)k, hist, whist);
+  if (k > 0 && k < V) floor_key = radix_threshold<false, false>(row, V, m, invT, 0u, (float)k, hist, whist, h64);
   const float p = top_p ? top_p[r] : 0.f;
   if (p > 0.f && p < 1.f) {
     float z = 0.f;
@@ -228,7 +299,7 @@ sample_kernel(const float* __restrict__ logits, int V, const float* __restrict__
       if (ordered_key(x) >= floor_key) z += expf((x - m) * invT);
     }
     z = block_sum(z, red_f);
-    floor_key = radix_threshold<true>(row, V, m, invT, floor_key, p * z, hist, whist);
+    floor_key = radix_threshold<true, false>(row, V, m, invT, floor_key, p * z, hist, whist, h64);
   }
   // running sum in index order over the kept elements; thread owns a contiguous chunk
   const int chunk = (V + blockDim.x - 1) / blockDim.x;
@@ -276,6 +347,163 @@ sample_kernel(const float* __restrict__ logits, int V, const float* __restrict__
   if (threadIdx.x == 0) out[r] = found >= 0 ? found : amax;
 }
 
+// ---------------------------------------------------------------- a row on a cluster of CTAs
+// One CTA per row reads its 128 k logits from L2 a dozen times (maximum, top-k and top-p
+// descents of up to four passes each, sums), at the rate one SM gets from L2: 266 us with top-k
+// and top-p (120 us here, for 8 rows).  Here a row is cut into SC_CLUSTER parts, one per CTA of a cluster; a CTA reads
+// its part from global memory once and keeps it in shared memory, and the CTAs exchange
+// histograms and sums through distributed shared memory, always added in rank order, so every
+// CTA takes the same decisions and the result is the same on every run.  Same arithmetic per
+// element as sample_kernel; sums are associated differently (parts instead of 1024 strides).
+#define SC_THREADS 512
+#define SC_CLUSTER 8
+#define SC_MIN_V 16384            // shorter rows stay with sample_kernel
+
+// sum of v over the cluster in rank order (every CTA gets the same bits); *before = the sum
+// over the ranks below this CTA's.  Called by all threads; v of thread 0 counts.
+__device__ float sc_sum(float v, ClusterPub* pub, float* bcast, float* before) {
+  const int par = pub->parity;
+  if (threadIdx.x == 0) pub->f[par] = v;
+  sc_barrier();
+  if (threadIdx.x == 0) {
+    const unsigned C = sc_size(), me = sc_rank();
+    float run = 0.f, mine = 0.f;
+    for (unsigned c = 0; c < C; ++c) {
+      if (c == me) mine = run;
+      run += sc_load(&pub->f[par], c);
+    }
+    bcast[0] = run;
+    bcast[1] = mine;
+    pub->parity = par ^ 1;
+  }
+  __syncthreads();
+  if (before) *before = bcast[1];
+  return bcast[0];
+}
+
+__global__ void __launch_bounds__(SC_THREADS)
+sample_cluster_kernel(const float* __restrict__ logits, int V, int part, const float* __restrict__ temperature,
+                      const int* __restrict__ top_k, const float* __restrict__ top_p,
+                      const unsigned long long* __restrict__ seeds,
+                      const unsigned long long* __restrict__ draw_index, int* __restrict__ out) {
+  extern __shared__ __align__(16) float sc_part[];          // this CTA's part of the row
+  __shared__ float red_f[33];
+  __shared__ int red_i[33];
+  __shared__ float hist[258];
+  __shared__ float whist[SC_THREADS / 32][256];
+  __shared__ unsigned long long h64[256];
+  __shared__ float scan[SC_THREADS / 32 + 1];
+  __shared__ float bcast[2];
+  __shared__ int found;
+  __shared__ ClusterPub pub;
+  pdl_trigger();
+  pdl_wait();
+  const int r = blockIdx.y;
+  const unsigned me = sc_rank(), C = sc_size();
+  const int base = (int)me * part, n = max(0, min(part, V - base));   // elements [base, base + n)
+  const float* row = logits + (size_t)r * V;
+  if (threadIdx.x == 0) pub.parity = 0;
+  // the part into shared memory (float4 where the row's start allows it; part is a multiple of 4)
+  if (((((size_t)row) & 15) == 0) && (n & 3) == 0) {
+    const float4* src = reinterpret_cast<const float4*>(row + base);
+    float4* dst = reinterpret_cast<float4*>(sc_part);
+    for (int i = threadIdx.x; i < (n >> 2); i += SC_THREADS) dst[i] = src[i];
+  } else {
+    for (int i = threadIdx.x; i < n; i += SC_THREADS) sc_part[i] = row[base + i];
+  }
+  __syncthreads();
+  const float T = temperature[r];
+  // the maximum and its first index: of the part, then of the row (the lowest rank wins a tie)
+  float m_local;
+  const int a_local = block_argmax(sc_part, n, red_f, red_i, &m_local);
+  if (threadIdx.x == 0) { pub.f[0] = n > 0 ? m_local : -INFINITY; pub.i[0] = base + a_local; }
+  sc_barrier();
+  float m = -INFINITY;
+  int amax = 0;
+  for (unsigned c = 0; c < C; ++c) {
+    const float v = sc_load(&pub.f[0], c);
+    if (v > m) { m = v; amax = sc_load(&pub.i[0], c); }
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) pub.parity = 1;
+  __syncthreads();
+  if (T <= 1e-9f) {
+    if (me == 0 && threadIdx.x == 0) out[r] = amax;
+    sc_barrier();                            // nobody leaves while a neighbour may still read it
+    return;
+  }
+  const float invT = 1.f / T;
+  unsigned int floor_key = 0;
+  const int k = top_k ? top_k[r] : 0;
+  if (k > 0 && k < V) floor_key = radix_threshold<false, true>(sc_part, n, m, invT, 0u, (float)k, hist, whist, h64, &pub);
+  const float p = top_p ? top_p[r] : 0.f;
+  if (p > 0.f && p < 1.f) {
+    float z = 0.f;
+    for (int i = threadIdx.x; i < n; i += SC_THREADS) {
+      const float x = sc_part[i];
+      if (ordered_key(x) >= floor_key) z += expf((x - m) * invT);
+    }
+    z = block_sum(z, red_f);
+    z = sc_sum(z, &pub, bcast, nullptr);
+    floor_key = radix_threshold<true, true>(sc_part, n, m, invT, floor_key, p * z, hist, whist, h64, &pub);
+  }
+  // running sum in index order over the kept elements: a thread owns a contiguous piece of
+  // the part, a CTA the part, the ranks follow each other
+  const int chunk = (n + SC_THREADS - 1) / SC_THREADS;
+  const int i0 = min(n, (int)threadIdx.x * chunk), i1 = min(n, i0 + chunk);
+  float local = 0.f;
+  for (int i = i0; i < i1; ++i) {
+    const float x = sc_part[i];
+    if (ordered_key(x) >= floor_key) local += expf((x - m) * invT);
+  }
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  float incl = local;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const float v = __shfl_up_sync(0xffffffffu, incl, o);
+    if (lane >= o) incl += v;
+  }
+  if (threadIdx.x == 0) found = -1;
+  if (lane == 31) scan[warp] = incl;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float run = 0.f;
+    for (int w = 0; w < SC_THREADS / 32; ++w) { const float v = scan[w]; scan[w] = run; run += v; }
+    scan[SC_THREADS / 32] = run;
+  }
+  __syncthreads();
+  float ranks_before;
+  const float total = sc_sum(scan[SC_THREADS / 32], &pub, bcast, &ranks_before);
+  const float before = ranks_before + scan[warp] + incl - local;
+  const float u = uniform_draw(seeds ? seeds[r] : 0ULL, draw_index ? draw_index[r] : 0ULL);
+  const float target = u * total;
+  if (local > 0.f && target >= before && target < before + local) {
+    float cum = before;
+    int pick = -1;
+    for (int i = i0; i < i1; ++i) {
+      const float x = sc_part[i];
+      if (ordered_key(x) >= floor_key) {
+        cum += expf((x - m) * invT);
+        pick = base + i;
+        if (target < cum) break;
+      }
+    }
+    if (pick >= 0) atomicMax(&found, pick);
+  }
+  __syncthreads();
+  // the largest index anybody found (rounding can make two neighbours claim the draw, or
+  // nobody: then the maximum's index, as in sample_kernel)
+  const int par = pub.parity;
+  if (threadIdx.x == 0) pub.i[par] = found;
+  sc_barrier();
+  if (me == 0 && threadIdx.x == 0) {
+    int best = -1;
+    for (unsigned c = 0; c < C; ++c) best = max(best, sc_load(&pub.i[par], c));
+    out[r] = best >= 0 ? best : amax;
+  }
+  sc_barrier();                              // nobody leaves while rank 0 may still read it
+}
+
 extern "C" int gg_argmax(const float* logits, int R, int V, int* out, cudaStream_t stream) {
   GG_REQUIRE(R >= 0 && V > 0, "argmax: bad sizes R=%d V=%d", R, V);
   if (R == 0) return GG_OK;
@@ -289,6 +517,44 @@ extern "C" int gg_sample(const float* logits, int R, int V, const float* tempera
   GG_REQUIRE(R >= 0 && V > 0, "sample: bad sizes R=%d V=%d", R, V);
   GG_REQUIRE(temperature != nullptr, "sample: no temperatures given");
   if (R == 0) return GG_OK;
+  static int use_cluster = -1;
+  if (use_cluster < 0) { const char* e = getenv("GOLLMGO_B200_SAMPLE_CLUSTER"); use_cluster = e ? atoi(e) : 1; }
+  const int part = (((V + SC_CLUSTER - 1) / SC_CLUSTER) + 3) & ~3;
+  const size_t smem = (size_t)part * sizeof(float);
+  static int num_sms = 0;
+  if (!num_sms) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess ||
+        cudaDeviceGetAttribute(&num_sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || num_sms <= 0)
+      num_sms = 148;
+  }
+  // (with more rows than clusters fit at once, two CTAs per SM, a CTA per row is as fast: 268
+  // against 283 us for 64 rows; 8 rows: 266 against 120 us)
+  if (use_cluster && V >= SC_MIN_V && smem <= 160 * 1024 && R * SC_CLUSTER <= 2 * num_sms) {
+    static bool set = false;
+    if (!set) {
+      cudaError_t e = cudaFuncSetAttribute(sample_cluster_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
+      if (e != cudaSuccess) return gg_fail(GG_ERR_CUDA, "sample: %s", cudaGetErrorString(e));
+      set = true;
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(SC_CLUSTER, R);
+    cfg.blockDim = dim3(SC_THREADS);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = SC_CLUSTER;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = gg_pdl_enabled() ? 2 : 1;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, sample_cluster_kernel, logits, V, part, temperature, top_k, top_p, seeds, draw_index, out);
+    if (e != cudaSuccess) return gg_fail(GG_ERR_CUDA, "sample: launch: %s", cudaGetErrorString(e));
+    return gg_check_launch("sample");
+  }
   gg_launch(sample_kernel, dim3(R), dim3(SAMPLE_THREADS), 0, stream, logits, V, temperature, top_k, top_p, seeds, draw_index, out);
   return gg_check_launch("sample");
 }

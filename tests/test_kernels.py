@@ -430,10 +430,12 @@ def test_argmax_first_maximum_wins(ops, cuda_device):
     assert out.tolist() == [77, V - 1, 0, 0, int(logits[4].argmax())]
 
 
-def test_sample_matches_the_plain_sampler(ops, cuda_device):
+@pytest.mark.parametrize("V", [1013, 16385, 50257, 128256])
+def test_sample_matches_the_plain_sampler(ops, cuda_device, V):
+    """(From 16384 entries a row is spread over a cluster of CTAs: another kernel.)"""
     import plain_llama as P
     torch.manual_seed(7)
-    V, R = 1013, 24
+    R = 24
     logits = (torch.randn(R, V) * 2.5).cuda()
     temps = [0.0, 0.8, 1.0, 1.3, 0.5, 2.0] * 4
     top_k = [0, 0, 50, 0, 7, 1] * 4
@@ -459,11 +461,16 @@ def test_sample_matches_the_plain_sampler(ops, cuda_device):
         assert p[got] > 0 and abs(float(cum[got]) - u) < 1e-4 or abs(float(cum[got] - p[got]) - u) < 1e-4, \
             f"row {r}: kernel chose {got}, plain {want}"
     assert agree >= R - 2
+    again = torch.empty_like(out)
+    ops.sample(logits, dev(temps, torch.float32), dev(top_k, torch.int32), dev(top_p, torch.float32),
+               dev(seeds, torch.int64), dev(draws, torch.int64), again)
+    assert torch.equal(out, again)
 
 
-def test_sample_statistics_and_seeds(ops, cuda_device):
-    V, R = 50, 4000
-    row = torch.linspace(-2, 2, V)
+@pytest.mark.parametrize("V", [50, 20000])
+def test_sample_statistics_and_seeds(ops, cuda_device, V):
+    R = 4000
+    row = torch.linspace(-2, 2, V) if V == 50 else torch.cat([torch.linspace(-2, 2, 50), torch.full((V - 50,), -60.0)])
     logits = row.repeat(R, 1).cuda()
     dev = lambda x, dt: torch.tensor(x, dtype=dt, device="cuda")
     out = torch.empty(R, dtype=torch.int32, device="cuda")
@@ -471,7 +478,7 @@ def test_sample_statistics_and_seeds(ops, cuda_device):
     ops.sample(logits, *args, dev([5] * R, torch.int64), dev(list(range(R)), torch.int64), out)
     freq = torch.bincount(out.long().cpu(), minlength=V).double() / R
     p = torch.softmax(row.double() / 0.7, 0)
-    assert float((freq - p).abs().max()) < 0.02
+    assert float((freq - p).abs().max()) < 0.025
     again = torch.empty_like(out)
     ops.sample(logits, *args, dev([5] * R, torch.int64), dev(list(range(R)), torch.int64), again)
     assert torch.equal(out, again)                                     # same seed and draw: same token
