@@ -236,17 +236,46 @@ __device__ unsigned int radix_threshold(const float* row, int V, float m, float 
       if (threadIdx.x == 0) pub->parity = par ^ 1;
     }
     __syncthreads();
-    if (threadIdx.x == 0) {
-      float cum = above;
-      int bin = 255;
-      for (; bin > low_bin; --bin) {
-        if (cum + hist[bin] >= target) break;
-        cum += hist[bin];
+    if (warp == 0) {
+      // the first bin from the top whose weight, added to that of the bins above, reaches the
+      // target.  Lane l takes bins 255 - 8 l down to 248 - 8 l (one thread walking 256 bins is
+      // 256 dependent reads of shared memory, 4 us a pass); only bins above low_bin count, and
+      // low_bin itself is the answer where none of them does.
+      float hs[8], s = 0.f;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const int b = 255 - 8 * lane - j;
+        hs[j] = b > low_bin ? hist[b] : 0.f;
+        s += hs[j];
       }
-      // stopped at the lowest bin looked at without reaching the target: the bins below count too
-      const bool again = low_bin > 0 && bin == low_bin && cum + hist[bin] < target;
-      hist[256] = cum;
-      hist[257] = __int_as_float(again ? -1 : bin);
+      float incl = s;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const float v = __shfl_up_sync(0xffffffffu, incl, o);
+        if (lane >= o) incl += v;
+      }
+      float cum = above + (incl - s);
+      int fb = -1;
+      float fcum = 0.f;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const int b = 255 - 8 * lane - j;
+        if (b > low_bin && fb < 0) {
+          if (cum + hs[j] >= target) { fb = b; fcum = cum; }
+          else cum += hs[j];
+        }
+      }
+      const unsigned any = __ballot_sync(0xffffffffu, fb >= 0);
+      const int src = any ? __ffs(any) - 1 : 31;
+      const int bin = any ? __shfl_sync(0xffffffffu, fb, src) : low_bin;
+      const float all = __shfl_sync(0xffffffffu, incl, 31);
+      const float cumv = any ? __shfl_sync(0xffffffffu, fcum, src) : above + all;
+      if (lane == 0) {
+        // stopped at the lowest bin looked at without reaching the target: the bins below count too
+        const bool again = low_bin > 0 && bin == low_bin && cumv + hist[bin] < target;
+        hist[256] = cumv;
+        hist[257] = __int_as_float(again ? -1 : bin);
+      }
     }
     __syncthreads();
     if (__float_as_int(hist[257]) < 0) {       // the same pass again over all bins
@@ -350,7 +379,7 @@ sample_kernel(const float* __restrict__ logits, int V, const float* __restrict__
 // ---------------------------------------------------------------- a row on a cluster of CTAs
 // One CTA per row reads its 128 k logits from L2 a dozen times (maximum, top-k and top-p
 // descents of up to four passes each, sums), at the rate one SM gets from L2: 266 us with top-k
-// and top-p (120 us here, for 8 rows).  Here a row is cut into SC_CLUSTER parts, one per CTA of a cluster; a CTA reads
+// and top-p (72 us here, for 8 rows).  Here a row is cut into SC_CLUSTER parts, one per CTA of a cluster; a CTA reads
 // its part from global memory once and keeps it in shared memory, and the CTAs exchange
 // histograms and sums through distributed shared memory, always added in rank order, so every
 // CTA takes the same decisions and the result is the same on every run.  Same arithmetic per
@@ -529,7 +558,7 @@ extern "C" int gg_sample(const float* logits, int R, int V, const float* tempera
       num_sms = 148;
   }
   // (with more rows than clusters fit at once, two CTAs per SM, a CTA per row is as fast: 268
-  // against 283 us for 64 rows; 8 rows: 266 against 120 us)
+  // against 283 us for 64 rows, measured before the bin of a pass was chosen by a warp; 8 rows: 266 against 120 us then)
   if (use_cluster && V >= SC_MIN_V && smem <= 160 * 1024 && R * SC_CLUSTER <= 2 * num_sms) {
     static bool set = false;
     if (!set) {
