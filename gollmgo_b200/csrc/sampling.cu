@@ -93,12 +93,15 @@ __global__ void argmax_kernel(const float* __restrict__ logits, int V, int* __re
 // with key > K weigh less than `target` and those with key >= K weigh at least
 // `target`.  weight(i) = 1 (count mode, the k-th largest) or exp((x_i - m) * invT)
 // (mass mode).  Only elements with key >= floor_key take part.
-// Logits crowd into a few values of the leading byte, so one shared histogram with atomics
-// serialises (a millisecond per row at a vocabulary of 128 k).  Every warp keeps a histogram
-// of its own instead: the lanes that fall into the same bin are found by comparison with a
-// leader's bin, their weights are summed by the warp, and the leader adds the sum without an
-// atomic; the warps' histograms are then added in warp order.  The sums therefore have a
-// fixed order and the result is the same on every run.
+// Leading byte: logits crowd into a few of its values (one shared histogram with atomics
+// serialised there: a millisecond per row at a vocabulary of 128 k), and the threshold is
+// almost always within the three values at and below the maximum's.  So a thread first adds up
+// the weights of its elements in just those three bins, in registers, and the block adds the
+// threads' sums in a fixed order.  Only if the three bins together do not reach the target is
+// the leading byte binned in full.  Lower bytes (and that full pass): the elements still in the
+// range spread over many bins; atomic adds on a histogram of 64-bit integers (weights in fixed
+// point, 40 fraction bits).  Integer sums do not depend on their order and the others have a
+// fixed one, so the result is the same on every run.
 // ---- a row spread over the CTAs of a thread-block cluster (sample_cluster_kernel): what a
 // CTA shows its neighbours.  Two copies, used in turn: a copy is written again only after a
 // further cluster barrier, which nobody passes before everybody has read the one before.
@@ -138,96 +141,29 @@ template <typename T> __device__ __forceinline__ T sc_load(const T* local, unsig
 template <bool MASS, bool CL>
 __device__ unsigned int radix_threshold(const float* row, int V, float m, float invT,
                                         unsigned int floor_key, float target, float* hist,
-                                        float (*whist)[256], unsigned long long* h64, ClusterPub* pub = nullptr) {
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+                                        float* red, unsigned long long* h64, ClusterPub* pub = nullptr) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const float FX = 1099511627776.f;        // 2^40
   unsigned int prefix = 0, pmask = 0;
   float above = 0.f;       // weight of keys strictly above the current prefix range
-  // In the first pass every element takes part and the bins of small values hold nearly all of
-  // them, though the threshold is almost always within the three bins at and below the
-  // maximum's.  So the first pass only bins those (`low_bin` = the lowest bin looked at); if
-  // their weight does not reach the target, the pass is repeated over all bins.
-  int low_bin = max(0, (int)(ordered_key(m) >> 24) - 2);
-  for (int shift = 24; shift >= 0; shift -= 8) {
-    if (shift != 24) low_bin = 0;
-    for (int i = lane; i < 256; i += 32) whist[warp][i] = 0.f;
-    if (shift != 24) {
-      for (int i = threadIdx.x; i < 256; i += blockDim.x) h64[i] = 0ULL;
-      __syncthreads();
-    }
-    __syncwarp();
-    // one element of every lane: the lanes of a bin are found by comparison with a leader's
-    auto consume = [&](float x, bool valid) {
-      if (shift != 24) {
-        // Below the leading byte the elements still in the range spread over many bins: the
-        // vote below would take a round per distinct bin.  Atomic adds on one histogram of
-        // 64-bit integers instead (weights in fixed point, 40 fraction bits): integer sums do
-        // not depend on their order, so the result stays the same on every run.
-        if (valid) {
-          const unsigned int k = ordered_key(x);
-          if (k >= floor_key && (k & pmask) == prefix) {
-            const unsigned long long w = MASS ? (unsigned long long)(expf((x - m) * invT) * 1099511627776.f) : 1ULL;
-            atomicAdd(h64 + ((k >> shift) & 255u), w);
-          }
-        }
-        return;
-      }
-      int bin = -1;
-      float w = 0.f;
-      if (valid) {
-        const unsigned int k = ordered_key(x);
-        if (k >= floor_key && (k & pmask) == prefix && (int)((k >> shift) & 255u) >= low_bin) {
-          bin = (int)((k >> shift) & 255u);
-          w = MASS ? expf((x - m) * invT) : 1.f;
-        }
-      }
-      unsigned todo = __ballot_sync(0xffffffffu, bin >= 0);
-      while (todo) {
-        const int leader = __ffs(todo) - 1;
-        const int b = __shfl_sync(0xffffffffu, bin, leader);
-        const bool mine = bin == b;
-        const unsigned same = __ballot_sync(0xffffffffu, mine);
-        const float sum = MASS ? warp_sum(mine ? w : 0.f) : (float)__popc(same);   // counting needs no sum
-        if (lane == leader) whist[warp][b] += sum;
-        todo &= ~same;
-      }
-    };
-    // four values per load where the row allows it: a quarter as many trips to L2 in a loop
-    // whose votes keep the loads from overlapping
+  // every element of the row (or of this CTA's part of it), four per load where possible
+  auto for_each = [&](auto&& f) {
     const int V4 = (((size_t)row) & 15) == 0 ? V >> 2 : 0;
     const float4* row4 = reinterpret_cast<const float4*>(row);
-    for (int i0 = 0; i0 < V4; i0 += 4 * blockDim.x) {
-      float4 v[4];
-      bool valid[4];
-#pragma unroll
-      for (int u = 0; u < 4; ++u) {            // four loads in flight before the first vote
-        const int i = i0 + u * blockDim.x + threadIdx.x;
-        valid[u] = i < V4;
-        v[u] = valid[u] ? row4[i] : make_float4(0.f, 0.f, 0.f, 0.f);
-      }
-#pragma unroll
-      for (int u = 0; u < 4; ++u) {
-        consume(v[u].x, valid[u]);
-        consume(v[u].y, valid[u]);
-        consume(v[u].z, valid[u]);
-        consume(v[u].w, valid[u]);
-      }
+    for (int i = threadIdx.x; i < V4; i += blockDim.x) {
+      const float4 v = row4[i];
+      f(v.x); f(v.y); f(v.z); f(v.w);
     }
-    for (int i0 = V4 << 2; i0 < V; i0 += blockDim.x) {
-      const int i = i0 + threadIdx.x;
-      consume(i < V ? row[i] : 0.f, i < V);
-    }
-    __syncthreads();
-    for (int i = threadIdx.x; i < 256; i += blockDim.x) {
-      float v = 0.f;
-      if (shift == 24) { for (int wv = 0; wv < nw; ++wv) v += whist[wv][i]; }
-      else v = MASS ? (float)h64[i] * (1.f / 1099511627776.f) : (float)h64[i];
-      if (CL) pub->hist[pub->parity][i] = v; else hist[i] = v;
-    }
+    for (int i = (V4 << 2) + threadIdx.x; i < V; i += blockDim.x) f(row[i]);
+  };
+  // hist[0..n) = the block's (CL: the cluster's) sum of hist[0..n) as every thread sees it
+  auto exchange = [&](int n) {
     if (CL) {
       const int par = pub->parity;
+      for (int i = threadIdx.x; i < n; i += blockDim.x) pub->hist[par][i] = hist[i];
       sc_barrier();                            // (also a barrier of the CTA)
       const unsigned C = sc_size();
-      for (int i = threadIdx.x; i < 256; i += blockDim.x) {
+      for (int i = threadIdx.x; i < n; i += blockDim.x) {
         float v = 0.f;
         for (unsigned c = 0; c < C; ++c) v += sc_load(&pub->hist[par][i], c);
         hist[i] = v;
@@ -236,16 +172,63 @@ __device__ unsigned int radix_threshold(const float* row, int V, float m, float 
       if (threadIdx.x == 0) pub->parity = par ^ 1;
     }
     __syncthreads();
+  };
+  // ---- leading byte, the three bins at and below the maximum's
+  const int top = (int)(ordered_key(m) >> 24);
+  bool full = true;                            // the leading byte still has to be binned in full
+  {
+    float acc0 = 0.f, acc1 = 0.f, acc2 = 0.f;
+    for_each([&](float x) {
+      const unsigned int k = ordered_key(x);
+      const int d = top - (int)(k >> 24);
+      if (k >= floor_key && d >= 0 && d <= 2) {
+        const float w = MASS ? expf((x - m) * invT) : 1.f;
+        if (d == 0) acc0 += w; else if (d == 1) acc1 += w; else acc2 += w;
+      }
+    });
+    acc0 = block_sum(acc0, red);
+    acc1 = block_sum(acc1, red);
+    acc2 = block_sum(acc2, red);
+    if (threadIdx.x == 0) { hist[0] = acc0; hist[1] = acc1; hist[2] = acc2; }
+    __syncthreads();
+    exchange(3);
+    float cum = 0.f;
+    for (int d = 0; d <= 2 && d <= top; ++d) {
+      if (cum + hist[d] >= target) {
+        prefix = (unsigned int)(top - d) << 24;
+        pmask = 255u << 24;
+        above = cum;
+        full = false;
+        break;
+      }
+      cum += hist[d];
+    }
+    __syncthreads();                           // hist is written again below
+  }
+  for (int shift = full ? 24 : 16; shift >= 0; shift -= 8) {
+    for (int i = threadIdx.x; i < 256; i += blockDim.x) h64[i] = 0ULL;
+    __syncthreads();
+    for_each([&](float x) {
+      const unsigned int k = ordered_key(x);
+      if (k >= floor_key && (k & pmask) == prefix) {
+        const unsigned long long w = MASS ? (unsigned long long)(expf((x - m) * invT) * FX) : 1ULL;
+        atomicAdd(h64 + ((k >> shift) & 255u), w);
+      }
+    });
+    __syncthreads();
+    for (int i = threadIdx.x; i < 256; i += blockDim.x)
+      hist[i] = MASS ? (float)h64[i] * (1.f / FX) : (float)h64[i];
+    __syncthreads();
+    exchange(256);
     if (warp == 0) {
       // the first bin from the top whose weight, added to that of the bins above, reaches the
-      // target.  Lane l takes bins 255 - 8 l down to 248 - 8 l (one thread walking 256 bins is
-      // 256 dependent reads of shared memory, 4 us a pass); only bins above low_bin count, and
-      // low_bin itself is the answer where none of them does.
+      // target (bin 0 where none does).  Lane l takes bins 255 - 8 l down to 248 - 8 l: one
+      // thread walking 256 bins is 256 dependent reads of shared memory, 4 us a pass.
       float hs[8], s = 0.f;
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
         const int b = 255 - 8 * lane - j;
-        hs[j] = b > low_bin ? hist[b] : 0.f;
+        hs[j] = b > 0 ? hist[b] : 0.f;
         s += hs[j];
       }
       float incl = s;
@@ -260,30 +243,22 @@ __device__ unsigned int radix_threshold(const float* row, int V, float m, float 
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
         const int b = 255 - 8 * lane - j;
-        if (b > low_bin && fb < 0) {
+        if (b > 0 && fb < 0) {
           if (cum + hs[j] >= target) { fb = b; fcum = cum; }
           else cum += hs[j];
         }
       }
       const unsigned any = __ballot_sync(0xffffffffu, fb >= 0);
       const int src = any ? __ffs(any) - 1 : 31;
-      const int bin = any ? __shfl_sync(0xffffffffu, fb, src) : low_bin;
+      const int bin = any ? __shfl_sync(0xffffffffu, fb, src) : 0;
       const float all = __shfl_sync(0xffffffffu, incl, 31);
       const float cumv = any ? __shfl_sync(0xffffffffu, fcum, src) : above + all;
       if (lane == 0) {
-        // stopped at the lowest bin looked at without reaching the target: the bins below count too
-        const bool again = low_bin > 0 && bin == low_bin && cumv + hist[bin] < target;
         hist[256] = cumv;
-        hist[257] = __int_as_float(again ? -1 : bin);
+        hist[257] = __int_as_float(bin);
       }
     }
     __syncthreads();
-    if (__float_as_int(hist[257]) < 0) {       // the same pass again over all bins
-      __syncthreads();
-      low_bin = 0;
-      shift += 8;
-      continue;
-    }
     above = hist[256];
     const unsigned int bin = (unsigned int)__float_as_int(hist[257]);
     prefix |= bin << shift;
@@ -301,7 +276,6 @@ sample_kernel(const float* __restrict__ logits, int V, const float* __restrict__
   __shared__ float red_f[33];
   __shared__ int red_i[33];
   __shared__ float hist[258];
-  __shared__ float whist[SAMPLE_THREADS / 32][256];       // a histogram per warp (radix_threshold)
   __shared__ unsigned long long h64[256];
   __shared__ float scan[SAMPLE_THREADS / 32 + 1];
   __shared__ int found;
@@ -319,7 +293,7 @@ sample_kernel(const float* __restrict__ logits, int V, const float* __restrict__
   const float invT = 1.f / T;
   unsigned int floor_key = 0;
   const int k = top_k ? top_k[r] : 0;
-  if (k > 0 && k < V) floor_key = radix_threshold<false, false>(row, V, m, invT, 0u, (float)k, hist, whist, h64);
+  if (k > 0 && k < V) floor_key = radix_threshold<false, false>(row, V, m, invT, 0u, (float)k, hist, red_f, h64);
   const float p = top_p ? top_p[r] : 0.f;
   if (p > 0.f && p < 1.f) {
     float z = 0.f;
@@ -328,7 +302,7 @@ sample_kernel(const float* __restrict__ logits, int V, const float* __restrict__
       if (ordered_key(x) >= floor_key) z += expf((x - m) * invT);
     }
     z = block_sum(z, red_f);
-    floor_key = radix_threshold<true, false>(row, V, m, invT, floor_key, p * z, hist, whist, h64);
+    floor_key = radix_threshold<true, false>(row, V, m, invT, floor_key, p * z, hist, red_f, h64);
   }
   // running sum in index order over the kept elements; thread owns a contiguous chunk
   const int chunk = (V + blockDim.x - 1) / blockDim.x;
@@ -379,7 +353,7 @@ sample_kernel(const float* __restrict__ logits, int V, const float* __restrict__
 // ---------------------------------------------------------------- a row on a cluster of CTAs
 // One CTA per row reads its 128 k logits from L2 a dozen times (maximum, top-k and top-p
 // descents of up to four passes each, sums), at the rate one SM gets from L2: 266 us with top-k
-// and top-p (72 us here, for 8 rows).  Here a row is cut into SC_CLUSTER parts, one per CTA of a cluster; a CTA reads
+// and top-p before the descent was rewritten (53 us here, for 8 rows).  Here a row is cut into SC_CLUSTER parts, one per CTA of a cluster; a CTA reads
 // its part from global memory once and keeps it in shared memory, and the CTAs exchange
 // histograms and sums through distributed shared memory, always added in rank order, so every
 // CTA takes the same decisions and the result is the same on every run.  Same arithmetic per
@@ -419,7 +393,6 @@ sample_cluster_kernel(const float* __restrict__ logits, int V, int part, const f
   __shared__ float red_f[33];
   __shared__ int red_i[33];
   __shared__ float hist[258];
-  __shared__ float whist[SC_THREADS / 32][256];
   __shared__ unsigned long long h64[256];
   __shared__ float scan[SC_THREADS / 32 + 1];
   __shared__ float bcast[2];
@@ -464,7 +437,7 @@ sample_cluster_kernel(const float* __restrict__ logits, int V, int part, const f
   const float invT = 1.f / T;
   unsigned int floor_key = 0;
   const int k = top_k ? top_k[r] : 0;
-  if (k > 0 && k < V) floor_key = radix_threshold<false, true>(sc_part, n, m, invT, 0u, (float)k, hist, whist, h64, &pub);
+  if (k > 0 && k < V) floor_key = radix_threshold<false, true>(sc_part, n, m, invT, 0u, (float)k, hist, red_f, h64, &pub);
   const float p = top_p ? top_p[r] : 0.f;
   if (p > 0.f && p < 1.f) {
     float z = 0.f;
@@ -474,7 +447,7 @@ sample_cluster_kernel(const float* __restrict__ logits, int V, int part, const f
     }
     z = block_sum(z, red_f);
     z = sc_sum(z, &pub, bcast, nullptr);
-    floor_key = radix_threshold<true, true>(sc_part, n, m, invT, floor_key, p * z, hist, whist, h64, &pub);
+    floor_key = radix_threshold<true, true>(sc_part, n, m, invT, floor_key, p * z, hist, red_f, h64, &pub);
   }
   // running sum in index order over the kept elements: a thread owns a contiguous piece of
   // the part, a CTA the part, the ranks follow each other
@@ -557,8 +530,9 @@ extern "C" int gg_sample(const float* logits, int R, int V, const float* tempera
         cudaDeviceGetAttribute(&num_sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || num_sms <= 0)
       num_sms = 148;
   }
-  // (with more rows than clusters fit at once, two CTAs per SM, a CTA per row is as fast: 268
-  // against 283 us for 64 rows, measured before the bin of a pass was chosen by a warp; 8 rows: 266 against 120 us then)
+  // (with more rows than clusters fit at once, two CTAs per SM, a CTA per row is about as fast:
+  // 64 rows with top-k and top-p 158 against 145 us, temperature only 43 against 59; 8 rows: 53 us
+  // on clusters against 120 with a CTA per row)
   if (use_cluster && V >= SC_MIN_V && smem <= 160 * 1024 && R * SC_CLUSTER <= 2 * num_sms) {
     static bool set = false;
     if (!set) {
