@@ -353,7 +353,7 @@ sample_kernel(const float* __restrict__ logits, int V, const float* __restrict__
 // ---------------------------------------------------------------- a row on a cluster of CTAs
 // One CTA per row reads its 128 k logits from L2 a dozen times (maximum, top-k and top-p
 // descents of up to four passes each, sums), at the rate one SM gets from L2: 266 us with top-k
-// and top-p before the descent was rewritten (53 us here, for 8 rows).  Here a row is cut into SC_CLUSTER parts, one per CTA of a cluster; a CTA reads
+// and top-p before the descent was rewritten (43 us here, for 8 rows).  Here a row is cut into SC_CLUSTER parts, one per CTA of a cluster; a CTA reads
 // its part from global memory once and keeps it in shared memory, and the CTAs exchange
 // histograms and sums through distributed shared memory, always added in rank order, so every
 // CTA takes the same decisions and the result is the same on every run.  Same arithmetic per
@@ -451,7 +451,7 @@ sample_cluster_kernel(const float* __restrict__ logits, int V, int part, const f
   }
   // running sum in index order over the kept elements: a thread owns a contiguous piece of
   // the part, a CTA the part, the ranks follow each other
-  const int chunk = (n + SC_THREADS - 1) / SC_THREADS;
+  const int chunk = ((n + SC_THREADS - 1) / SC_THREADS) | 1;      // odd: the lanes' pieces start in different banks
   const int i0 = min(n, (int)threadIdx.x * chunk), i1 = min(n, i0 + chunk);
   float local = 0.f;
   for (int i = i0; i < i1; ++i) {
@@ -531,7 +531,7 @@ extern "C" int gg_sample(const float* logits, int R, int V, const float* tempera
       num_sms = 148;
   }
   // (with more rows than clusters fit at once, two CTAs per SM, a CTA per row is about as fast:
-  // 64 rows with top-k and top-p 158 against 145 us, temperature only 43 against 59; 8 rows: 53 us
+  // 64 rows with top-k and top-p 158 against 145 us, temperature only 43 against 59; 8 rows: 43 us
   // on clusters against 120 with a CTA per row)
   if (use_cluster && V >= SC_MIN_V && smem <= 160 * 1024 && R * SC_CLUSTER <= 2 * num_sms) {
     static bool set = false;

@@ -154,9 +154,28 @@ def attn_prefill(args) -> None:
               flush=True)
 
 
+def sample(args) -> None:
+    """Token selection from float32 logits [batch, vocab]: arg-max, then sampling with a
+    temperature alone, with top-k, with top-p and with both."""
+    B, V = args.batch, args.vocab
+    torch.manual_seed(0)
+    logits = torch.randn(B, V, device="cuda") * 3
+    out = torch.empty(B, dtype=torch.int32, device="cuda")
+    temp = torch.full((B,), 0.8, device="cuda")
+    top_k = torch.full((B,), 50, dtype=torch.int32, device="cuda")
+    top_p = torch.full((B,), 0.9, device="cuda")
+    seeds = torch.arange(B, dtype=torch.int64, device="cuda")
+    draw = torch.zeros(B, dtype=torch.int64, device="cuda")
+    print(f"argmax rows={B} vocab={V}: {_time(lambda i: ops.argmax(logits, out), args.reps):7.1f} us", flush=True)
+    for name, k, p in (("temperature only", None, None), ("top-k 50", top_k, None), ("top-p 0.9", None, top_p),
+                       ("top-k 50 + top-p 0.9", top_k, top_p)):
+        t = _time(lambda i: ops.sample(logits, temp, k, p, seeds, draw, out), args.reps)
+        print(f"sample ({name}) rows={B} vocab={V}: {t:7.1f} us", flush=True)
+
+
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(prog="python -m gollmgo_b200.microbench")
-    ap.add_argument("kernel", choices=["gemm_small_m", "gemm_tc", "attn_decode", "attn_prefill"])
+    ap.add_argument("kernel", choices=["gemm_small_m", "gemm_tc", "attn_decode", "attn_prefill", "sample"])
     ap.add_argument("--tokens", type=int, default=None)
     ap.add_argument("--batch", type=int, default=64)
     ap.add_argument("--context", type=int, default=2048)
@@ -172,7 +191,8 @@ def main(argv=None) -> int:
     args = ap.parse_args(argv)
     if args.tokens is None:
         args.tokens = 8 if args.kernel == "gemm_small_m" else 2048
-    {"gemm_small_m": gemm_small_m, "gemm_tc": gemm_tc, "attn_decode": attn_decode, "attn_prefill": attn_prefill}[args.kernel](args)
+    {"gemm_small_m": gemm_small_m, "gemm_tc": gemm_tc, "attn_decode": attn_decode, "attn_prefill": attn_prefill,
+     "sample": sample}[args.kernel](args)
     return 0
 
 
