@@ -154,6 +154,32 @@ class Attention:
     def fuses_next_norm(self, num_tokens):
         return fuses_norms(num_tokens, self.w_o, self.ctx.act_dtype)
 
+    def _decode(self, qkv, kc, vc, group, batch, out, window, flat_step, fused, table, writes_cache):
+        """The step's single decoded tokens (batch.dec_seqs) against the cache."""
+        ws, n, bt = self.ctx.workspace, batch.num_decode, batch.block_tables[group]
+        if flat_step:
+            # more pairs than CTAs at once: equal ranges of tiles instead of whole slices
+            pieces = ops.attn_decode_flat_pieces(n, self.nh, self.nkv, self.d)
+            ops.attn_decode_flat(qkv, self.qkv_width, kc, vc, bt, batch.bt_stride, batch.cu_q_lens,
+                                 batch.context_lens, batch.dec_seqs, n,
+                                 ws.get("attn_part_o", 1, pieces * 16 * self.d),
+                                 ws.get("attn_part_ml", 1, pieces * 16 * 2),
+                                 ws.get("attn_flat_prefix", 1, n + 1), out, self.nh, self.nkv, self.d,
+                                 self.ctx.page_size, window, self.scale)
+            return
+        splits = decode_splits(n, self._ctas_per_split, self.num_sms, self._cluster_cap, batch.long_context)
+        part_o = ws.get("attn_part_o", 1, n * self.nh * splits * self.d)
+        part_ml = ws.get("attn_part_ml", 1, n * self.nh * splits * 2)
+        if fused:
+            ops.attn_decode_rope(qkv, kc, vc, bt, batch.bt_stride, batch.cu_q_lens, batch.context_lens,
+                                 batch.dec_seqs, n, splits, part_o, part_ml, out, self.nh,
+                                 self.nkv, self.d, self.ctx.page_size, window, self.scale, batch.positions,
+                                 batch.slot_mapping[group], table, writes_cache)
+        else:
+            ops.attn_decode(qkv, self.qkv_width, kc, vc, bt, batch.bt_stride, batch.cu_q_lens,
+                            batch.context_lens, batch.dec_seqs, n, splits,
+                            part_o, part_ml, out, self.nh, self.nkv, self.d, self.ctx.page_size, window, self.scale)
+
     def forward(self, x, batch, cache, writes_cache=True, then=None):
         T = x.shape[0]
         ws = self.ctx.workspace
@@ -186,32 +212,8 @@ class Attention:
                              allow_mma=ATTN_POLICY != "general",
                              tile128_seq=batch.tile128_seq, tile128_q0=batch.tile128_q0,
                              num_tiles128=batch.num_tiles128, allow_tc=ATTN_POLICY == "auto")
-        if batch.num_decode and flat_step:
-            # more pairs than CTAs at once: equal ranges of tiles instead of whole slices
-            n = batch.num_decode
-            pieces = ops.attn_decode_flat_pieces(n, self.nh, self.nkv, self.d)
-            ops.attn_decode_flat(qkv, self.qkv_width, kc, vc, bt, batch.bt_stride, batch.cu_q_lens,
-                                 batch.context_lens, batch.dec_seqs, n,
-                                 ws.get("attn_part_o", 1, pieces * 16 * self.d),
-                                 ws.get("attn_part_ml", 1, pieces * 16 * 2),
-                                 ws.get("attn_flat_prefix", 1, n + 1), out, self.nh, self.nkv, self.d,
-                                 self.ctx.page_size, window, self.scale)
-        elif batch.num_decode:
-            splits = decode_splits(batch.num_decode, self._ctas_per_split, self.num_sms, self._cluster_cap,
-                                   batch.long_context)
-            part_o = ws.get("attn_part_o", 1, batch.num_decode * self.nh * splits * self.d)
-            part_ml = ws.get("attn_part_ml", 1, batch.num_decode * self.nh * splits * 2)
-        if batch.num_decode and flat_step:
-            pass
-        elif batch.num_decode and fused:
-            ops.attn_decode_rope(qkv, kc, vc, bt, batch.bt_stride, batch.cu_q_lens, batch.context_lens,
-                                 batch.dec_seqs, batch.num_decode, splits, part_o, part_ml, out, self.nh,
-                                 self.nkv, self.d, self.ctx.page_size, window, self.scale, batch.positions,
-                                 batch.slot_mapping[group], table, writes_cache)
-        elif batch.num_decode:
-            ops.attn_decode(qkv, self.qkv_width, kc, vc, bt, batch.bt_stride, batch.cu_q_lens,
-                            batch.context_lens, batch.dec_seqs, batch.num_decode, splits,
-                            part_o, part_ml, out, self.nh, self.nkv, self.d, self.ctx.page_size, window, self.scale)
+        if batch.num_decode:
+            self._decode(qkv, kc, vc, group, batch, out, window, flat_step, fused, table, writes_cache)
         y = ws.get("mixer_out", T, self.hidden)
         return linear(out, self.w_o, y, then)
 
