@@ -173,6 +173,44 @@ class CacheManager:
             short = max(short, (want - have) - free)
         return max(short, 0)
 
+    def pages_delta(self, req_id, n_tokens: int) -> List[Tuple[int, int]]:
+        """Per group (taken, given back): the pages that appending the next n_tokens of the
+        request takes from the group's pool, and the pages behind a window that go back to it
+        first.  ``append`` succeeds iff taken <= free + given back in every group.  A request
+        that is not admitted (or ``None``) holds nothing yet.  This is what a scheduler plans
+        with: it never redoes the page arithmetic of a group itself."""
+        rc = self.requests.get(req_id) if req_id is not None else None
+        out = []
+        for gi in range(len(self.groups)):
+            have = len(rc.pages[gi]) if rc else 0
+            held = rc.num_tokens if rc else 0
+            want = -(-(held + n_tokens) // self.page_size)
+            out.append((max(want - have, 0), len(self._behind_window(rc, gi)) if rc else 0))
+        return out
+
+    def pages_held(self, req_id) -> List[int]:
+        """Per group, how many pages the request holds now (what freeing it gives back)."""
+        rc = self.requests.get(req_id)
+        if rc is None:
+            return [0] * len(self.groups)
+        return [sum(1 for p in pages if p >= 0) for pages in rc.pages]
+
+    def free_pages_per_group(self) -> List[int]:
+        return [g.pool.num_free for g in self.groups]
+
+    def capacity_tokens(self, portion: int = 1) -> Optional[int]:
+        """Most tokens one request can ever hold: the pool of the smallest group that keeps
+        every key.  A group with a window only has to hold the window and one step's portion
+        (its older pages go back as the request grows); None = no group sets a limit (every
+        group has a window that fits, or the model keeps no pages at all)."""
+        limit = None
+        for g in self.groups:
+            pool = g.pool.num_pages * self.page_size
+            if g.need.window is not None and pool >= g.need.window + portion + 2 * self.page_size:
+                continue
+            limit = pool if limit is None else min(limit, pool)
+        return limit
+
     def append(self, req_id, n_tokens: int) -> Appended:
         """Make room for the next n_tokens of the request in every group, all or
         nothing; returns where they go.  Pages behind a window are given back first."""

@@ -136,27 +136,34 @@ class BatchBuilder:
         """build() for a step in which every entry brings one token and wants its logits: the
         per-sequence arrays are packed by native code (csrc/host_pack.cu) from the cache
         manager's flat tables; the same layout and the same result as the general path."""
-        from ..csrc import ops
-        cache, ps, G = self.cache, self.cache.page_size, self.G
+        cache = self.cache
         ids = [e.request_id for e in entries]
         B = len(ids)
         if len(set(ids)) != B:
             raise ValueError("a request appears twice in one step")
+        Bp = fixed_seqs if fixed_seqs is not None else B
+        if Bp < B:
+            raise ValueError("more sequences than the fixed layout holds")
         starts: List[int] = []
         try:
             for rid in ids:
                 starts.append(cache.append_one(rid))
+            return self._pack_decode(entries, ids, starts, Bp, fixed_stride, static_dev)
         except Exception:
-            for rid, s0 in zip(ids, starts):           # all or nothing
+            # all or nothing: whatever fails from here on (no pages left, a layout that does not
+            # fit, the native packer refusing its arguments) leaves the cache as it was
+            for rid, s0 in zip(ids, starts):
                 cache.rollback(rid, s0)
             raise
+
+    def _pack_decode(self, entries, ids, starts, Bp, fixed_stride, static_dev) -> StepBatch:
+        from ..csrc import ops
+        cache, ps, G = self.cache, self.cache.page_size, self.G
+        B = len(ids)
         reqs = cache.requests
         rcs = [reqs[rid] for rid in ids]
         slots = [rc.state_slot for rc in rcs]
         max_pages = max(len(p) for rc in rcs for p in rc.pages) if G else 1
-        Bp = fixed_seqs if fixed_seqs is not None else B
-        if Bp < B:
-            raise ValueError("more sequences than the fixed layout holds")
         stride = fixed_stride if fixed_stride is not None else max(1, max_pages)
         if stride < max_pages:
             raise ValueError(f"a sequence holds {max_pages} pages, the fixed block table has {stride}")
@@ -227,7 +234,7 @@ class BatchBuilder:
         ids = [e.request_id for e in entries]
         if len(set(ids)) != len(ids):
             raise ValueError("a request appears twice in one step")
-        # all-or-nothing: check room for every entry before touching the cache
+        # what can be checked without the cache is checked before it is touched
         for e in entries:
             if len(e.tokens) == 0:
                 raise ValueError(f"request {e.request_id!r}: a step entry needs at least one token")
@@ -235,15 +242,25 @@ class BatchBuilder:
                 if not (0 <= w < len(e.tokens)):
                     raise ValueError(f"request {e.request_id!r}: wanted place {w} is outside its "
                                      f"{len(e.tokens)} tokens")
+            if e.token_src >= 0 and len(e.tokens) != 1:
+                raise ValueError("only a single decoded token can come from the device")
+        if fixed_seqs is not None and fixed_seqs < len(entries):
+            raise ValueError("more sequences than the fixed layout holds")
         appended = []
         try:
             for e in entries:
                 appended.append(cache.append(e.request_id, len(e.tokens)))
+            return self._pack(entries, ids, appended, fixed_seqs, fixed_stride, static_dev)
         except Exception:
-            # undo: what was appended in this call is rolled back by truncation
+            # all or nothing: whatever fails from here on (no pages left, a block table wider than
+            # the fixed layout, a buffer that is too small) leaves the cache as it was; what was
+            # appended in this call is rolled back by truncation
             for e, a in zip(entries, appended):
                 cache.rollback(e.request_id, a.start)
             raise
+
+    def _pack(self, entries, ids, appended, fixed_seqs, fixed_stride, static_dev) -> StepBatch:
+        cache, ps, G = self.cache, self.cache.page_size, self.G
         B = len(entries)
         q_lens = [len(e.tokens) for e in entries]
         q_starts = [a.start for a in appended]
@@ -257,8 +274,6 @@ class BatchBuilder:
         dec = [b for b in range(B) if q_lens[b] == 1]
         max_pages = max(len(cache.block_table(e.request_id, g)) for e in entries for g in range(G)) if G else 1
         Bp = fixed_seqs if fixed_seqs is not None else B
-        if Bp < B:
-            raise ValueError("more sequences than the fixed layout holds")
         stride = fixed_stride if fixed_stride is not None else max(1, max_pages)
         if stride < max_pages:
             raise ValueError(f"a sequence holds {max_pages} pages, the fixed block table has {stride}")
@@ -290,8 +305,6 @@ class BatchBuilder:
             base = 0
             for e, n in zip(entries, q_lens):
                 if e.token_src >= 0:
-                    if n != 1:
-                        raise ValueError("only a single decoded token can come from the device")
                     h[lay.token_src + base] = e.token_src
                 base += n
             has_src = True

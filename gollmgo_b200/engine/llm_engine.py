@@ -6,6 +6,11 @@ Shape of the loop and of the public calls follows the reference's ServingEngine
 670-691 Enqueue, 800-823 cleanup) and its Request{ID, TokenIDs, MaxTokens}
 (internal/engine/engine.go:7-11); it runs in the caller's thread instead of a
 goroutine: ``step()`` is one turn of the loop, ``generate()`` runs it to the end.
+
+A step that fails (the runner raises, or a kernel reports that it gave up on a
+bounded wait) ends the sequences that took part in it with an error result and
+gives their pages and state slots back; the queue behind them is served as
+before (internal/engine/serving.go:199-202, 646-666 recoverFromStepFailure).
 """
 from __future__ import annotations
 
@@ -31,6 +36,7 @@ class TokenResult:
     token_id: int
     finished: bool
     finish_reason: Optional[str] = None
+    error: Optional[str] = None          # set on the last result of a request whose step failed (token_id -1)
 
 
 @dataclass
@@ -43,6 +49,7 @@ class RequestOutput:
     e2e_s: Optional[float] = None
     token_times: List[float] = field(default_factory=list)
     preemptions: int = 0
+    error: Optional[str] = None          # finish_reason "error": what failed
 
 
 @dataclass
@@ -53,34 +60,48 @@ class EngineStats:
     generated_tokens: int = 0
     preemptions: int = 0
     pages_high_water: int = 0
+    failed_steps: int = 0
+    failed_requests: int = 0
+    batch_sum: int = 0                   # sequences over all steps (mean batch = batch_sum / steps)
 
 
 class Engine:
     def __init__(self, model: Optional[str] = None, *, config: Optional[dict] = None,
                  weights_seed: Optional[int] = None, engine_config: Optional[EngineConfig] = None,
-                 **engine_options):
+                 runner=None, sampler=None, **engine_options):
         """``model``: a folder with config.json and *.safetensors.  Or ``config`` (a
         config.json dict) with ``weights_seed`` for random weights made on the device.
-        Engine options (EngineConfig fields) may be given as keywords."""
+        Engine options (EngineConfig fields) may be given as keywords.
+
+        ``runner`` and ``sampler`` replace the step function and the token selection with
+        objects of the caller's (the runner: ``spec``, ``cache``, ``max_model_len``, ``device``,
+        ``last_tokens``, ``step(entries)``, ``check_kernels()``; the sampler: ``sample_async``,
+        ``wait``): the loop, the scheduler and the failure handling can then be driven without
+        a device, which is how the tests inject a step that fails."""
         ecfg = engine_config or EngineConfig(**engine_options)
-        if model is not None:
+        if runner is not None:
+            self.runner = runner
+        elif model is not None:
             self.runner = ModelRunner(read_config_json(model), ecfg, weights=model)
         elif config is not None:
             self.runner = ModelRunner(config, ecfg, weights_seed=weights_seed if weights_seed is not None else 0)
         else:
             raise ValueError("give a model folder, or a config with weights_seed")
-        from ..sampling.sampler import Sampler
         self.ecfg = ecfg
         self.spec = self.runner.spec
         self.scheduler = Scheduler(ecfg, self.runner.cache, self.runner.max_model_len)
-        self.sampler = Sampler(self.runner.device, max(ecfg.max_batch_size, 1), self.runner.last_tokens)
+        if sampler is not None:
+            self.sampler = sampler
+        else:
+            from ..sampling.sampler import Sampler
+            self.sampler = Sampler(self.runner.device, max(ecfg.max_batch_size, 1), self.runner.last_tokens)
         self._inflight = None
         self.sequences: Dict[str, Sequence] = {}
         self.stats = EngineStats()
         self._next_id = 0
         self._seed_rng = random.Random()
         self._stopped = False
-        if ecfg.cuda_graphs and ecfg.capture_at_start:
+        if ecfg.cuda_graphs and ecfg.capture_at_start and hasattr(self.runner, "capture_graphs"):
             self.runner.capture_graphs()
 
     # ------------------------------------------------------------------ requests
@@ -123,6 +144,7 @@ class Engine:
         plan: SchedulerOutput = self.scheduler.schedule()
         self.stats.preemptions += len(plan.preempted)
         launched = None
+        results: List[TokenResult] = []
         if plan.scheduled:
             entries, samplers = [], []
             for s in plan.scheduled:
@@ -138,9 +160,20 @@ class Engine:
                 entries.append(StepEntry(seq.id, toks, [s.num_tokens - 1] if s.samples else [], src))
                 if s.samples:
                     samplers.append(seq)
-            logits = self.runner.step(entries)
-            handle = self.sampler.sample_async(logits, [q.params for q in samplers],
-                                               [len(q.output) for q in samplers])
+            try:
+                logits = self.runner.step(entries)
+                handle = self.sampler.sample_async(logits, [q.params for q in samplers],
+                                                   [len(q.output) for q in samplers])
+            except Exception as exc:          # noqa: BLE001  (whatever the step function raises)
+                # the step did not run: first hand out what the step before produced (those
+                # tokens are good), then end the sequences of this one
+                inflight, self._inflight = self._inflight, None
+                try:
+                    results = self._resolve(inflight)
+                except Exception as exc2:     # noqa: BLE001
+                    results = self._fail(inflight[2], exc2)
+                results += self._fail([s.seq for s in plan.scheduled], exc)
+                return results
             for s in plan.scheduled:
                 self.scheduler.advance(s)
             for row, seq in enumerate(samplers):
@@ -149,24 +182,64 @@ class Engine:
                 self.scheduler.token_sampled(seq)
                 if len(seq.output) >= seq.params.max_tokens:
                     self.scheduler.finish(seq, "length")          # known without the token's value
-            launched = (handle, samplers)
+            launched = (handle, samplers, [s.seq for s in plan.scheduled])
             st = self.stats
             st.steps += 1
+            st.batch_sum += len(plan.scheduled)
             st.prefill_tokens += plan.prefill_tokens
             st.decode_tokens += plan.decode_tokens
-            st.pages_high_water = max(g.pool.high_water for g in self.runner.cache.groups)
+            st.pages_high_water = max((g.pool.high_water for g in self.runner.cache.groups), default=0)
         elif self._inflight is None and self.scheduler.has_work() and not plan.preempted:
             raise RuntimeError("scheduler made no progress: the page pool is too small for the "
                                "request at the head of the queue")
-        results = self._resolve(self._inflight)
-        self._inflight = launched
+        inflight, self._inflight = self._inflight, launched
+        try:
+            results = self._resolve(inflight)
+        except Exception as exc:              # noqa: BLE001
+            # the step before turned out to have failed (a kernel gave up on a bounded wait, the
+            # copy of its tokens did not arrive).  The step launched in this turn read its cache
+            # and its tokens, so it is void as well.
+            results = self._fail(inflight[2] + (launched[2] if launched else []), exc)
+            self._drain(launched)
+            self._inflight = None
+        return results
+
+    def _drain(self, launched) -> None:
+        """Wait for a launched step whose results will not be used."""
+        if launched is None:
+            return
+        try:
+            self.sampler.wait(launched[0])
+            self.runner.check_kernels()
+        except Exception:                     # noqa: BLE001  (it is void either way)
+            pass
+
+    def _fail(self, seqs, exc) -> List[TokenResult]:
+        """End the sequences of a failed step: placeholders of tokens that will never be read
+        are dropped, pages and state slots go back, each gets one last result that carries the
+        error.  A sequence that had ended already with every token known is left alone."""
+        msg = f"{type(exc).__name__}: {exc}"
+        self.stats.failed_steps += 1
+        results = []
+        seen = set()
+        for seq in seqs:
+            if seq.id in seen or (seq.finished and seq.resolved == len(seq.output)):
+                continue
+            seen.add(seq.id)
+            del seq.output[seq.resolved:]
+            seq.dropped = True
+            seq.error = msg
+            seq.num_computed = 0
+            self.scheduler.finish(seq, "error")
+            self.stats.failed_requests += 1
+            results.append(TokenResult(seq.request_id, -1, True, "error", msg))
         return results
 
     def _resolve(self, inflight) -> List[TokenResult]:
         """Read the tokens of a launched step and settle its sequences."""
         if inflight is None:
             return []
-        handle, samplers = inflight
+        handle, samplers = inflight[0], inflight[1]
         tokens = self.sampler.wait(handle)
         self.runner.check_kernels()
         now = time.perf_counter()
@@ -188,9 +261,9 @@ class Engine:
                 reason = "stop"
                 del seq.output[idx + 1:]       # a placeholder of the step launched since
                 seq.dropped = True
-                if not seq.finished:
-                    self.scheduler.finish(seq, "stop")
-                seq.finish_reason = "stop"
+                # wherever it is by now: running, ended by length at launch, or back in the
+                # queue because it was preempted while this token was on its way
+                self.scheduler.finish(seq, "stop")
             elif seq.resolved >= seq.params.max_tokens:
                 reason = "length"
             results.append(TokenResult(seq.request_id, tok, reason is not None, reason))
@@ -237,7 +310,7 @@ class Engine:
         return RequestOutput(seq.request_id, list(seq.prompt), list(seq.output), seq.finish_reason,
                              (seq.first_token_at - seq.created_at) if seq.first_token_at else None,
                              (seq.last_token_at - seq.created_at) if seq.last_token_at else None,
-                             list(seq.token_times), seq.preemptions)
+                             list(seq.token_times), seq.preemptions, seq.error)
 
     def stop(self) -> None:
         """Finish every live request (reference: ServingEngine.Stop, serving.go:693-709)."""

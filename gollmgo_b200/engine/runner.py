@@ -132,9 +132,27 @@ class ModelRunner:
         logits [wanted places, vocab] on the device, in the order of the entries
         and of each entry's ``want``."""
         self._validate(entries)
-        for e in entries:
-            if e.request_id not in self.cache.requests:
-                self.cache.admit(e.request_id)
+        admitted, starts = [], {}
+        try:
+            for e in entries:
+                if e.request_id not in self.cache.requests:
+                    self.cache.admit(e.request_id)
+                    admitted.append(e.request_id)
+                starts[e.request_id] = self.cache.num_tokens(e.request_id)
+            return self._run(entries)
+        except Exception:
+            # a step that fails leaves nothing behind: no token of it counts as cached (what a
+            # kernel may have written lies beyond every request's count and is overwritten by
+            # the tokens that come there next), and requests it admitted are gone again
+            for rid, n in starts.items():
+                if rid in self.cache.requests and self.cache.num_tokens(rid) > n:
+                    self.cache.rollback(rid, n)
+            for rid in admitted:
+                if rid in self.cache.requests:
+                    self.cache.free(rid)
+            raise
+
+    def _run(self, entries: Sequence[StepEntry]) -> torch.Tensor:
         decode_only = all(len(e.tokens) == 1 and list(e.want) == [0] for e in entries)
         # a step while some live request holds a long context is a step of its own kind: parts
         # may choose differently for it (the attention's count of slices), so it has graphs of its own

@@ -73,14 +73,18 @@ class Scheduler:
         self.num_preemptions = 0
 
     # ------------------------------------------------------------------ queue
-    def pool_tokens(self) -> int:
-        return self.cache.num_pages * self.cache.page_size
+    def capacity_tokens(self) -> int:
+        """Most tokens one request may hold: the model's longest sequence, and what the
+        cache manager says a single request can ever keep (it knows which groups slide)."""
+        portion = min(self.cfg.prefill_chunk_size or self.cfg.max_token_budget, self.cfg.max_token_budget)
+        cap = self.cache.capacity_tokens(portion)
+        return self.max_model_len if cap is None else min(self.max_model_len, cap)
 
     def add(self, seq: Sequence) -> None:
         if self.cfg.max_queue_depth > 0 and len(self.waiting) >= self.cfg.max_queue_depth:
             raise QueueFull(f"queue is full: depth {len(self.waiting)}")
         need = len(seq.prompt) + seq.params.max_tokens
-        limit = min(self.max_model_len, self.pool_tokens())
+        limit = self.capacity_tokens()
         if not seq.prompt:
             raise RequestTooLong("a request needs at least one prompt token")
         if need > limit:
@@ -92,13 +96,6 @@ class Scheduler:
         return bool(self.waiting or self.running)
 
     # ------------------------------------------------------------------ pages
-    def _pages_for(self, seq: Sequence, n: int) -> int:
-        """Pages the next n tokens of an admitted sequence take beyond what it holds
-        (the largest need over the cache groups)."""
-        ps = self.cache.page_size
-        held = -(-seq.num_computed // ps)
-        return -(-(seq.num_computed + n) // ps) - held
-
     def _preempt(self, seq: Sequence, out: SchedulerOutput) -> None:
         seq.transition(SeqState.PREEMPTED)
         seq.num_computed = 0
@@ -118,29 +115,42 @@ class Scheduler:
         cfg = self.cfg
         budget = cfg.max_token_budget
         chunk_cap = cfg.prefill_chunk_size or (1 << 30)
-        free = self.cache.min_free_pages()
+        # Free pages per cache group as this plan uses them up.  What a portion takes and what a
+        # sliding group gives back first is asked of the cache manager (pages_delta), in the order
+        # in which the step will append, so a plan that is accepted here is one the cache accepts.
+        free: List[int] = self.cache.free_pages_per_group()
         planned: List[Scheduled] = []
+        deltas: Dict[int, list] = {}                     # seq id -> its (taken, given back) per group
         planned_new: List[Sequence] = []                # admitted in this step (each takes a state slot)
+
+        def fits(delta) -> bool:
+            return all(take <= f + back for (take, back), f in zip(delta, free))
+
+        def book(delta, sign: int) -> None:
+            for g, (take, back) in enumerate(delta):
+                free[g] -= sign * (take - back)
 
         def fits_or_preempt(seq: Sequence, n: int) -> bool:
             """Make room for n tokens of seq by preempting later-admitted sequences
             (never an earlier one).  False if seq itself had to go."""
-            nonlocal free
-            while self._pages_for(seq, n) > free:
+            delta = self.cache.pages_delta(seq.id, n)
+            while not fits(delta):
                 victim_id = self.admit_order[-1]
                 victim = self.running[victim_id]
                 # a victim already planned in this step loses its plan
                 for i, s in enumerate(planned):
                     if s.seq is victim:
-                        free += self._pages_for(victim, s.num_tokens)
+                        book(deltas.pop(victim.id), -1)
                         planned.pop(i)
                         break
-                held = -(-victim.num_computed // self.cache.page_size)
+                held = self.cache.pages_held(victim.id)
                 self._preempt(victim, out)
-                free += held
+                for g, h in enumerate(held):
+                    free[g] += h
                 if victim is seq:
                     return False
-            free -= self._pages_for(seq, n)
+            book(delta, +1)
+            deltas[seq.id] = delta
             return True
 
         # 1. decoding sequences, oldest first, one token each
@@ -172,9 +182,10 @@ class Scheduler:
             if any(seq is p for p in out.preempted):
                 break                                   # just preempted: not in the same step
             n = min(seq.remaining, chunk_cap, budget)
-            need = -(-n // self.cache.page_size)
+            delta = self.cache.pages_delta(None, n)
             reserve = len(self.running)                 # one more page for everyone who is running
-            if need + reserve > free or self.cache.slots.num_free <= len(planned_new):
+            room = all(take + reserve <= f for (take, _), f in zip(delta, free))
+            if not room or self.cache.slots.num_free <= len(planned_new):
                 if cfg.strict_fcfs:
                     break
                 skipped.append(self.waiting.popleft())
@@ -184,7 +195,8 @@ class Scheduler:
             self.running[seq.id] = seq
             self.admit_order.append(seq.id)
             planned_new.append(seq)
-            free -= need
+            book(delta, +1)
+            deltas[seq.id] = delta
             planned.append(Scheduled(seq, n))
             budget -= n
         for seq in reversed(skipped):
@@ -210,7 +222,15 @@ class Scheduler:
             seq.transition(SeqState.DECODING)
 
     def finish(self, seq: Sequence, reason: str) -> None:
+        """End a sequence wherever it is: running, or back in the queue after a preemption
+        (its last token, still on the device when it was preempted, may be the one that ends
+        it; its pages are gone already).  Finishing twice only changes the reason."""
         seq.finish_reason = reason
+        if seq.state is SeqState.FINISHED:
+            return
+        if seq.state in (SeqState.WAITING, SeqState.PREEMPTED):
+            self.waiting = deque(s for s in self.waiting if s is not seq)
+            seq.state = SeqState.WAITING
         seq.transition(SeqState.FINISHED)
         self.running.pop(seq.id, None)
         if seq.id in self.admit_order:

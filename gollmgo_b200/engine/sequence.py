@@ -3,7 +3,9 @@
 States and transitions are the reference's (internal/scheduler/sequence.go:13-45):
 WAITING -> PREFILLING (-> itself for every further portion) -> DECODING ->
 FINISHED, and DECODING -> PREEMPTED -> WAITING; here a sequence can also be
-preempted while it is still prefilling.
+preempted while it is still prefilling, and a sequence that waits (again) for
+admission can finish: a token of its that was still on the device when it was
+preempted may turn out to end it, and a failed step ends what it held.
 """
 from __future__ import annotations
 
@@ -26,7 +28,7 @@ class SeqState(enum.Enum):
 
 
 _VALID = {
-    SeqState.WAITING: {SeqState.PREFILLING},
+    SeqState.WAITING: {SeqState.PREFILLING, SeqState.FINISHED},
     SeqState.PREFILLING: {SeqState.PREFILLING, SeqState.DECODING, SeqState.PREEMPTED, SeqState.FINISHED},
     SeqState.DECODING: {SeqState.FINISHED, SeqState.PREEMPTED},
     SeqState.PREEMPTED: {SeqState.WAITING},
@@ -56,6 +58,7 @@ class Sequence:
         self.resolved = 0                  # tokens of `output` whose value the host knows
         self.pending_row = -1              # row of the unknown token in the sampler's device buffer
         self.dropped = False               # ended by an end-of-sequence token; later samples are void
+        self.error: Optional[str] = None   # why it ended, if a step it took part in failed
 
     @property
     def tokens(self) -> List[int]:

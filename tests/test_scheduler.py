@@ -201,3 +201,70 @@ def test_without_strict_fcfs_a_request_that_does_not_fit_is_passed_over():
     assert [s.id for s in sched.waiting] == [1]
     drain(sched, cache)
     assert cache.free_pages() == 6
+
+
+def make_groups(needs, num_pages, page, **cfg):
+    ecfg = EngineConfig(block_size=page, num_blocks=num_pages, **cfg)
+    cache = CacheManager(needs, page, num_pages, max_requests=16)
+    return Scheduler(ecfg, cache, max_model_len=10_000), cache
+
+
+def test_a_group_with_a_window_is_planned_by_what_the_cache_manager_says():
+    """Every layer slides (window 8, pages of 4 tokens, 7 pages): a request far longer than the
+    pool fits, because pages behind the window go back as it grows; the plan never asks the
+    cache for more than it can give (run_step would raise OutOfPages), and two requests share
+    the small pool by preemption where they must."""
+    sched, cache = make_groups([PagedKVNeed(1, 8, 8)], 7, 4, prefill_chunk_size=4, max_token_budget=8)
+    a, b = seq(0, 30, max_tokens=40), seq(1, 9, max_tokens=25)
+    sched.add(a), sched.add(b)                   # 70 and 34 tokens in a pool of 28
+    drain(sched, cache)
+    assert a.finished and b.finished and len(a.output) == 40 and len(b.output) == 25
+    assert cache.free_pages() == 7 and not cache.requests
+    # the same outputs as on a pool where nothing is ever short
+    sched2, cache2 = make_groups([PagedKVNeed(1, 8, 8)], 200, 4, prefill_chunk_size=4, max_token_budget=8)
+    a2, b2 = seq(0, 30, max_tokens=40), seq(1, 9, max_tokens=25)
+    sched2.add(a2), sched2.add(b2)
+    drain(sched2, cache2)
+    assert (a.output, b.output) == (a2.output, b2.output) and sched2.num_preemptions == 0
+
+
+def test_the_group_that_keeps_every_key_sets_the_limit_beside_one_that_slides():
+    needs = [PagedKVNeed(1, 8, 8), PagedKVNeed(1, 8, None)]
+    sched, cache = make_groups(needs, 10, 4, prefill_chunk_size=4, max_token_budget=8)
+    assert len(cache.groups) == 2 and sched.capacity_tokens() == 40
+    with pytest.raises(RequestTooLong):
+        sched.add(seq(0, 30, max_tokens=11))
+    seqs = [seq(1, 20, max_tokens=20), seq(2, 7, max_tokens=12), seq(3, 15, max_tokens=9)]
+    for s in seqs:
+        sched.add(s)
+    drain(sched, cache)
+    assert all(s.finished for s in seqs) and sched.num_preemptions > 0
+    assert [g.pool.num_free for g in cache.groups] == [10, 10]
+
+
+def test_a_model_without_pages_is_never_short_of_them():
+    from gollmgo_b200.cache import FixedStateNeed
+    sched, cache = make_groups([FixedStateNeed((4,))], 1, 4, prefill_chunk_size=4, max_token_budget=8)
+    assert not cache.groups and sched.capacity_tokens() == 10_000
+    seqs = [seq(i, 50 + i, max_tokens=30) for i in range(3)]
+    for s in seqs:
+        sched.add(s)
+    drain(sched, cache)
+    assert all(s.finished for s in seqs) and sched.num_preemptions == 0
+
+
+def test_finishing_a_sequence_that_waits_again_after_a_preemption():
+    sched, cache = make(num_pages=4, page=4, prefill_chunk_size=0)
+    a, b = seq(0, 7, max_tokens=8), seq(1, 4, max_tokens=8)
+    sched.add(a), sched.add(b)
+    for _ in range(40):
+        out = run_step(sched, cache)
+        if out.preempted:
+            break
+    assert b.state is SeqState.WAITING and sched.waiting[0] is b
+    sched.finish(b, "stop")
+    assert b.finished and b.finish_reason == "stop" and not sched.waiting
+    sched.finish(b, "abort")                     # twice: only the reason changes
+    assert b.finished and b.finish_reason == "abort"
+    drain(sched, cache)
+    assert a.finished and cache.free_pages() == 4
