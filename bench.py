@@ -101,6 +101,57 @@ def prefill_flops(c, L, T):
     return 2.0 * T * L * per_layer + L * 2.0 * 2.0 * nh * d * T * T / 2 + 2.0 * H * c["vocab_size"]
 
 
+def reference_arm(args) -> int:
+    """The same metric on the reference: its five CUDA files built as they are and driven
+    through their C API (baseline/reference_arm.py; nothing of gollmgo_b200 is imported)."""
+    sys.path.insert(0, os.path.join(ROOT, "baseline"))
+    import reference_arm as ra
+    if args.gpus != 1:
+        print(json.dumps({"impl": "reference", "unavailable": "the reference's engine runs on one GPU"}))
+        return 0
+    W, K, B = max(args.warmup, 3), max(args.steps, 1), args.batch
+    cfg = dict(LLAMA_3_1_8B)
+    L_full = cfg["num_hidden_layers"]
+    cfg["num_hidden_layers"] = L = args.layers or L_full
+    try:
+        r = ra.run_bench(cfg, B, CONTEXT, K, W, PREFILL_TOKENS, points=() if args.skip_points else (1, 64),
+                         clock_sampler=ClockSampler)
+    except ra.Unavailable as exc:
+        print(json.dumps({"impl": "reference", "unavailable": str(exc).replace("\n", " ")[:400]}))
+        return 0
+    pk = peaks()
+    ms = r["ms_per_step"]
+    ctx_mean = CONTEXT + W + (K + 1) / 2
+    bytes_step = layer_weight_bytes(cfg, L) + kv_bytes(cfg, L, [ctx_mean] * B)
+    achieved = bytes_step / (ms / 1e3) / 1e9
+    pf_ms = r["prefill_ms"]
+    line = {
+        "metric": "decode tokens/s (Llama-3.1-8B shape, batch %d, context %d)" % (B, CONTEXT),
+        "value": round(B / (ms / 1e3), 1), "unit": "tokens/s", "n_gpus": 1, "steps": K, "warmup": W,
+        "ms_per_step": round(ms, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16", "data": "synthetic (random weights, uniform random token ids)", "impl": "reference",
+        "config": {"model": "Llama-3.1-8B shape", "layers": L, "layers_of_configuration": L_full,
+                   "hidden_size": cfg["hidden_size"], "heads": cfg["num_attention_heads"],
+                   "kv_heads": cfg["num_key_value_heads"], "head_dim": cfg["head_dim"],
+                   "intermediate_size": cfg["intermediate_size"], "vocab_size": cfg["vocab_size"],
+                   "global_batch": B, "seq_len": CONTEXT, "context_start": CONTEXT, "decode_steps": K,
+                   "parallelism": "single GPU", "max_seq_len": r["max_seq_len"],
+                   "api": "gollmgo_model_forward_prefill + gollmgo_model_forward_paged (C API, ctypes)",
+                   "l2": "inputs larger than L2 (weights 15 GB per step)", "peaks": pk["source"]},
+        "e2e": {"value": round(B / r["wall_per_step"], 1), "unit": "tokens/s",
+                "h2d_bytes_per_step": r["h2d_bytes_per_step"], "d2h_bytes_per_step": r["d2h_bytes_per_step"]},
+        "clocks": r["clocks"],
+        "prefill": {"value": round(PREFILL_TOKENS / (pf_ms / 1e3), 1), "tokens": PREFILL_TOKENS,
+                    "ms": round(pf_ms, 3),
+                    "frac": round(prefill_flops(cfg, L, PREFILL_TOKENS) / (pf_ms / 1e3) / (pk["bf16_tflops"] * 1e12), 4)},
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
+                     "frac": round(achieved / pk["hbm_gbs"], 4)},
+        "points": r["points"],
+    }
+    print(json.dumps(line))
+    return 0
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -112,10 +163,7 @@ def main() -> int:
     ap.add_argument("--skip-points", action="store_true")
     args = ap.parse_args()
     if args.impl == "reference":
-        print(json.dumps({"impl": "reference", "unavailable":
-                          "TensorGreed/gollmgo is a Go program with CUDA libraries behind cgo: pip finds "
-                          "neither setup.py nor pyproject.toml, and no Go toolchain is in this image"}))
-        return 0
+        return reference_arm(args)
     if args.gpus != 1:
         print(json.dumps({"error": "this engine runs on one GPU; --gpus must be 1", "n_gpus": args.gpus}))
         return 2

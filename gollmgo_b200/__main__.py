@@ -143,27 +143,65 @@ def cmd_bench(argv) -> int:
     ap.add_argument("--output-len", type=int, default=128)
     ap.add_argument("--warmup-requests", type=int, default=0)
     ap.add_argument("--repetitions", type=int, default=1)
+    ap.add_argument("--prompt-len-range", default="", metavar="LO,HI",
+                    help="prompt lengths drawn uniformly from [LO, HI] (from --workload-seed) instead of --prompt-len")
+    ap.add_argument("--output-len-range", default="", metavar="LO,HI",
+                    help="output lengths drawn uniformly from [LO, HI] instead of --output-len")
+    ap.add_argument("--workload-seed", type=int, default=0, help="seed of the drawn lengths and token ids")
     args = ap.parse_args(argv)
+    import random
     import torch
     from .sampling import SamplingParams
     if args.mode in ("decode", "prefill"):
         return _bench_step(args)
+
+    def span(text, what):
+        try:
+            lo, hi = (int(x) for x in text.split(","))
+        except ValueError:
+            raise SystemExit(f"error: {what} wants LO,HI (two integers), got {text!r}") from None
+        if not (1 <= lo <= hi):
+            raise SystemExit(f"error: {what} needs 1 <= LO <= HI, got {text!r}")
+        return lo, hi
+    p_span = span(args.prompt_len_range, "--prompt-len-range") if args.prompt_len_range else None
+    o_span = span(args.output_len_range, "--output-len-range") if args.output_len_range else None
     eng = _make_engine(args)
     V = eng.spec.vocab_size
-    params = SamplingParams(max_tokens=args.output_len, ignore_eos=True)
-    # prompts as the reference's offline bench makes them: prompt[j] = (j + i) % 255
-    # (cmd/gollmgo/main.go:335-422)
-    mk = lambda n, off=0: [[(j + i + off) % min(V, 255) for j in range(args.prompt_len)] for i in range(n)]
+
+    def workload(n, seed):
+        """n (prompt, params).  Fixed lengths: prompts as the reference's offline bench makes
+        them, prompt[j] = (j + i) % 255 (cmd/gollmgo/main.go:335-422).  Drawn lengths: lengths
+        and token ids uniform from the seed."""
+        rng = random.Random(seed)
+        out = []
+        for i in range(n):
+            plen = rng.randint(*p_span) if p_span else args.prompt_len
+            olen = rng.randint(*o_span) if o_span else args.output_len
+            if p_span or o_span:
+                prompt = [rng.randrange(V) for _ in range(plen)]
+            else:
+                prompt = [(j + i + seed) % min(V, 255) for j in range(plen)]
+            out.append((prompt, SamplingParams(max_tokens=olen, ignore_eos=True)))
+        return out
+
+    def run(items):
+        return eng.generate([p for p, _ in items], [q for _, q in items])
     if args.warmup_requests:
-        eng.generate(mk(args.warmup_requests, 7), params)
+        run(workload(args.warmup_requests, args.workload_seed + 7))
     result = None
     for rep in range(args.repetitions):
+        items = workload(args.num_prompts, args.workload_seed)
+        s0 = (eng.stats.steps, eng.stats.batch_sum, eng.stats.preemptions, eng.stats.prefill_tokens,
+              eng.stats.decode_tokens)
+        for g in eng.runner.cache.groups:
+            g.pool.high_water = g.pool.num_used
         torch.cuda.synchronize()
         t0 = time.perf_counter()
-        outs = eng.generate(mk(args.num_prompts), params)
+        outs = run(items)
         torch.cuda.synchronize()
         elapsed = time.perf_counter() - t0
         toks = sum(len(o.token_ids) for o in outs)
+        steps = eng.stats.steps - s0[0]
         itl = [b - a for o in outs for a, b in zip(o.token_times, o.token_times[1:])]
         ttft = [o.ttft_s for o in outs if o.ttft_s is not None]
         e2e = [o.e2e_s for o in outs if o.e2e_s is not None]
@@ -172,16 +210,26 @@ def cmd_bench(argv) -> int:
             "timestamp": datetime.datetime.now(datetime.timezone.utc).isoformat(timespec="seconds"),
             "git_sha": _git_sha(), "hardware": torch.cuda.get_device_name(args.device),
             "mode": args.mode, "num_prompts": args.num_prompts, "measured_requests": len(outs),
-            "prompt_len": args.prompt_len, "output_len": args.output_len,
+            "prompt_len": args.prompt_len if not p_span else None, "output_len": args.output_len if not o_span else None,
+            "prompt_len_range": list(p_span) if p_span else None, "output_len_range": list(o_span) if o_span else None,
+            "workload_seed": args.workload_seed,
+            "prompt_tokens": sum(len(p) for p, _ in items), "output_tokens": toks,
             "warmup_requests": args.warmup_requests, "repetitions": args.repetitions,
             "prompt_generation": "synthetic token ids", "token_count_mode": "exact",
             "elapsed_seconds": round(elapsed, 4), "tokens_per_second": round(toks / elapsed, 2),
-            "requests_per_second": round(len(outs) / elapsed, 3), "error_count": 0,
+            "total_tokens_per_second": round((toks + sum(len(p) for p, _ in items)) / elapsed, 2),
+            "requests_per_second": round(len(outs) / elapsed, 3),
+            "error_count": sum(1 for o in outs if o.finish_reason == "error"),
             "ttft_p50_ms": ms(ttft, .5), "ttft_p95_ms": ms(ttft, .95), "ttft_p99_ms": ms(ttft, .99),
             "e2e_p50_ms": ms(e2e, .5), "e2e_p95_ms": ms(e2e, .95), "e2e_p99_ms": ms(e2e, .99),
             "itl_p50_ms": ms(itl, .5), "itl_p95_ms": ms(itl, .95), "itl_p99_ms": ms(itl, .99),
-            "dtype": args.dtype, "engine_steps": eng.stats.steps, "preemptions": eng.stats.preemptions,
-            "pages_high_water": eng.stats.pages_high_water,
+            "dtype": args.dtype, "engine_steps": steps,
+            "mean_batch": round((eng.stats.batch_sum - s0[1]) / max(steps, 1), 2),
+            "mean_tokens_per_step": round((eng.stats.prefill_tokens - s0[3] + eng.stats.decode_tokens - s0[4])
+                                          / max(steps, 1), 1),
+            "preemptions": eng.stats.preemptions - s0[2],
+            "pages_high_water": max((g.pool.high_water for g in eng.runner.cache.groups), default=0),
+            "cache_pages": eng.runner.num_pages, "page_size": eng.runner.cache.page_size,
         }
         _log(args, "info", "repetition done", rep=rep, tokens_per_second=result["tokens_per_second"])
     print(json.dumps(result, indent=2))

@@ -3,6 +3,8 @@
 // who needs it, the size limit and the rules of use.
 #include "no_alloc.h"
 
+#include <atomic>
+
 #include "attention_common.cuh"
 
 extern "C" int gg_attn_decode(const void* q, long long q_stride, const void* kcache,
@@ -18,7 +20,9 @@ extern "C" int gg_attn_decode(const void* q, long long q_stride, const void* kca
 static __device__ __align__(256) float g_noalloc_scratch[GG_NOALLOC_MAX_PART_O + GG_NOALLOC_MAX_PART_ML];
 
 #define GG_NOALLOC_MAX_DEVICES 64
-static float* g_scratch_addr[GG_NOALLOC_MAX_DEVICES];      // per device, null until looked up
+// Per device, null until looked up.  Atomic, so two host threads that make their first call
+// on a device at the same time both end up with the one address (each may look it up).
+static std::atomic<float*> g_scratch_addr[GG_NOALLOC_MAX_DEVICES];
 
 // Device address of the scratch array on the current device; looked up once per device.
 static int scratch_for_current_device(float** ptr) {
@@ -27,14 +31,14 @@ static int scratch_for_current_device(float** ptr) {
   if (e != cudaSuccess) return gg_fail(GG_ERR_CUDA, "attn_decode_noalloc: cudaGetDevice: %s", cudaGetErrorString(e));
   if (dev < 0 || dev >= GG_NOALLOC_MAX_DEVICES)
     return gg_fail(GG_ERR_UNSUPPORTED, "attn_decode_noalloc: device index %d is beyond %d", dev, GG_NOALLOC_MAX_DEVICES);
-  if (!g_scratch_addr[dev]) {
-    float* p = nullptr;
+  float* p = g_scratch_addr[dev].load(std::memory_order_acquire);
+  if (!p) {
     e = cudaGetSymbolAddress((void**)&p, g_noalloc_scratch);
     if (e != cudaSuccess || !p)
       return gg_fail(GG_ERR_CUDA, "attn_decode_noalloc: cudaGetSymbolAddress: %s", cudaGetErrorString(e));
-    g_scratch_addr[dev] = p;
+    g_scratch_addr[dev].store(p, std::memory_order_release);
   }
-  *ptr = g_scratch_addr[dev];
+  *ptr = p;
   return GG_OK;
 }
 
@@ -44,8 +48,12 @@ extern "C" int gg_attn_decode_noalloc(const void* q, long long q_stride, const v
                                       const int* dec_seqs, int n_dec, int num_splits, void* out,
                                       int nh, int nkv, int d, int page_size, int window,
                                       float scale, int allow_mma, cudaStream_t stream) {
-  GG_REQUIRE(n_dec >= 0 && num_splits >= 1 && nh > 0 && d > 0,
-             "attn_decode_noalloc: bad sizes n_dec=%d splits=%d nh=%d d=%d", n_dec, num_splits, nh, d);
+  // what is wrong with the arguments is said first, before the device is asked for anything
+  GG_REQUIRE(n_dec >= 0 && num_splits >= 1 && num_splits <= 65535,
+             "attn_decode_noalloc: bad n_dec %d or splits %d", n_dec, num_splits);
+  GG_REQUIRE(nh > 0 && nkv > 0 && nh % nkv == 0, "attn_decode_noalloc: %d heads are not a multiple of %d kv heads", nh, nkv);
+  GG_REQUIRE(d > 0 && d <= 256, "attn_decode_noalloc: head size %d is outside 1..256", d);
+  GG_REQUIRE(page_size > 0 && bt_stride > 0, "attn_decode_noalloc: bad page size %d or block table width %d", page_size, bt_stride);
   const long long rows = (long long)n_dec * nh * num_splits;
   GG_REQUIRE(rows * d <= GG_NOALLOC_MAX_PART_O && rows * 2 <= GG_NOALLOC_MAX_PART_ML,
              "attn_decode_noalloc: %lld partial rows of %d floats exceed the built-in scratch "

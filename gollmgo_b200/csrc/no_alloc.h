@@ -20,7 +20,10 @@
 //     GG_ERR_INVALID and a message, nothing is launched.
 //   * The first call on a device looks up the array's device address (once per
 //     device, with that device current).  Make that first call outside of any
-//     stream capture.
+//     stream capture.  Host threads may make their first calls at the same time:
+//     the cached address is an atomic, and all of them find the same one.
+//   * Arguments are checked before anything else; a call that is refused has
+//     touched neither the device nor the array.
 //   * All calls share the one array, and it keeps whatever the last call left in
 //     it.  Nothing in it has to start at zero: each call writes every entry it
 //     later reads.  Two calls that overlap on the GPU (different streams, no

@@ -6,6 +6,10 @@ list for every sequence, rebuilt each step, and its CUDA bridge splits a mixed
 batch into a prompt call and a decode call (internal/backend/cuda/model_bridge.go:305-383).
 Here a batch is any mix of portions (one token or many) and runs as one forward
 pass; the device gets block tables, not per-token slot lists.
+
+The builder knows nothing of any kernel.  Index lists over the query rows of prompt
+portions are built only as the model's mixers ask for them (``QueryTiles``: a tile
+height and an order); a model whose mixers ask for none gets none.
 """
 from __future__ import annotations
 
@@ -16,9 +20,7 @@ from typing import List, Optional, Sequence
 import numpy as np
 import torch
 
-ATTN_TILE_ROWS = 16        # query rows of one tile of the general attention kernel (ATT_BQ)
-ATTN_TILE_ROWS_MMA = 64    # ... of the mma.sync kernel (csrc/attention_mma.cu)
-ATTN_TILE_ROWS_TC = 128    # ... and of the tcgen05 kernel (csrc/attention_tc.cu)
+from ..parts.context import QueryTiles
 
 
 @dataclass
@@ -32,12 +34,20 @@ class StepEntry:
     token_src: int = -1
 
 
+class TileList:
+    """One QueryTiles list of a step on the device: tile i covers rows q0[i] .. q0[i] + height
+    of sequence seq[i] (``count`` tiles)."""
+
+    def __init__(self, need: QueryTiles, seq: torch.Tensor, q0: torch.Tensor, count: int):
+        self.need, self.seq, self.q0, self.count = need, seq, q0, count
+
+
 class StepBatch:
     """Device views (int32 unless noted) and host facts of one step."""
     num_tokens: int
     num_seqs: int
     num_logit_rows: int
-    num_tiles: int
+    num_portions: int                      # sequences that bring more than one token (prompt portions)
     num_decode: int
     bt_stride: int
     token_ids: torch.Tensor
@@ -48,16 +58,9 @@ class StepBatch:
     context_lens: torch.Tensor
     state_slots: torch.Tensor
     logit_rows: torch.Tensor
-    tile_seq: torch.Tensor
-    tile_q0: torch.Tensor
-    tile64_seq: torch.Tensor
-    tile64_q0: torch.Tensor
-    num_tiles64: int
-    tile128_seq: torch.Tensor
-    tile128_q0: torch.Tensor
-    num_tiles128: int
+    tiles: "dict[QueryTiles, TileList]"    # the index lists the model's mixers asked for
     dec_seqs: torch.Tensor
-    long_context: bool = False             # some live request holds a long context (set by the runner)
+    tags: tuple = ()                       # the step's kind, as the model's parts tagged it (set by the runner)
     slot_mapping: List[torch.Tensor]
     block_tables: List[torch.Tensor]
     # host side
@@ -74,10 +77,9 @@ def _align(n: int) -> int:
 class BatchLayout:
     """Offsets of every array in the packed int32 buffer, for given capacities."""
 
-    def __init__(self, T: int, B: int, R: int, NT: int, ND: int, G: int, stride: int, NT64: int = 0,
-                 NT128: int = 0):
-        self.T, self.B, self.R, self.NT, self.ND, self.G, self.stride = T, B, R, NT, ND, G, stride
-        self.NT64, self.NT128 = NT64, NT128
+    def __init__(self, T: int, B: int, R: int, tile_counts: Sequence[int], ND: int, G: int, stride: int):
+        self.T, self.B, self.R, self.ND, self.G, self.stride = T, B, R, ND, G, stride
+        self.tile_counts = list(tile_counts)
         off = 0
 
         def take(n):
@@ -93,12 +95,8 @@ class BatchLayout:
         self.context_lens = take(B)
         self.state_slots = take(B)
         self.logit_rows = take(R)
-        self.tile_seq = take(NT)
-        self.tile_q0 = take(NT)
-        self.tile64_seq = take(NT64)
-        self.tile64_q0 = take(NT64)
-        self.tile128_seq = take(NT128)
-        self.tile128_q0 = take(NT128)
+        self.tile_seq = [take(n) for n in self.tile_counts]
+        self.tile_q0 = [take(n) for n in self.tile_counts]
         self.dec_seqs = take(ND)
         self.block_tables = [take(B * stride) for _ in range(G)]
         self.size = off
@@ -112,16 +110,21 @@ class BatchBuilder:
     empty ones that no kernel touches.
     """
 
-    def __init__(self, cache, device, capacity_ints: int = 1 << 16):
+    def __init__(self, cache, device, capacity_ints: int = 1 << 16, query_tiles: Sequence[QueryTiles] = ()):
         self.cache = cache
         self.device = torch.device(device)
         self.G = len(cache.groups)
+        self.query_tiles = list(dict.fromkeys(query_tiles))      # what the model's mixers asked for
         self._host = None
         self._dev = None
         self._copied = None
         # steps of single decoded tokens are packed by native code (GOLLMGO_B200_NATIVE_PACK=0: by the general path)
         self.native_decode = os.environ.get("GOLLMGO_B200_NATIVE_PACK", "1") != "0"
         self._ensure(capacity_ints)
+
+    def decode_layout(self, seqs: int, stride: int) -> BatchLayout:
+        """The layout of a step of ``seqs`` single tokens (what a captured step's buffer holds)."""
+        return BatchLayout(seqs, seqs, seqs, [0] * len(self.query_tiles), seqs, self.G, stride)
 
     def _ensure(self, n: int) -> None:
         if self._host is not None and self._host.numel() >= n:
@@ -167,9 +170,9 @@ class BatchBuilder:
         stride = fixed_stride if fixed_stride is not None else max(1, max_pages)
         if stride < max_pages:
             raise ValueError(f"a sequence holds {max_pages} pages, the fixed block table has {stride}")
-        lay = BatchLayout(Bp, Bp, Bp, 0, Bp, G, stride, 0, 0)
+        lay = self.decode_layout(Bp, stride)
         used = min(stride, max(1, max_pages))
-        hlay = lay if used == stride else BatchLayout(Bp, Bp, Bp, 0, Bp, G, used, 0, 0)
+        hlay = lay if used == stride else self.decode_layout(Bp, used)
         cuda = self.device.type == "cuda"
         if static_dev is None:
             self._ensure(lay.size)
@@ -205,15 +208,14 @@ class BatchBuilder:
             self._copied.record()
         sb = StepBatch()
         sb.num_tokens, sb.num_seqs, sb.num_logit_rows = Bp, Bp, Bp
-        sb.num_tiles, sb.num_decode, sb.bt_stride = 0, Bp, stride
+        sb.num_portions, sb.num_decode, sb.bt_stride = 0, Bp, stride
         v = lambda off, n: dev[off:off + max(n, 1)]
         sb.token_ids, sb.positions = v(lay.token_ids, Bp), v(lay.positions, Bp)
         sb.token_src = v(lay.token_src, Bp) if (static_dev is not None or any(x >= 0 for x in srcs)) else None
         sb.cu_q_lens, sb.context_lens = v(lay.cu_q_lens, Bp + 1), v(lay.context_lens, Bp)
         sb.state_slots, sb.logit_rows = v(lay.state_slots, Bp), v(lay.logit_rows, Bp)[:Bp]
-        sb.tile_seq, sb.tile_q0 = v(lay.tile_seq, 0), v(lay.tile_q0, 0)
-        sb.tile64_seq, sb.tile64_q0, sb.num_tiles64 = v(lay.tile64_seq, 0), v(lay.tile64_q0, 0), 0
-        sb.tile128_seq, sb.tile128_q0, sb.num_tiles128 = v(lay.tile128_seq, 0), v(lay.tile128_q0, 0), 0
+        sb.tiles = {need: TileList(need, v(lay.tile_seq[i], 0), v(lay.tile_q0[i], 0), 0)
+                    for i, need in enumerate(self.query_tiles)}
         sb.dec_seqs = v(lay.dec_seqs, Bp)
         sb.slot_mapping = [v(o, Bp) for o in lay.slot_mapping]
         sb.block_tables = [v(o, Bp * stride) for o in lay.block_tables]
@@ -265,12 +267,14 @@ class BatchBuilder:
         q_lens = [len(e.tokens) for e in entries]
         q_starts = [a.start for a in appended]
         T = sum(q_lens)
-        tiles = [(b, q0) for b in range(B) if q_lens[b] > 1 for q0 in range(0, q_lens[b], ATTN_TILE_ROWS)]
-        tiles64 = [(b, q0) for b in range(B) if q_lens[b] > 1
-                   for q0 in range(0, q_lens[b], ATTN_TILE_ROWS_MMA)]
-        tiles128 = [(b, q0) for b in range(B) if q_lens[b] > 1
-                    for q0 in range(0, q_lens[b], ATTN_TILE_ROWS_TC)]
-        tiles128.sort(key=lambda t: -(q_starts[t[0]] + t[1]))      # most keys to attend to first
+        portions = [b for b in range(B) if q_lens[b] > 1]
+        tile_lists = []
+        for need in self.query_tiles:
+            tl = [(b, q0) for b in portions for q0 in range(0, q_lens[b], need.height)]
+            if need.most_keys_first:
+                tl.sort(key=lambda t: -(q_starts[t[0]] + t[1]))
+            tile_lists.append(tl)
+        counts = [len(tl) for tl in tile_lists]
         dec = [b for b in range(B) if q_lens[b] == 1]
         max_pages = max(len(cache.block_table(e.request_id, g)) for e in entries for g in range(G)) if G else 1
         Bp = fixed_seqs if fixed_seqs is not None else B
@@ -284,12 +288,11 @@ class BatchBuilder:
             base += n
         rows.extend(range(T, Tp))    # ... whose logits are computed and ignored
         R = len(rows)
-        lay = BatchLayout(Tp, Bp, R, len(tiles), len(dec) + (Bp - B), G, stride, len(tiles64), len(tiles128))
+        lay = BatchLayout(Tp, Bp, R, counts, len(dec) + (Bp - B), G, stride)
         # on the host the block tables are packed with only as many columns as are in use; with a
         # fixed (wide) device stride they are copied as a 2-d block, not as the whole table
         used = min(stride, max(1, max_pages))
-        hlay = lay if used == stride else BatchLayout(Tp, Bp, R, len(tiles), len(dec) + (Bp - B), G, used,
-                                                      len(tiles64), len(tiles128))
+        hlay = lay if used == stride else BatchLayout(Tp, Bp, R, counts, len(dec) + (Bp - B), G, used)
         if static_dev is None:
             self._ensure(lay.size)
             if self._copied is not None:
@@ -324,13 +327,10 @@ class BatchBuilder:
         h[lay.state_slots:lay.state_slots + B] = [cache.state_slot(e.request_id) for e in entries]
         h[lay.state_slots + B:lay.state_slots + Bp] = -1
         h[lay.logit_rows:lay.logit_rows + R] = rows
-        if tiles:
-            h[lay.tile_seq:lay.tile_seq + len(tiles)] = [t[0] for t in tiles]
-            h[lay.tile_q0:lay.tile_q0 + len(tiles)] = [t[1] for t in tiles]
-            h[lay.tile64_seq:lay.tile64_seq + len(tiles64)] = [t[0] for t in tiles64]
-            h[lay.tile64_q0:lay.tile64_q0 + len(tiles64)] = [t[1] for t in tiles64]
-            h[lay.tile128_seq:lay.tile128_seq + len(tiles128)] = [t[0] for t in tiles128]
-            h[lay.tile128_q0:lay.tile128_q0 + len(tiles128)] = [t[1] for t in tiles128]
+        for i, tl in enumerate(tile_lists):
+            if tl:
+                h[lay.tile_seq[i]:lay.tile_seq[i] + len(tl)] = [t[0] for t in tl]
+                h[lay.tile_q0[i]:lay.tile_q0[i] + len(tl)] = [t[1] for t in tl]
         nd = len(dec) + (Bp - B)
         h[lay.dec_seqs:lay.dec_seqs + len(dec)] = dec
         h[lay.dec_seqs + len(dec):lay.dec_seqs + nd] = -1
@@ -359,17 +359,14 @@ class BatchBuilder:
 
         sb = StepBatch()
         sb.num_tokens, sb.num_seqs, sb.num_logit_rows = Tp, Bp, R
-        sb.num_tiles, sb.num_decode, sb.bt_stride = len(tiles), nd, stride
+        sb.num_portions, sb.num_decode, sb.bt_stride = len(portions), nd, stride
         v = lambda off, n: dev[off:off + max(n, 1)]
         sb.token_ids, sb.positions = v(lay.token_ids, Tp), v(lay.positions, Tp)
         sb.token_src = v(lay.token_src, Tp) if (has_src or static_dev is not None) else None
         sb.cu_q_lens, sb.context_lens = v(lay.cu_q_lens, Bp + 1), v(lay.context_lens, Bp)
         sb.state_slots, sb.logit_rows = v(lay.state_slots, Bp), v(lay.logit_rows, R)[:R]
-        sb.tile_seq, sb.tile_q0 = v(lay.tile_seq, len(tiles)), v(lay.tile_q0, len(tiles))
-        sb.tile64_seq, sb.tile64_q0 = v(lay.tile64_seq, len(tiles64)), v(lay.tile64_q0, len(tiles64))
-        sb.num_tiles64 = len(tiles64)
-        sb.tile128_seq, sb.tile128_q0 = v(lay.tile128_seq, len(tiles128)), v(lay.tile128_q0, len(tiles128))
-        sb.num_tiles128 = len(tiles128)
+        sb.tiles = {need: TileList(need, v(lay.tile_seq[i], counts[i]), v(lay.tile_q0[i], counts[i]), counts[i])
+                    for i, need in enumerate(self.query_tiles)}
         sb.dec_seqs = v(lay.dec_seqs, nd)
         sb.slot_mapping = [v(o, Tp) for o in lay.slot_mapping]
         sb.block_tables = [v(o, Bp * stride) for o in lay.block_tables]

@@ -24,10 +24,9 @@ from .. import architectures  # noqa: F401  (registers the architectures)
 from ..cache import CacheManager, OutOfPages, PagedKVNeed
 from ..config import EngineConfig, read_config_json
 from ..csrc import ops
-from ..parts import BuildContext, build_model, set_matmul_precision
-from ..parts.context import LONG_CONTEXT
+from ..parts import BuildContext, StepFacts, build_model, set_matmul_precision
 from ..weights import checkpoint_source, random_source
-from .batch import BatchBuilder, BatchLayout, StepBatch, StepEntry
+from .batch import BatchBuilder, StepBatch, StepEntry
 
 _DTYPES = {"bfloat16": torch.bfloat16, "float32": torch.float32}
 GRAPH_BUCKETS = (1, 2, 4, 8, 16, 24, 32, 48, 64, 96, 128, 192, 256)
@@ -68,7 +67,7 @@ class ModelRunner:
                                   max_requests=max(engine_config.max_batch_size, 4) * 2,
                                   dtype=self.dtype, device=self.device)
         self.caches = [self._cache_view(i, n) for i, n in enumerate(needs)]
-        self.builder = BatchBuilder(self.cache, self.device)
+        self.builder = BatchBuilder(self.cache, self.device, query_tiles=self.model.query_tiles())
         # tokens sampled on the device in the last step, by row: the next step may take its
         # inputs from here before the host has read them
         self.last_tokens = torch.zeros(max(engine_config.max_batch_size, 1), dtype=torch.int32,
@@ -154,15 +153,19 @@ class ModelRunner:
 
     def _run(self, entries: Sequence[StepEntry]) -> torch.Tensor:
         decode_only = all(len(e.tokens) == 1 and list(e.want) == [0] for e in entries)
-        # a step while some live request holds a long context is a step of its own kind: parts
-        # may choose differently for it (the attention's count of slices), so it has graphs of its own
-        long_context = int(self.cache.ntok.max()) >= LONG_CONTEXT
+        # The model's parts may tag the step from what is known before its batch is built (the
+        # attention: some live request holds a long context).  Steps with different tags are steps
+        # of different kinds: a part may choose differently for them, so each kind has captured
+        # graphs of its own.  The runner only carries the tags; it does not know what they mean.
+        facts = StepFacts(len(entries), sum(len(e.tokens) for e in entries), decode_only,
+                          int(self.cache.ntok.max()))
+        tags = self.model.step_tags(facts)
         if decode_only and self.ecfg.cuda_graphs:
             bucket = next((b for b in GRAPH_BUCKETS if b >= len(entries)), None)
             if bucket is not None and bucket <= self.ctx.max_seqs:
-                return self._graph_step(entries, bucket, long_context)
+                return self._graph_step(entries, bucket, tags)
         batch = self.builder.build(entries)
-        batch.long_context = long_context
+        batch.tags = tags
         batch.prev_tokens = self.last_tokens if batch.token_src is not None else None
         logits = self.model.forward(batch, self.caches)
         self.steps += 1
@@ -179,16 +182,16 @@ class ModelRunner:
     def _graph_stride(self) -> int:
         return -(-self.max_model_len // self.cache.page_size)
 
-    def _graph_step(self, entries, bucket: int, long_context: bool = False) -> torch.Tensor:
-        key = (bucket, True) if long_context else bucket
+    def _graph_step(self, entries, bucket: int, tags: tuple = ()) -> torch.Tensor:
+        key = (bucket, tags) if tags else bucket
         cs = self._graphs.get(key)
         stride = self._graph_stride()
         if cs is None:
-            lay = BatchLayout(bucket, bucket, bucket, 0, bucket, len(self.cache.groups), stride)
+            lay = self.builder.decode_layout(bucket, stride)
             cs = _CapturedStep(torch.zeros(lay.size, dtype=torch.int32, device=self.device))
             self._graphs[key] = cs
         batch = self.builder.build(entries, fixed_seqs=bucket, fixed_stride=stride, static_dev=cs.meta)
-        batch.long_context = long_context
+        batch.tags = tags
         batch.prev_tokens = self.last_tokens
         if cs.graph is None:
             torch.cuda.synchronize(self.device)

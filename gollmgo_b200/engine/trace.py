@@ -70,7 +70,12 @@ def run_step(runner: ModelRunner, entries: List[StepEntry]) -> torch.Tensor:
     return out
 
 
-def replay(runner: ModelRunner, lines: IO[str], out_dir: str, log: IO[str] = sys.stdout) -> int:
+def replay(runner: ModelRunner, lines: IO[str], out_dir: str, log: IO[str] = sys.stdout,
+           page_log: IO[str] = None) -> int:
+    """Run the steps read from ``lines``.  ``page_log``: after every step one JSON line
+    {"step": n, "pages": {request id: [page ids of group 0, of group 1, ...]}} for the requests
+    of that step, so that a test can see which request held which page when (-1 = a page that a
+    sliding group has given back)."""
     os.makedirs(out_dir, exist_ok=True)
     steps = 0
     for line in lines:
@@ -89,6 +94,11 @@ def replay(runner: ModelRunner, lines: IO[str], out_dir: str, log: IO[str] = sys
             else:
                 torch.cuda.synchronize(runner.device)
             runner.check_kernels()
+            if page_log is not None:
+                held = {str(e.request_id): [list(map(int, runner.cache.block_table(e.request_id, g)))
+                                            for g in range(len(runner.cache.groups))] for e in entries}
+                page_log.write(json.dumps({"step": step, "pages": held}) + "\n")
+                page_log.flush()
         for rid in rec.get("end", []):
             if runner.has(rid):
                 runner.release(rid)

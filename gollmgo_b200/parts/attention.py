@@ -17,6 +17,7 @@ import torch
 from ..cache import PagedKVNeed
 from ..csrc import ops
 from ..weights import WeightSpec
+from .context import QueryTiles
 from .linear import fuses_norms, linear
 from .registry import build_position, register_mixer
 
@@ -30,11 +31,17 @@ FUSE_DECODE_ROPE = os.environ.get("GOLLMGO_B200_FUSE_ROPE", "1") != "0"
 # use the kernel that cuts all tiles into equal ranges (ops.attn_decode_flat); 0 = never.
 FLAT_DECODE_FILL = float(os.environ.get("GOLLMGO_B200_FLAT_DECODE_FILL", "1.0"))
 MAX_SPLITS = 16
-# A step whose longest context has reached context.LONG_CONTEXT tokens is a step of its own kind (the
-# runner captures it separately and sets batch.long_context): the count of slices is then
+# The index lists over the query rows of prompt portions that the three prompt kernels walk:
+# tiles of 16 rows (general kernel, csrc/attention.cu), of 64 (mma.sync, csrc/attention_mma.cu),
+# of 128 with the tiles that attend to most keys first (tcgen05, csrc/attention_tc.cu)
+TILES_GENERAL, TILES_MMA, TILES_TC = QueryTiles(16), QueryTiles(64), QueryTiles(128, most_keys_first=True)
+# From this many tokens in some live request's cache the attention tags a step "long_context": a
+# step of its own kind (captured separately), for which the count of slices is
 # chosen for contexts of LONG_TILES tiles, among up to MAX_SPLITS_LONG.  One sequence at
 # 32768 tokens: 8 slices in a cluster are 64 CTAs for 134 MB of cache a layer (87 us); 32
 # slices and a merge kernel are 256 CTAs.
+LONG_CONTEXT = int(os.environ.get("GOLLMGO_B200_LONG_CONTEXT", "8192"))
+LONG_TAG = "long_context"
 LONG_TILES = 256
 MAX_SPLITS_LONG = 64
 FORCED_SPLITS = int(os.environ.get("GOLLMGO_B200_DECODE_SPLITS", "0"))   # for measurements: this count, whatever the batch
@@ -135,6 +142,18 @@ class Attention:
     def cache_need(self):
         return PagedKVNeed(self.nkv, self.d, self.window)
 
+    def query_tiles(self):
+        """The tile lists of the prompt kernels this mixer can end up using."""
+        need = [TILES_GENERAL]
+        if self.ctx.act_dtype == torch.bfloat16 and self.d in (64, 128) and ATTN_POLICY != "general":
+            need.append(TILES_MMA)
+            if ATTN_POLICY == "auto":
+                need.append(TILES_TC)
+        return need
+
+    def step_tags(self, facts):
+        return (LONG_TAG,) if facts.max_context >= LONG_CONTEXT else ()
+
     def weights(self):
         return {"q_proj.weight": WeightSpec((self.nh * self.d, self.hidden)),
                 "k_proj.weight": WeightSpec((self.nkv * self.d, self.hidden)),
@@ -167,7 +186,7 @@ class Attention:
                                  ws.get("attn_flat_prefix", 1, n + 1), out, self.nh, self.nkv, self.d,
                                  self.ctx.page_size, window, self.scale)
             return
-        splits = decode_splits(n, self._ctas_per_split, self.num_sms, self._cluster_cap, batch.long_context)
+        splits = decode_splits(n, self._ctas_per_split, self.num_sms, self._cluster_cap, LONG_TAG in batch.tags)
         part_o = ws.get("attn_part_o", 1, n * self.nh * splits * self.d)
         part_ml = ws.get("attn_part_ml", 1, n * self.nh * splits * 2)
         if fused:
@@ -193,7 +212,7 @@ class Attention:
         table = self.position.rope_table()
         flat_step = (self._flat_ok and batch.num_decode * self._ctas_per_split
                      >= FLAT_DECODE_FILL * CTAS_PER_SM * self.num_sms)
-        fused = (FUSE_DECODE_ROPE and batch.num_decode > 0 and not batch.num_tiles and ATTN_POLICY != "general"
+        fused = (FUSE_DECODE_ROPE and batch.num_decode > 0 and not batch.num_portions and ATTN_POLICY != "general"
                  and not flat_step
                  and not hasattr(self.position, "apply")
                  and ops.attn_decode_rope_ok(qkv.dtype, self.nh, self.nkv, self.d, table, self.position.interleaved))
@@ -204,14 +223,18 @@ class Attention:
         out = ws.get("attn_out", T, self.nh * self.d)
         window = int(self.window or 0)
         bt = batch.block_tables[group]
-        if batch.num_tiles:
+        if batch.num_portions:
+            if TILES_GENERAL not in batch.tiles:
+                raise RuntimeError("the step's batch was built without the index lists this mixer declares in "
+                                   "query_tiles(): give them to the BatchBuilder (query_tiles=...)")
+            t16, t64, t128 = batch.tiles[TILES_GENERAL], batch.tiles.get(TILES_MMA), batch.tiles.get(TILES_TC)
             ops.attn_prefill(qkv, self.qkv_width, kc, vc, bt, batch.bt_stride, batch.cu_q_lens,
-                             batch.context_lens, batch.tile_seq, batch.tile_q0, batch.num_tiles,
+                             batch.context_lens, t16.seq, t16.q0, t16.count,
                              out, self.nh, self.nkv, self.d, self.ctx.page_size, window, self.scale,
-                             batch.tile64_seq, batch.tile64_q0, batch.num_tiles64,
-                             allow_mma=ATTN_POLICY != "general",
-                             tile128_seq=batch.tile128_seq, tile128_q0=batch.tile128_q0,
-                             num_tiles128=batch.num_tiles128, allow_tc=ATTN_POLICY == "auto")
+                             t64.seq if t64 else None, t64.q0 if t64 else None, t64.count if t64 else 0,
+                             allow_mma=t64 is not None,
+                             tile128_seq=t128.seq if t128 else None, tile128_q0=t128.q0 if t128 else None,
+                             num_tiles128=t128.count if t128 else 0, allow_tc=t128 is not None)
         if batch.num_decode:
             self._decode(qkv, kc, vc, group, batch, out, window, flat_step, fused, table, writes_cache)
         y = ws.get("mixer_out", T, self.hidden)

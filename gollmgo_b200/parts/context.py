@@ -3,16 +3,32 @@ limits, and a workspace of named activation buffers that parts share.
 """
 from __future__ import annotations
 
-import os
+from dataclasses import dataclass
 from typing import Dict, Optional, Tuple
 
 import torch
 
 
-# From this many tokens in some live request's cache a step counts as one with a long context:
-# the runner sets batch.long_context and keeps captured steps of their own for it, and a part
-# may choose differently for such steps (the attention: more slices of the context).
-LONG_CONTEXT = int(os.environ.get("GOLLMGO_B200_LONG_CONTEXT", "8192"))
+@dataclass(frozen=True)
+class QueryTiles:
+    """An index list a mixer asks the batch builder for: the query rows of every prompt
+    portion (a sequence with more than one token in the step) cut into tiles of ``height``
+    rows, as (sequence, first row) pairs; ``most_keys_first`` orders them by how many keys
+    they attend to, longest first.  A mixer names the lists it wants in ``query_tiles()``;
+    the step's batch then holds each under ``batch.tiles[that QueryTiles]``."""
+    height: int
+    most_keys_first: bool = False
+
+
+@dataclass(frozen=True)
+class StepFacts:
+    """What is known of a step before its batch is built; parts may derive step tags from it
+    (``step_tags(facts)``): steps with different tags are steps of different kinds, each with
+    captured graphs of its own, and ``batch.tags`` tells a part which kind it is in."""
+    num_seqs: int
+    num_tokens: int
+    decode_only: bool
+    max_context: int              # most tokens any live request holds in the cache
 
 
 class Workspace:

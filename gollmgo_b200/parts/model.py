@@ -17,7 +17,7 @@ from ..csrc import ops
 from ..weights import WeightSpec
 from .context import BuildContext
 from .linear import linear
-from .registry import build_block, build_feed_forward, build_mixer, build_norm
+from .registry import build_block, build_feed_forward, build_mixer, build_norm, build_position
 from .spec import ModelSpec
 
 
@@ -25,7 +25,7 @@ def _prefixed(prefix: str, weights: Dict[str, WeightSpec], single_name: str = ""
     return {(single_name if local == "" else prefix + local): spec for local, spec in weights.items()}
 
 
-def spec_manifest(spec: ModelSpec, parts=None) -> Dict[str, WeightSpec]:
+def spec_manifest(spec: ModelSpec, parts=None, embed_position=None) -> Dict[str, WeightSpec]:
     """Checkpoint tensors the model expects.  ``parts`` = per layer
     (mixer, feed_forward, mixer_norm, ffn_norm) if already built."""
     m: Dict[str, WeightSpec] = {spec.embed_name: WeightSpec((spec.vocab_size, spec.hidden_size))}
@@ -35,6 +35,8 @@ def spec_manifest(spec: ModelSpec, parts=None) -> Dict[str, WeightSpec]:
         m.update(_prefixed("", n1.weights(), ls.mixer_norm_name))
         m.update(_prefixed("", n2.weights(), ls.ffn_norm_name))
     m[spec.final_norm_name] = WeightSpec((spec.hidden_size,))
+    if embed_position is not None:
+        m.update(_prefixed(spec.embed_position_prefix, embed_position.weights()))
     m[spec.head_name] = WeightSpec((spec.vocab_size, spec.hidden_size), optional=spec.tie_embeddings)
     return m
 
@@ -51,6 +53,7 @@ class DecoderModel:
             self.parts.append((mixer, ff, n1, n2))
             self.blocks.append(build_block(ls, mixer, ff, n1, n2, ctx))
         self.final_norm = build_norm(spec.final_norm, ctx)
+        self.embed_position = build_position(spec.embed_position, ctx) if spec.embed_position else None
         ws = ctx.workspace
         ws.reserve("residual", ctx.max_tokens * spec.hidden_size, torch.float32)
         ws.reserve("head_in", ctx.max_tokens * spec.hidden_size, ctx.act_dtype)
@@ -61,7 +64,7 @@ class DecoderModel:
 
     # ------------------------------------------------------------------ weights
     def manifest(self) -> Dict[str, WeightSpec]:
-        return spec_manifest(self.spec, self.parts)
+        return spec_manifest(self.spec, self.parts, self.embed_position)
 
     def load(self, get: Callable[[str], torch.Tensor]) -> None:
         """Bind weights: ``get(name)`` delivers a checkpoint tensor on the device."""
@@ -73,6 +76,8 @@ class DecoderModel:
             n1.load(lambda local, n=ls.mixer_norm_name: get(n))
             n2.load(lambda local, n=ls.ffn_norm_name: get(n))
         self.final_norm.load(lambda local: get(s.final_norm_name))
+        if self.embed_position is not None:
+            self.embed_position.load(lambda local, p=s.embed_position_prefix: get(p + local))
         head = None if s.tie_embeddings else get(s.head_name)
         self.head = self.embed if head is None else head.contiguous()
 
@@ -102,6 +107,26 @@ class DecoderModel:
             needs[e.cache] = need
         return needs
 
+    # ------------------------------------------------------------------ what the parts ask of a step
+    def query_tiles(self) -> list:
+        """The index lists (QueryTiles) the mixers want in every step's batch."""
+        wanted = []
+        for mixer, _, _, _ in self.parts:
+            for need in getattr(mixer, "query_tiles", lambda: ())():
+                if need not in wanted:
+                    wanted.append(need)
+        return wanted
+
+    def step_tags(self, facts) -> tuple:
+        """The step's kind: the tags of every part that offers ``step_tags(facts)``, sorted."""
+        tags = set()
+        for parts in self.parts:
+            for part in parts:
+                f = getattr(part, "step_tags", None)
+                if f is not None:
+                    tags.update(f(facts))
+        return tuple(sorted(tags))
+
     # ------------------------------------------------------------------ forward
     def forward(self, batch, caches) -> torch.Tensor:
         """Run the batch's tokens; return float32 logits [len(logit_rows), vocab].
@@ -111,6 +136,8 @@ class DecoderModel:
         resid = ws.get("residual", T, H)
         ops.embed_gather(batch.token_ids, self.embed, resid, self.bad_id,
                          getattr(batch, "token_src", None), getattr(batch, "prev_tokens", None))
+        if self.embed_position is not None:
+            self.embed_position.add_to_embedding(resid, batch)
         delta = None
         order = self.spec.run_order
         for i, e in enumerate(order):

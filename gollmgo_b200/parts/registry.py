@@ -16,10 +16,21 @@ position        cls(spec, ctx)
                   .apply(qkv, batch, nh, nkv, d)              optional: rewrite the q and k heads of
                                                               qkv [T, (nh+2nkv)*d] in place (positions in
                                                               batch.positions) before k, v go to the cache
+                a position encoding named in ModelSpec.embed_position acts on the embedded tokens
+                instead and offers
+                  .weights(), .load(get)                      its tensors, under ModelSpec.embed_position_prefix
+                  .add_to_embedding(resid, batch)             resid [T, hidden] float32, in place
 mixer           cls(spec, ctx)
                   .cache_need() -> PagedKVNeed | FixedStateNeed | None
                   .weights(), .load(get)
                   .forward(x, batch, cache, writes_cache) -> tensor [T, hidden]
+                  .query_tiles() -> [QueryTiles]              optional: index lists over the query rows of
+                                                              prompt portions that every batch should hold
+                                                              for it (batch.tiles[need])
+                  .step_tags(facts) -> tuple of str           optional (any part): tags of a step, from the
+                                                              StepFacts known before its batch is built; the
+                                                              runner captures steps of different tags
+                                                              separately and sets batch.tags
 feed-forward    cls(spec, ctx)
                   .weights(), .load(get)
                   .forward(x, batch) -> tensor [T, hidden]

@@ -67,6 +67,11 @@ class ModelSpec:
     max_positions: int
     eos_token_ids: Tuple[int, ...] = ()
     bos_token_id: Optional[int] = None
+    # a position encoding that acts on the embedded tokens, before the first layer (a table of
+    # learned positions, say), with the prefix of its checkpoint tensors; None = the layers'
+    # mixers do all the position encoding there is (rotary: inside attention)
+    embed_position: Optional[PartSpec] = None
+    embed_position_prefix: str = ""
 
     @property
     def num_cache_entries(self) -> int:

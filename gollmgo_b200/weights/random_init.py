@@ -42,16 +42,18 @@ def random_source(manifest: Dict[str, WeightSpec], seed: int, device, dtype: tor
     """``get(name)`` that makes each tensor of the manifest on ``device``."""
     def get(name: str):
         spec = manifest[name]
-        if spec.optional and spec.kind == "float" and name.startswith("lm_head"):
+        if spec.optional:                  # what the model can do without (the head of a tied model) is left out
             return None
         return random_tensor(name, spec, seed, device, dtype, std, norm_jitter)
     return get
 
 
 def write_random_model(model_dir: str, config: dict, seed: int, dtype: str = "bfloat16",
-                       std: float = 0.02, norm_jitter: float = 0.0) -> str:
+                       std: float = 0.02, norm_jitter: float = 0.0, device="cpu") -> str:
     """Write ``config.json`` and ``model.safetensors`` for ``config`` (a config.json
-    dict naming a registered architecture).  Returns ``model_dir``."""
+    dict naming a registered architecture).  Returns ``model_dir``.  ``device``: where the
+    numbers are drawn (a CUDA device draws a checkpoint of real layer sizes in seconds; the
+    values depend on the kind of device, the file is the same kind of file)."""
     from ..parts.model import manifest_for_config      # late: parts imports weights
     torch_dtype = {"bfloat16": torch.bfloat16, "float32": torch.float32}[dtype]
     manifest = manifest_for_config(config)
@@ -60,7 +62,7 @@ def write_random_model(model_dir: str, config: dict, seed: int, dtype: str = "bf
     cfg["torch_dtype"] = dtype
     with open(os.path.join(model_dir, "config.json"), "w") as f:
         json.dump(cfg, f, indent=1)
-    tensors = ((name, random_tensor(name, spec, seed, "cpu", torch_dtype, std, norm_jitter))
+    tensors = ((name, random_tensor(name, spec, seed, device, torch_dtype, std, norm_jitter).cpu())
                for name, spec in manifest.items() if not spec.optional)
     save_file(tensors, os.path.join(model_dir, "model.safetensors"),
               metadata={"format": "pt", "seed": seed})

@@ -19,7 +19,10 @@ stored for; ``rope_interleaved: true`` selects the reference's adjacent pairs
 ``(2p, 2p+1)`` (kernels/gollmgo_ops.cu:321-358).
 
 All arithmetic is float64 unless ``dtype`` says otherwise, so that it is the
-most exact thing in the comparison.
+most exact thing in the comparison.  ``forward(..., device=...)`` does the same
+arithmetic on that device (the weights stay where they are and are brought over
+tensor by tensor), which is what makes the layer sizes of a real checkpoint
+affordable; ``rows`` limits the head product to the positions that are compared.
 """
 from __future__ import annotations
 
@@ -32,7 +35,7 @@ import torch
 
 def embed(table: torch.Tensor, ids) -> torch.Tensor:
     """x0[t, :] = float(E[id_t, :])  -- kernels/gollmgo_ops.cu:538-552."""
-    ids = torch.as_tensor(ids, dtype=torch.long)
+    ids = torch.as_tensor(ids, dtype=torch.long, device=table.device)
     return table[ids].to(torch.float64)
 
 
@@ -87,7 +90,7 @@ def apply_rope(x: torch.Tensor, positions: torch.Tensor, inv_freq: torch.Tensor,
     x = x.to(torch.float64)
     d = x.shape[-1]
     half = d // 2
-    ang = positions.to(torch.float64)[:, None] * inv_freq[None, :]   # [T, d/2]
+    ang = positions.to(x.device, torch.float64)[:, None] * inv_freq.to(x.device)[None, :]   # [T, d/2]
     cos = torch.cos(ang)[:, None, :]
     sin = torch.sin(ang)[:, None, :]
     out = torch.empty_like(x)
@@ -116,9 +119,9 @@ def attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor,
     nkv = k.shape[1]
     group = nh // nkv
     scale = 1.0 / math.sqrt(d)
-    out = torch.zeros(T, nh, d, dtype=torch.float64)
-    i_idx = torch.arange(T)[:, None]
-    j_idx = torch.arange(T)[None, :]
+    out = torch.zeros(T, nh, d, dtype=torch.float64, device=q.device)
+    i_idx = torch.arange(T, device=q.device)[:, None]
+    j_idx = torch.arange(T, device=q.device)[None, :]
     allowed = j_idx <= i_idx
     if window is not None:
         allowed &= j_idx > i_idx - window
@@ -165,6 +168,16 @@ def layer_windows(config: dict) -> list:
     return [win if t == "sliding_attention" else None for t in types]
 
 
+class _On:
+    """The weights dict, each tensor brought to ``device`` when it is asked for."""
+
+    def __init__(self, w, device):
+        self.w, self.device = w, device
+
+    def __getitem__(self, name):
+        return self.w[name].to(self.device)
+
+
 def decoder_layer(x, w: dict, l: int, config: dict, positions, inv_freq, window):
     """One pre-norm block: x += Wo attn(rope(q), rope(k), v); x += mlp(norm(x))
     -- kernels/gollmgo_model.cu:551-792 (run_layer)."""
@@ -172,6 +185,7 @@ def decoder_layer(x, w: dict, l: int, config: dict, positions, inv_freq, window)
     eps = config.get("rms_norm_eps", 1e-5)
     p = f"model.layers.{l}."
     T = x.shape[0]
+    w = _On(w, x.device)
     h = rms_norm(x, w[p + "input_layernorm.weight"], eps)
     q = (h @ w[p + "self_attn.q_proj.weight"].to(torch.float64).T).view(T, nh, d)
     k = (h @ w[p + "self_attn.k_proj.weight"].to(torch.float64).T).view(T, nkv, d)
@@ -187,22 +201,26 @@ def decoder_layer(x, w: dict, l: int, config: dict, positions, inv_freq, window)
     return x
 
 
-def forward(w: dict, config: dict, token_ids) -> torch.Tensor:
+def forward(w: dict, config: dict, token_ids, device=None, rows=None) -> torch.Tensor:
     """Logits [T, V] (float64) of one whole sequence starting at position 0
-    -- kernels/gollmgo_model.cu:862-899 (gollmgo_model_forward)."""
+    -- kernels/gollmgo_model.cu:862-899 (gollmgo_model_forward).  With ``rows`` only the
+    logits at those positions, [len(rows), V]; with ``device`` the arithmetic runs there."""
     nh, nkv, d = _cfg(config)
     T = len(token_ids)
-    positions = torch.arange(T)
+    dev = torch.device(device) if device is not None else w["model.embed_tokens.weight"].device
+    positions = torch.arange(T, device=dev)
     inv_freq = rope_inv_freq(d, float(config.get("rope_theta", 10000.0)),
-                             config.get("rope_scaling"))
+                             config.get("rope_scaling")).to(dev)
     windows = layer_windows(config)
-    x = embed(w["model.embed_tokens.weight"], token_ids)
+    x = embed(w["model.embed_tokens.weight"], token_ids).to(dev)
     for l in range(config["num_hidden_layers"]):
         x = decoder_layer(x, w, l, config, positions, inv_freq, windows[l])
-    x = rms_norm(x, w["model.norm.weight"], config.get("rms_norm_eps", 1e-5))
+    if rows is not None:
+        x = x[torch.as_tensor(list(rows), dtype=torch.long, device=dev)]
+    x = rms_norm(x, w["model.norm.weight"].to(dev), config.get("rms_norm_eps", 1e-5))
     head = w["model.embed_tokens.weight"] if config.get("tie_word_embeddings", False) \
         else w["lm_head.weight"]
-    return x @ head.to(torch.float64).T
+    return x @ head.to(dev).to(torch.float64).T
 
 
 # --------------------------------------------------------------------------- sampling

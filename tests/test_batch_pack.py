@@ -16,7 +16,8 @@ def run(native: bool, seed: int, fixed: bool):
     rng = random.Random(seed)
     needs = [PagedKVNeed(2, 16, None), PagedKVNeed(2, 16, 20), PagedKVNeed(2, 16, None)]   # two groups
     cm = CacheManager(needs, 8, 64, 6, dtype=torch.bfloat16, device="cuda")
-    bb = BatchBuilder(cm, "cuda")
+    from gollmgo_b200.parts import QueryTiles
+    bb = BatchBuilder(cm, "cuda", query_tiles=[QueryTiles(16), QueryTiles(32, most_keys_first=True)])
     bb.native_decode = native
     static = torch.zeros(4096, dtype=torch.int32, device="cuda") if fixed else None
     live, out, next_id = [], [], 0
@@ -43,7 +44,7 @@ def run(native: bool, seed: int, fixed: bool):
                "slots": sb.state_slots[:B].tolist(), "rows": sb.logit_rows.tolist(), "dec": sb.dec_seqs.tolist(),
                "sm": [s[:B].tolist() for s in sb.slot_mapping],
                "bt": [t.view(B, sb.bt_stride).tolist() for t in sb.block_tables],
-               "facts": (sb.num_tokens, sb.num_seqs, sb.num_logit_rows, sb.num_tiles, sb.num_decode, sb.bt_stride,
+               "facts": (sb.num_tokens, sb.num_seqs, sb.num_logit_rows, sb.num_portions, sb.num_decode, sb.bt_stride,
                          sb.request_ids, sb.q_lens, sb.q_starts, sb.state_slot_list)}
         if fixed:
             # columns beyond the ones in use keep what an earlier step left there; compare what a kernel may read

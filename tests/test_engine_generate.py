@@ -214,7 +214,8 @@ def test_steps_with_a_long_context_are_steps_of_their_own(tmp_path, cuda_device,
     long decoding against the whole sequence, before and after the change."""
     import importlib
     R = importlib.import_module("gollmgo_b200.engine.runner")
-    monkeypatch.setattr(R, "LONG_CONTEXT", 60)
+    A = importlib.import_module("gollmgo_b200.parts.attention")
+    monkeypatch.setattr(A, "LONG_CONTEXT", 60)           # the attention tags such steps; the runner only carries the tag
     from gollmgo_b200.config import EngineConfig
     from gollmgo_b200.engine.batch import StepEntry
     cfg, page, std, jitter = tiny_configs.get(name)
@@ -223,7 +224,6 @@ def test_steps_with_a_long_context_are_steps_of_their_own(tmp_path, cuda_device,
     runner = R.load_runner(d, EngineConfig(dtype="bfloat16", block_size=page, num_blocks=96, max_batch_size=4,
                                            max_token_budget=64, max_model_len=256))
     mixer = runner.model.blocks[0].mixer
-    A = importlib.import_module("gollmgo_b200.parts.attention")
     assert A.decode_splits(2, mixer._ctas_per_split, mixer.num_sms, mixer._cluster_cap, True) > 8
     seqs = tt.random_requests(cfg["vocab_size"], [140, 90], seed=9)
     refs = tt.plain_logits(w, cfg, seqs)
@@ -243,7 +243,8 @@ def test_steps_with_a_long_context_are_steps_of_their_own(tmp_path, cuda_device,
         for j, n in enumerate(step):
             got[n].append(out[j:j + 1])
     kinds = set(runner._graphs)
-    assert 2 in kinds and (2, True) in kinds and (1, True) in kinds, kinds
+    long = (A.LONG_TAG,)
+    assert 2 in kinds and (2, long) in kinds and (1, long) in kinds, kinds
     for n in names:
         rows = torch.cat(got[n])
         ref = refs[n][:rows.shape[0]]
@@ -326,6 +327,19 @@ def test_command_line_generate_and_bench(models):
     assert p.returncode == 0, p.stderr
     res = json.loads(p.stdout)
     assert res["num_prompts"] == 6 and res["tokens_per_second"] > 0 and res["error_count"] == 0
+    # lengths drawn from a seed: the same workload twice, every request served, the step counters kept
+    runs = []
+    for _ in range(2):
+        p = subprocess.run(base + ["bench", *common, "--mode", "offline", "--num-prompts", "7", "--prompt-len-range",
+                                   "3,20", "--output-len-range", "2,9", "--workload-seed", "5"],
+                           capture_output=True, text=True, cwd=root)
+        assert p.returncode == 0, p.stderr
+        runs.append(json.loads(p.stdout))
+    a, b = runs
+    assert a["prompt_tokens"] == b["prompt_tokens"] and a["output_tokens"] == b["output_tokens"]
+    assert 7 * 3 <= a["prompt_tokens"] <= 7 * 20 and 7 * 2 <= a["output_tokens"] <= 7 * 9
+    assert a["engine_steps"] > 0 and 1 <= a["mean_batch"] <= 4 and a["pages_high_water"] > 0
+    assert a["error_count"] == 0 and a["prompt_len_range"] == [3, 20]
     for mode, extra in (("decode", ["--batch", "3", "--context", "20", "--output-len", "8"]),
                         ("prefill", ["--prompt-len", "40"])):
         args = [a for a in common if a not in ("--num-blocks", "32")]

@@ -70,7 +70,7 @@ def test_position_part_tables(kit):
 def run_mixer(kit, mixer, need, x_parts, dtype, page):
     """Step the mixer over one sequence cut into the given portions; return all outputs."""
     cm = kit.CacheManager([need], page, 64, 4, dtype=dtype, device="cuda")
-    bb = kit.BatchBuilder(cm, "cuda")
+    bb = kit.BatchBuilder(cm, "cuda", query_tiles=getattr(mixer, "query_tiles", lambda: ())())
     cm.admit("s")
     outs = []
     for x in x_parts:
@@ -165,7 +165,7 @@ def test_block_is_the_plain_decoder_layer(kit, dtype):
     x0 = torch.randn(T, 48)
     want = P.decoder_layer(x0.double(), w, 0, cfg, torch.arange(T), P.rope_inv_freq(16, 10000.0, None), None)
     cm = kit.CacheManager([mixer.cache_need()], 16, 16, 2, dtype=dtype, device="cuda")
-    bb = kit.BatchBuilder(cm, "cuda")
+    bb = kit.BatchBuilder(cm, "cuda", query_tiles=mixer.query_tiles())
     cm.admit("s")
     batch = bb.build([kit.StepEntry("s", [0] * T, [])])
     resid = x0.cuda().clone()
@@ -217,7 +217,7 @@ def test_two_blocks_of_a_short_step_with_norms_inside_the_products(kit, cuda_dev
     for l in range(2):
         want = P.decoder_layer(want, w, l, cfg, torch.arange(T), inv, None)
     cm = kit.CacheManager([blocks[0][1].cache_need(), blocks[1][1].cache_need()], 16, 16, 2, dtype=dtype, device="cuda")
-    bb = kit.BatchBuilder(cm, "cuda")
+    bb = kit.BatchBuilder(cm, "cuda", query_tiles=blocks[0][1].query_tiles())
     cm.admit("s")
     batch = bb.build([kit.StepEntry("s", [0] * T, [])])
     resid = x0.cuda().clone()

@@ -145,3 +145,92 @@ def test_toy_mixer_registers_builds_and_steps(tmp_path, cuda_device):
     runner.release("a"), runner.release("b")
     runner.cache.audit()
     assert runner.cache.slots.num_free == runner.cache.slots.max_requests
+
+
+class TileProbeMixer:
+    """A mixer without cache or state that asks the batch builder for an index list of its own
+    (tiles of 32 query rows, those with most keys first) and tags steps of three or more
+    sequences.  It records what it is given; y = x W^T."""
+    seen = []
+
+    def __init__(self, spec, ctx):
+        from gollmgo_b200.parts import QueryTiles
+        self.hidden = int(spec["hidden_size"])
+        self.need = QueryTiles(32, most_keys_first=True)
+        self.w = None
+
+    def cache_need(self):
+        return None
+
+    def query_tiles(self):
+        return [self.need]
+
+    def step_tags(self, facts):
+        return ("crowd",) if facts.num_seqs >= 3 else ()
+
+    def weights(self):
+        from gollmgo_b200.weights import WeightSpec
+        return {"proj.weight": WeightSpec((self.hidden, self.hidden))}
+
+    def load(self, get):
+        self.w = get("proj.weight").float()
+
+    def forward(self, x, batch, cache, writes_cache=True):
+        tl = batch.tiles[self.need]
+        TileProbeMixer.seen.append((list(zip(tl.seq[:tl.count].tolist(), tl.q0[:tl.count].tolist())) if tl.count else [],
+                                    batch.tags, batch.num_portions, sorted(k.height for k in batch.tiles)))
+        return (x.float() @ self.w.T).to(x.dtype)
+
+
+def probe_spec(cfg):
+    from gollmgo_b200.parts import LayerSpec, ModelSpec, PartSpec, RunEntry
+    norm = PartSpec("rmsnorm", {"size": H, "eps": 1e-5})
+    ffn = PartSpec("gated_mlp", {"hidden_size": H, "intermediate_size": I})
+    layer = LayerSpec(PartSpec("pre_norm"), PartSpec("toy_tile_probe", {"hidden_size": H}), ffn, norm, norm,
+                      mixer_prefix="p.mix.", ffn_prefix="p.ffn.", mixer_norm_name="p.n1", ffn_norm_name="p.n2")
+    return ModelSpec("ProbeForCausalLM", V, H, (layer,), (RunEntry(0, 0),), norm, tie_embeddings=True,
+                     embed_name="p.embed", final_norm_name="p.norm", head_name="p.head", max_positions=512)
+
+
+def test_a_mixer_gets_the_index_lists_and_step_tags_it_declares(tmp_path, cuda_device):
+    """The batch builder builds exactly the lists the model's mixers ask for (here one list of
+    32-row tiles and nothing of the attention kernels'), and the runner keys its captured
+    steps by the tags the parts give, without knowing either."""
+    from gollmgo_b200.config import EngineConfig, register_architecture
+    from gollmgo_b200.engine.batch import StepEntry
+    from gollmgo_b200.engine.runner import load_runner
+    from gollmgo_b200.parts import register_mixer
+    from gollmgo_b200.weights import write_random_model
+    register_mixer("toy_tile_probe", TileProbeMixer)
+    register_architecture("ProbeForCausalLM", lambda d: d, probe_spec)
+    d = write_random_model(str(tmp_path / "probe"), {"architectures": ["ProbeForCausalLM"]}, seed=4, dtype="float32",
+                           std=0.2)
+    w = {k: v.double() for k, v in load_file(os.path.join(d, "model.safetensors")).items()}
+    runner = load_runner(d, EngineConfig(dtype="float32", block_size=8, num_blocks=8, max_batch_size=4,
+                                         max_token_budget=256))
+    assert not runner.cache.groups                                   # nothing is paged for this model
+    TileProbeMixer.seen.clear()
+    g = torch.Generator().manual_seed(1)
+    toks = {r: torch.randint(0, V, (n,), generator=g).tolist() for r, n in (("a", 70), ("b", 1), ("c", 33))}
+    out = runner.step([StepEntry(r, t, [len(t) - 1]) for r, t in toks.items()]).cpu().double()
+    tiles, tags, portions, heights = TileProbeMixer.seen[-1]
+    assert heights == [32] and portions == 2 and tags == ("crowd",)
+    assert tiles == [(0, 64), (0, 32), (2, 32), (0, 0), (2, 0)]      # most keys first; the single token has no tile
+    # the model is position-free: every row is a function of its own token
+    def plain(t):
+        x = P.embed(w["p.embed"], [t])
+        x = x + P.rms_norm(x, w["p.n1"], 1e-5) @ w["p.mix.proj.weight"].T
+        x = x + P.gated_mlp(P.rms_norm(x, w["p.n2"], 1e-5), w["p.ffn.gate_proj.weight"], w["p.ffn.up_proj.weight"],
+                            w["p.ffn.down_proj.weight"])
+        return (P.rms_norm(x, w["p.norm"], 1e-5) @ w["p.embed"].T)[0]
+    for i, r in enumerate(toks):
+        torch.testing.assert_close(out[i], plain(toks[r][-1]), rtol=2e-4, atol=2e-4)
+    # decode-only steps: captured per (bucket, tags)
+    TileProbeMixer.seen.clear()
+    runner.step([StepEntry(r, [5], [0]) for r in ("a", "b", "c")])
+    runner.step([StepEntry(r, [6], [0]) for r in ("a", "b")])
+    assert (4, ("crowd",)) in runner._graphs and 2 in runner._graphs
+    assert {s[1] for s in TileProbeMixer.seen} == {("crowd",), ()} and all(s[0] == [] for s in TileProbeMixer.seen)
+    for r in toks:
+        runner.release(r)
+    runner.cache.audit()

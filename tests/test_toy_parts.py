@@ -169,3 +169,78 @@ def test_toy_feed_forward_position_encoding_and_block(tmp_path, cuda_device):
     torch.testing.assert_close(torch.cat(rows["b"]), ref_b, rtol=2e-4, atol=2e-4)
     runner.release("a"), runner.release("b")
     runner.cache.audit()
+
+
+class LearnedPositionTable:
+    """A learned vector per absolute position, added to the embedded tokens before the first layer."""
+    interleaved = False
+
+    def __init__(self, spec, ctx):
+        self.max_pos, self.hidden = int(spec["max_positions"]), int(spec["hidden_size"])
+        self.table = None
+
+    def rope_table(self):
+        return None
+
+    def weights(self):
+        from gollmgo_b200.weights import WeightSpec
+        return {"table": WeightSpec((self.max_pos, self.hidden))}
+
+    def load(self, get):
+        self.table = get("table").float()
+
+    def add_to_embedding(self, resid, batch):
+        T = resid.shape[0]
+        resid += self.table[batch.positions[:T].long()]
+
+
+def learned_positions_spec(cfg):
+    """One attention layer with no position encoding of its own; positions enter at the embedding."""
+    from gollmgo_b200.parts import LayerSpec, ModelSpec, PartSpec, RunEntry
+    norm = PartSpec("rmsnorm", {"size": H, "eps": 1e-5})
+    attn = PartSpec("attention", {"hidden_size": H, "num_heads": NH, "num_kv_heads": NKV, "head_dim": D,
+                                  "window": None, "position": PartSpec("none")})
+    layer = LayerSpec(PartSpec("pre_norm"), attn, PartSpec("gated_mlp", {"hidden_size": H, "intermediate_size": I}),
+                      norm, norm, mixer_prefix="l.mix.", ffn_prefix="l.ff.", mixer_norm_name="l.n1", ffn_norm_name="l.n2")
+    return ModelSpec("LearnedPosForCausalLM", V, H, (layer,), (RunEntry(0, 0),), norm, True, "l.embed", "l.norm",
+                     "l.head", MAXPOS,
+                     embed_position=PartSpec("toy_learned_table", {"max_positions": MAXPOS, "hidden_size": H}),
+                     embed_position_prefix="l.pos.")
+
+
+def test_a_position_encoding_at_the_embedding(tmp_path, cuda_device):
+    """A position encoding that is no part of any mixer: named in the ModelSpec, it gets its tensors
+    from the checkpoint and the step's positions from the batch, whole and in portions alike."""
+    from gollmgo_b200.config import EngineConfig, register_architecture
+    from gollmgo_b200.engine.batch import StepEntry
+    from gollmgo_b200.engine.runner import load_runner
+    from gollmgo_b200.parts import register_position
+    from gollmgo_b200.weights import write_random_model
+    register_position("toy_learned_table", LearnedPositionTable)
+    register_architecture("LearnedPosForCausalLM", lambda d: d, learned_positions_spec)
+    d = write_random_model(str(tmp_path / "lp"), {"architectures": ["LearnedPosForCausalLM"]}, seed=6,
+                           dtype="float32", std=0.2, norm_jitter=0.1)
+    w = {k: v.double() for k, v in load_file(os.path.join(d, "model.safetensors")).items()}
+    assert tuple(w["l.pos.table"].shape) == (MAXPOS, H)
+    g = torch.Generator().manual_seed(2)
+    toks = torch.randint(0, V, (29,), generator=g).tolist()
+    T = len(toks)
+    x = P.embed(w["l.embed"], toks) + w["l.pos.table"][:T]
+    h = P.rms_norm(x, w["l.n1"], 1e-5)
+    q = (h @ w["l.mix.q_proj.weight"].T).view(T, NH, D)
+    k = (h @ w["l.mix.k_proj.weight"].T).view(T, NKV, D)
+    v = (h @ w["l.mix.v_proj.weight"].T).view(T, NKV, D)
+    x = x + P.attention(q, k, v).reshape(T, NH * D) @ w["l.mix.o_proj.weight"].T
+    x = x + P.gated_mlp(P.rms_norm(x, w["l.n2"], 1e-5), w["l.ff.gate_proj.weight"], w["l.ff.up_proj.weight"],
+                        w["l.ff.down_proj.weight"])
+    want = P.rms_norm(x, w["l.norm"], 1e-5) @ w["l.embed"].T
+    runner = load_runner(d, EngineConfig(dtype="float32", block_size=8, num_blocks=16, max_batch_size=2,
+                                         max_token_budget=64))
+    got = runner.step([StepEntry("w", toks, range(T))]).cpu().double()
+    torch.testing.assert_close(got, want, rtol=2e-4, atol=2e-4)
+    rows = []
+    for lo, hi in ((0, 11), (11, 13), (13, 28), (28, 29)):
+        rows.append(runner.step([StepEntry("c", toks[lo:hi], range(hi - lo))]).cpu().double())
+    torch.testing.assert_close(torch.cat(rows), want, rtol=2e-4, atol=2e-4)
+    runner.release("w"), runner.release("c")
+    runner.cache.audit()

@@ -35,7 +35,9 @@ def test_replay_matches_plain(tmp_path, cuda_device, name, dtype):
     out = str(tmp_path / "out")
     tt.run_trace(model_dir, dtype, trace, out, block_size=page)
     worst = tt.compare(trace, out, reference, config["vocab_size"], TOL[dtype])
-    print(f"{name} {dtype}: {len(trace.steps)} steps, pool {trace.peak} tokens "
+    pool, asked, shared = tt.pages_were_used_again(trace, out + "/pages.jsonl", page)
+    print(f"{name} {dtype}: {len(trace.steps)} steps, pool {trace.peak} tokens = {pool} pages for {asked} "
+          f"pages asked in all, {shared} page ids held by several requests "
           f"(single-request peak {peak_single}), worst relative error {worst:.2e}")
 
 
@@ -60,3 +62,4 @@ def test_pages_given_back_are_never_read(tmp_path, cuda_device, name, dtype):
     env = dict(os.environ, GOLLMGO_B200_POISON_FREED="1")
     tt.run_trace(model_dir, dtype, trace, out, block_size=page, env=env)
     tt.compare(trace, out, reference, config["vocab_size"], TOL[dtype])
+    tt.pages_were_used_again(trace, out + "/pages.jsonl", page)

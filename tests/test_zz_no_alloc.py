@@ -1,9 +1,12 @@
 """The entry point for callers that cannot allocate device memory
 (gg_attn_decode_noalloc, csrc/no_alloc.h): called through its exported C symbol,
 twice in a row, and compared with the ordinary entry point that takes scratch
-buffers from the caller.  The second call uses other inputs, so anything the first
-call left in the built-in scratch would show.  This file sorts last on purpose: if
-it fails, every other test has already run."""
+buffers from the caller and with a plain float64 attention.  The second call uses other
+inputs, so anything the first call left in the built-in scratch would show.  One case has
+more slices than a thread-block cluster holds: only then does the bfloat16 kernel put its
+partial results into the built-in array (up to eight slices merge inside a cluster, through
+shared memory).  This file sorts last on purpose: if it fails, every other test has already
+run."""
 import ctypes
 import math
 import random
@@ -36,8 +39,24 @@ def _case(seed, nh, nkv, d, page, ctxs, dtype):
                 dec=torch.arange(B, dtype=torch.int32, device="cuda"), B=B)
 
 
+def _plain_attention(c, nh, nkv, d, page):
+    """softmax(q k^T / sqrt(d)) v over each sequence's pages, in float64."""
+    out = torch.empty(c["B"], nh * d, dtype=torch.float64, device="cuda")
+    group = nh // nkv
+    for b in range(c["B"]):
+        n = int(c["ctx"][b])
+        pages = c["bt"][b, :-(-n // page)].long()
+        k = c["kc"][pages].double().permute(1, 0, 2, 3).reshape(nkv, -1, d)[:, :n]      # [nkv, n, d]
+        v = c["vc"][pages].double().permute(1, 0, 2, 3).reshape(nkv, -1, d)[:, :n]
+        q = c["q"][b].double().view(nkv, group, d)
+        p = torch.softmax(q @ k.transpose(1, 2) / math.sqrt(d), dim=-1)
+        out[b] = (p @ v).reshape(-1)
+    return out
+
+
 @pytest.mark.parametrize("dtype,nh,nkv,d,page,splits", [
-    (torch.bfloat16, 32, 8, 128, 16, 4),      # tensor-core kernel
+    (torch.bfloat16, 32, 8, 128, 16, 4),      # tensor-core kernel, slices merged inside a cluster
+    (torch.bfloat16, 32, 8, 128, 16, 11),     # more slices than a cluster holds: partial results in the built-in array
     (torch.float32, 6, 2, 48, 8, 3),          # general kernel
 ])
 def test_no_alloc_entry_matches_the_ordinary_one(cuda_device, dtype, nh, nkv, d, page, splits):
@@ -66,6 +85,7 @@ def test_no_alloc_entry_matches_the_ordinary_one(cuda_device, dtype, nh, nkv, d,
         assert torch.cuda.memory_allocated() == before
         assert torch.isfinite(got.float()).all()
         torch.testing.assert_close(got.float(), want.float(), **tol)
+        torch.testing.assert_close(got.double(), _plain_attention(c, nh, nkv, d, page), **tol)
 
 
 def test_no_alloc_entry_refuses_what_does_not_fit(cuda_device):

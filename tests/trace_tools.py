@@ -32,6 +32,7 @@ class Trace:
         self.steps = []
         self.expect = {}          # step -> [(request name, position)]
         self.live = {}            # trace id -> tokens held
+        self.totals = {}          # trace id -> tokens it held when it ended (or holds)
         self.peak = 0
 
     def add(self, entries, end=()):
@@ -43,6 +44,7 @@ class Trace:
             rec["entries"].append({"id": tid, "tokens": list(tokens), "want": list(want)})
             exp.extend((name, start + w) for w in want)
             self.live[tid] = self.live.get(tid, 0) + len(tokens)
+            self.totals[tid] = self.live[tid]
         self.peak = max(self.peak, sum(round64(v) for v in self.live.values()))
         for tid in end:
             self.live.pop(tid, None)
@@ -117,10 +119,13 @@ def mixed(trace, requests, max_live=4, seed=0, tag="m"):
 
 
 def run_trace(model_dir, dtype, trace, out_dir, block_size=16, extra_args=(), timeout=600, env=None):
-    """Drive bin/trace_run: one step a line, waiting for its 'done' before the next."""
+    """Drive bin/trace_run: one step a line, waiting for its 'done' before the next.  The
+    pool is the trace's peak of live tokens and nothing more; which request held which page
+    is logged to <out_dir>/pages.jsonl."""
     os.makedirs(out_dir, exist_ok=True)
     cmd = [sys.executable, TRACE_RUN, "--model", model_dir, "--dtype", dtype, "--out", out_dir,
-           "--max-tokens", str(trace.peak), "--block-size", str(block_size), *extra_args]
+           "--max-tokens", str(trace.peak), "--block-size", str(block_size),
+           "--debug-pages", os.path.join(out_dir, "pages.jsonl"), *extra_args]
     proc = subprocess.Popen(cmd, stdin=subprocess.PIPE, stdout=subprocess.PIPE, text=True, env=env)
     try:
         for rec in trace.steps:
@@ -134,6 +139,28 @@ def run_trace(model_dir, dtype, trace, out_dir, block_size=16, extra_args=(), ti
         if proc.poll() is None:
             proc.kill()
     assert rc == 0, f"trace_run exited with {rc}"
+
+
+def pages_were_used_again(trace, page_log_path, block_size):
+    """What makes a replay a test of page reuse, asserted instead of assumed: the pool (the
+    trace's peak, which is what --max-tokens is given) holds fewer pages than the trace's
+    requests take together, and some page id was held by two different requests in the course
+    of the trace.  Returns (pool pages, pages of all requests, page ids held by more than one)."""
+    pool = -(-trace.peak // 64) * 64 // block_size
+    asked = sum(-(-n // block_size) for n in trace.totals.values())
+    assert pool < asked, f"the pool of {pool} pages holds all {asked} pages the trace ever asks for"
+    owners = {}
+    with open(page_log_path) as f:
+        for line in f:
+            rec = json.loads(line)
+            for rid, groups in rec["pages"].items():
+                for g, pages in enumerate(groups):
+                    for p in pages:
+                        if p >= 0:
+                            owners.setdefault((g, p), set()).add(rid)
+    shared = [k for k, v in owners.items() if len(v) > 1]
+    assert shared, "no page was ever held by two different requests"
+    return pool, asked, len(shared)
 
 
 def plain_logits(weights, config, requests):
