@@ -272,8 +272,9 @@ def main() -> int:
         n_tok += len(eng.step())
     torch.cuda.synchronize(dev)
     e2e_s = time.perf_counter() - t0
-    lay = runner._graphs[next(b for b in sorted(runner._graphs) if b >= B)].meta.numel() * 4 \
-        if runner._graphs else 0
+    # bytes of the step's packed metadata (token ids, positions, block tables, ...) that go to the device
+    metas = sorted((k[0] if isinstance(k, tuple) else k, c.meta.numel() * 4) for k, c in runner._graphs.items())
+    lay = next((nbytes for bucket, nbytes in metas if bucket >= B), 0)
     eng.stop()
     e2e = {"value": round(n_tok / e2e_s, 1), "unit": "tokens/s", "h2d_bytes_per_step": int(lay),
            "d2h_bytes_per_step": 4 * B}

@@ -61,6 +61,7 @@ class StepBatch:
     tiles: "dict[QueryTiles, TileList]"    # the index lists the model's mixers asked for
     dec_seqs: torch.Tensor
     tags: tuple = ()                       # the step's kind, as the model's parts tagged it (set by the runner)
+    facts: object = None                   # the StepFacts the tags were made from (set by the runner)
     slot_mapping: List[torch.Tensor]
     block_tables: List[torch.Tensor]
     # host side

@@ -157,15 +157,16 @@ class ModelRunner:
         # attention: some live request holds a long context).  Steps with different tags are steps
         # of different kinds: a part may choose differently for them, so each kind has captured
         # graphs of its own.  The runner only carries the tags; it does not know what they mean.
-        facts = StepFacts(len(entries), sum(len(e.tokens) for e in entries), decode_only,
-                          int(self.cache.ntok.max()))
-        tags = self.model.step_tags(facts)
+        n_tokens, longest = sum(len(e.tokens) for e in entries), int(self.cache.ntok.max())
         if decode_only and self.ecfg.cuda_graphs:
             bucket = next((b for b in GRAPH_BUCKETS if b >= len(entries)), None)
             if bucket is not None and bucket <= self.ctx.max_seqs:
-                return self._graph_step(entries, bucket, tags)
+                # a captured step runs the bucket's number of sequences (the rest are padding)
+                facts = StepFacts(bucket, bucket, True, longest)
+                return self._graph_step(entries, bucket, facts, self.model.step_tags(facts))
+        facts = StepFacts(len(entries), n_tokens, decode_only, longest)
         batch = self.builder.build(entries)
-        batch.tags = tags
+        batch.facts, batch.tags = facts, self.model.step_tags(facts)
         batch.prev_tokens = self.last_tokens if batch.token_src is not None else None
         logits = self.model.forward(batch, self.caches)
         self.steps += 1
@@ -182,7 +183,7 @@ class ModelRunner:
     def _graph_stride(self) -> int:
         return -(-self.max_model_len // self.cache.page_size)
 
-    def _graph_step(self, entries, bucket: int, tags: tuple = ()) -> torch.Tensor:
+    def _graph_step(self, entries, bucket: int, facts: StepFacts, tags: tuple = ()) -> torch.Tensor:
         key = (bucket, tags) if tags else bucket
         cs = self._graphs.get(key)
         stride = self._graph_stride()
@@ -191,7 +192,7 @@ class ModelRunner:
             cs = _CapturedStep(torch.zeros(lay.size, dtype=torch.int32, device=self.device))
             self._graphs[key] = cs
         batch = self.builder.build(entries, fixed_seqs=bucket, fixed_stride=stride, static_dev=cs.meta)
-        batch.tags = tags
+        batch.facts, batch.tags = facts, tags
         batch.prev_tokens = self.last_tokens
         if cs.graph is None:
             torch.cuda.synchronize(self.device)
@@ -214,30 +215,47 @@ class ModelRunner:
         return cs.logits[:len(entries)]
 
     def capture_graphs(self, up_to: Optional[int] = None) -> int:
-        """Capture the decode step of every batch bucket up to ``up_to`` sequences (default:
-        the largest batch) now, so that no request meets the tens of milliseconds of a
-        capture in the middle of its generation when the batch grows or shrinks into a bucket
-        for the first time.  Uses a request of its own of a few tokens and gives its page
-        back.  Returns the number of buckets captured."""
+        """Capture now the decode step of every batch bucket up to ``up_to`` sequences (default:
+        the largest batch), in every kind that the model's parts tell apart as contexts grow to
+        the longest sequence allowed (the tags of ``step_tags`` for contexts of 1, 2, 4, ...
+        tokens), so that no request meets the tens of milliseconds of a capture in the middle of
+        its generation when the batch or its context grows into a new kind for the first time.
+        Uses a request of its own of a few tokens and gives its page back.  Returns the number
+        of steps captured."""
         if not self.ecfg.cuda_graphs or self.device.type != "cuda":
             return 0
         rid = "__capture__"
         limit = min(up_to or self.ctx.max_seqs, self.ctx.max_seqs)
-        todo = [b for b in GRAPH_BUCKETS if b <= limit and (b not in self._graphs or self._graphs[b].graph is None)]
+        contexts, c = [], 1
+        while c < 2 * self.max_model_len:
+            contexts.append(min(c, self.max_model_len))
+            c *= 2
+        todo = []
+        for bkt in (b for b in GRAPH_BUCKETS if b <= limit):
+            for c in contexts:
+                facts = StepFacts(bkt, bkt, True, c)
+                tags = self.model.step_tags(facts)
+                key = (bkt, tags) if tags else bkt
+                if (key not in self._graphs or self._graphs[key].graph is None) and all(k != key for k, _, _ in todo):
+                    todo.append((key, facts, tags))
         if not todo or len(todo) + 1 > self.max_model_len:
             return 0
         marks = [g.pool.high_water for g in self.cache.groups]
         self.cache.admit(rid)
         done = 0
         try:
-            for b in todo:
-                self._graph_step([StepEntry(rid, [0], [0])], b)
+            for key, facts, tags in todo:
+                if self.cache.num_tokens(rid) + 1 >= self.max_model_len:       # the request is full: start it again
+                    self.cache.free(rid)
+                    self.cache.admit(rid)
+                self._graph_step([StepEntry(rid, [0], [0])], facts.num_seqs, facts, tags)
                 done += 1
             torch.cuda.synchronize(self.device)
         except OutOfPages:
             pass                                   # a pool too small even for this: capture at first use instead
         finally:
-            self.cache.free(rid)
+            if rid in self.cache.requests:
+                self.cache.free(rid)
             for g, m in zip(self.cache.groups, marks):
                 g.pool.high_water = m
         return done

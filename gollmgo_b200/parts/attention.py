@@ -9,6 +9,7 @@ three weights stacked.
 """
 from __future__ import annotations
 
+import functools
 import math
 import os
 
@@ -35,63 +36,77 @@ MAX_SPLITS = 16
 # tiles of 16 rows (general kernel, csrc/attention.cu), of 64 (mma.sync, csrc/attention_mma.cu),
 # of 128 with the tiles that attend to most keys first (tcgen05, csrc/attention_tc.cu)
 TILES_GENERAL, TILES_MMA, TILES_TC = QueryTiles(16), QueryTiles(64), QueryTiles(128, most_keys_first=True)
-# From this many tokens in some live request's cache the attention tags a step "long_context": a
-# step of its own kind (captured separately), for which the count of slices is
-# chosen for contexts of LONG_TILES tiles, among up to MAX_SPLITS_LONG.  One sequence at
-# 32768 tokens: 8 slices in a cluster are 64 CTAs for 134 MB of cache a layer (87 us); 32
-# slices and a merge kernel are 256 CTAs.
-LONG_CONTEXT = int(os.environ.get("GOLLMGO_B200_LONG_CONTEXT", "8192"))
-LONG_TAG = "long_context"
-LONG_TILES = 256
-MAX_SPLITS_LONG = 64
 FORCED_SPLITS = int(os.environ.get("GOLLMGO_B200_DECODE_SPLITS", "0"))   # for measurements: this count, whatever the batch
 CTAS_PER_SM = 3            # decode attention CTAs resident on one SM (csrc/attention_mma.cu)
-ASSUMED_TILES = 32         # context the choice is tuned for: 32 tiles of 64 keys
-# The cost of a count of slices, in units of the time a CTA takes for one tile when it does
-# not have to share the memory bandwidth (about 1.6 us):
-SPLIT_OVERHEAD = 4         # fixed cost with a merge kernel (prologue, combine, merge launch)
-CLUSTER_OVERHEAD = 2       # fixed cost where the slices merge inside a cluster instead
-PER_SLICE = 0.3            # what every further slice adds (barriers, partial results to merge)
-WAVE_PENALTY = 4           # every further round of CTAs or clusters, beyond its tiles
-BANDWIDTH_TILE = 0.003     # a tile's share of the memory bandwidth: no count of slices gets below
-                           # tiles x this, however many CTAs work at once
+TILE_KEYS = 64             # keys of one tile of the decode kernels
+# Into how many slices the context of a decoded token is cut is chosen from the step itself: the
+# batch, and the longest context any live request holds, rounded up to a power of two of tiles
+# (the attention tags a step with the count it chose, so a captured step is replayed only for
+# steps that would choose the same).  The estimate is in microseconds and bytes.  What is
+# measured (B200, the decode kernel of csrc/attention_mma.cu) and what is derived:
+CTA_STREAM_BYTES_PER_US = 20480.0   # one CTA alone streams a 32 KB tile (64 keys x 128 x k, v x bfloat16) in 1.6 us
+HBM_BYTES_PER_US = 6.8e6            # what the kernel streams at best with every CTA busy: no choice gets below bytes / this
+SPLIT_OVERHEAD_US = 6.4             # fixed cost with a merge kernel (prologue, combine, merge launch)
+CLUSTER_OVERHEAD_US = 3.2           # fixed cost where the slices merge inside a cluster instead
+PER_SLICE_US = 0.48                 # what every further slice adds (barriers, partial results to merge)
+WAVE_PENALTY_US = 6.4               # every further round of CTAs or clusters, beyond its tiles
 CLUSTER_FILL = 0.9         # share of the cluster capacity that one round can count on: clusters are placed
                            # while the kernel before still drains, and a launch that needs every last place
                            # often waits for a second round (measured: a quarter of the launches, 11 us each).
                            # A launch of several rounds anyway fills every place (batch 32: three slices in
                            # two rounds, 52.8 us a layer, against 61.1 for whole contexts on 256 of 444 places)
+# Contexts of this many tiles or more (8192 tokens) of so few sequences that even the largest
+# cluster per pair leaves places empty may be cut into up to MAX_SPLITS_MANY slices, merged by a
+# kernel of their own.  One sequence at 32768 tokens: 8 slices in a cluster are 64 CTAs for
+# 134 MB of cache a layer (87 us); 32 slices and a merge kernel are 256 CTAs.
+MANY_SLICES_FROM_TILES = 128
+MAX_SPLITS_MANY = 64
+MAX_TILES = 1024
 
 
-def decode_splits(n_dec: int, ctas_per_split: int, num_sms: int, cluster_capacity=None,
-                  long_context: bool = False) -> int:
-    """Slices of the context per decoded token: the count with the least estimated time
-    max(bandwidth floor, rounds x tiles per slice) + overheads for a typical context.  It
-    depends only on the batch, never on the actual context lengths, so a captured step
-    stays valid as contexts grow.  cluster_capacity[s], where given and not 0, is how many
-    clusters of s slices the device holds at once: the decode kernel merges such slices
-    itself (csrc/attention_mma.cu).  Tuned on measured step times at batches 1 to 64."""
-    if FORCED_SPLITS > 0:
-        return FORCED_SPLITS
+def context_tiles(max_context: int, window=None) -> int:
+    """Tiles of the longest context (or of the window, if shorter), rounded up to a power of
+    two: the sizes the choice of slices is made for."""
+    keys = max(1, int(max_context))
+    if window:
+        keys = min(keys, int(window) + TILE_KEYS)
+    tiles = -(-keys // TILE_KEYS)
+    return min(MAX_TILES, 1 << (tiles - 1).bit_length())
+
+
+@functools.lru_cache(maxsize=4096)
+def _decode_splits(n_dec, ctas_per_split, num_sms, cluster_capacity, tiles, tile_bytes, forced):
+    if forced > 0:
+        return forced
     slots = CTAS_PER_SM * num_sms
     ctas = max(1, n_dec * ctas_per_split)
-    # (only where even the largest cluster per pair leaves places empty: larger batches stream
-    # long contexts at 0.8 of the copy bandwidth with the choice made for short ones)
-    long_context = long_context and ctas * 8 < slots
-    tiles = LONG_TILES if long_context else ASSUMED_TILES
-    floor = ctas * tiles * BANDWIDTH_TILE
+    tile_us = tile_bytes / CTA_STREAM_BYTES_PER_US
+    floor_us = ctas * tiles * tile_bytes / HBM_BYTES_PER_US
+    many = tiles >= MANY_SLICES_FROM_TILES and ctas * 8 < slots
     best, best_cost = 1, None
-    for s in range(1, (MAX_SPLITS_LONG if long_context else MAX_SPLITS) + 1):
+    for s in range(1, (MAX_SPLITS_MANY if many else MAX_SPLITS) + 1):
         cap = cluster_capacity[s] if cluster_capacity and s < len(cluster_capacity) else 0
         if cap > 0:
-            rounds, fixed = -(-ctas // cap), CLUSTER_OVERHEAD
+            rounds, fixed = -(-ctas // cap), CLUSTER_OVERHEAD_US
             if rounds == 1 and ctas > cap * CLUSTER_FILL:
                 rounds = 2
         else:
-            rounds, fixed = -(-ctas * s // slots), SPLIT_OVERHEAD
-        cost = max(floor, rounds * -(-tiles // s)) + fixed + PER_SLICE * s + WAVE_PENALTY * (rounds - 1)
+            rounds, fixed = -(-ctas * s // slots), SPLIT_OVERHEAD_US
+        cost = max(floor_us, rounds * -(-tiles // s) * tile_us) + fixed + PER_SLICE_US * s + WAVE_PENALTY_US * (rounds - 1)
         if best_cost is None or cost < best_cost - 1e-9:
             best, best_cost = s, cost
     return best
+
+
+def decode_splits(n_dec: int, ctas_per_split: int, num_sms: int, cluster_capacity=None, tiles: int = 32,
+                  tile_bytes: int = 32768) -> int:
+    """Slices of the context per decoded token: the count with the least estimated time
+    max(bytes / bandwidth, rounds x tiles per slice x time of a tile) + overheads, for contexts
+    of ``tiles`` tiles of ``tile_bytes`` bytes (keys and values of one kv head).
+    cluster_capacity[s], where given and not 0, is how many clusters of s slices the device
+    holds at once: the decode kernel merges such slices itself (csrc/attention_mma.cu)."""
+    cap = tuple(cluster_capacity) if cluster_capacity else None
+    return _decode_splits(n_dec, ctas_per_split, num_sms, cap, int(tiles), int(tile_bytes), FORCED_SPLITS)
 
 
 class Attention:
@@ -124,8 +139,10 @@ class Attention:
         if ctx.device.type == "cuda":
             self._cluster_cap = [0] + [ops.attn_decode_cluster_capacity(ctx.act_dtype, self.d, s, self.nh // self.nkv)
                                        for s in range(1, ops.ATTN_MAX_CLUSTER + 1)]
-        rows = max(n * decode_splits(n, self._ctas_per_split, self.num_sms, self._cluster_cap, lc)
-                   for n in range(1, ctx.max_seqs + 1) for lc in (False, True))
+        esize = torch.empty((), dtype=ctx.act_dtype).element_size()
+        self._tile_bytes = TILE_KEYS * self.d * 2 * esize          # keys and values of one kv head
+        rows = max(n * self._splits(n, TILE_KEYS << b) for n in range(1, ctx.max_seqs + 1)
+                   for b in range(MAX_TILES.bit_length()))
         ws.reserve("attn_part_o", rows * self.nh * self.d, torch.float32)
         ws.reserve("attn_part_ml", rows * self.nh * 2, torch.float32)
         self._flat_ok = (ctx.device.type == "cuda" and ctx.act_dtype == torch.bfloat16 and self.d in (64, 128)
@@ -151,8 +168,21 @@ class Attention:
                 need.append(TILES_TC)
         return need
 
+    def _splits(self, n_dec: int, max_context: int) -> int:
+        return decode_splits(n_dec, self._ctas_per_split, self.num_sms, self._cluster_cap,
+                             context_tiles(max_context, self.window), self._tile_bytes)
+
+    def _flat_step(self, n_dec: int) -> bool:
+        """More (token, kv head) pairs than CTAs fit at once: equal ranges of tiles, no slices."""
+        return bool(self._flat_ok and n_dec * self._ctas_per_split >= FLAT_DECODE_FILL * CTAS_PER_SM * self.num_sms)
+
     def step_tags(self, facts):
-        return (LONG_TAG,) if facts.max_context >= LONG_CONTEXT else ()
+        """The count of slices this step's decoded tokens would be cut into: a step that is
+        captured with one count is replayed only for steps that choose the same."""
+        n = facts.num_seqs if facts.decode_only else 0
+        if n == 0 or self._flat_step(n):
+            return ()
+        return (f"kv_slices={self._splits(n, facts.max_context)}",)
 
     def weights(self):
         return {"q_proj.weight": WeightSpec((self.nh * self.d, self.hidden)),
@@ -186,7 +216,9 @@ class Attention:
                                  ws.get("attn_flat_prefix", 1, n + 1), out, self.nh, self.nkv, self.d,
                                  self.ctx.page_size, window, self.scale)
             return
-        splits = decode_splits(n, self._ctas_per_split, self.num_sms, self._cluster_cap, LONG_TAG in batch.tags)
+        facts = getattr(batch, "facts", None)
+        longest = facts.max_context if facts is not None else max(s + q for s, q in zip(batch.q_starts, batch.q_lens))
+        splits = self._splits(n, longest)
         part_o = ws.get("attn_part_o", 1, n * self.nh * splits * self.d)
         part_ml = ws.get("attn_part_ml", 1, n * self.nh * splits * 2)
         if fused:
@@ -210,8 +242,7 @@ class Attention:
             self.position.apply(qkv, batch, self.nh, self.nkv, self.d)
         # a step of decoded tokens only: the decode kernel rotates and writes the cache itself
         table = self.position.rope_table()
-        flat_step = (self._flat_ok and batch.num_decode * self._ctas_per_split
-                     >= FLAT_DECODE_FILL * CTAS_PER_SM * self.num_sms)
+        flat_step = self._flat_step(batch.num_decode)
         fused = (FUSE_DECODE_ROPE and batch.num_decode > 0 and not batch.num_portions and ATTN_POLICY != "general"
                  and not flat_step
                  and not hasattr(self.position, "apply")

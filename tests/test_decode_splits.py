@@ -12,16 +12,32 @@ CAPACITY = [0, 444, 222, 142, 104, 82, 71, 56, 48]
 SMS = 148
 
 
-def splits(n, long_context=False, capacity=CAPACITY, ctas_per_split=8):
-    return A.decode_splits(n, ctas_per_split, SMS, capacity, long_context)
+def splits(n, tiles=32, capacity=CAPACITY, ctas_per_split=8, tile_bytes=32768):
+    return A.decode_splits(n, ctas_per_split, SMS, capacity, tiles, tile_bytes)
 
 
 def test_the_count_stays_within_its_bounds_and_depends_on_nothing_else():
     for n in range(1, 300):
-        for lc in (False, True):
-            s = splits(n, lc)
-            assert 1 <= s <= (A.MAX_SPLITS_LONG if lc else A.MAX_SPLITS)
-            assert s == splits(n, lc)                       # same batch, same answer: a captured step stays valid
+        for tiles in (1, 8, 32, 128, 512):
+            s = splits(n, tiles)
+            many = tiles >= A.MANY_SLICES_FROM_TILES
+            assert 1 <= s <= (A.MAX_SPLITS_MANY if many else A.MAX_SPLITS)
+            assert s == splits(n, tiles)                    # same batch and context size, same answer
+
+
+def test_contexts_are_rounded_up_to_a_power_of_two_of_tiles():
+    assert [A.context_tiles(c) for c in (1, 64, 65, 128, 129, 2048, 2049, 10 ** 7)] == [1, 1, 2, 2, 4, 32, 64, A.MAX_TILES]
+    assert A.context_tiles(5000, window=100) == 4           # a window bounds what a query reads: 164 keys at most
+    assert A.context_tiles(90, window=100) == 2
+
+
+def test_short_contexts_are_cut_less_and_small_heads_too():
+    assert splits(1, 1) == 1 and splits(8, 2) <= 2           # nothing to cut in one or two tiles
+    assert splits(1, 4) <= splits(1, 32) <= splits(1, 512)
+    assert splits(8, 8) <= splits(8, 32)
+    # a head size of 64 halves a tile's bytes: the fixed costs weigh more, never more slices than for 128
+    for n in (1, 2, 4, 8, 16):
+        assert splits(n, 32, tile_bytes=16384) <= splits(n, 32)
 
 
 def test_few_sequences_are_cut_into_many_slices_and_many_sequences_are_not():
@@ -49,13 +65,13 @@ def test_a_launch_of_several_rounds_fills_every_place():
     assert splits(32, capacity=tight) != 3
 
 
-def test_long_contexts_change_the_choice_only_where_clusters_leave_places_empty():
+def test_long_contexts_of_few_sequences_are_cut_beyond_a_cluster():
     for n in range(1, 300):
         if n * 8 * 8 >= A.CTAS_PER_SM * SMS:
-            assert splits(n, True) == splits(n, False)
-    assert splits(1, True) > 8 and splits(2, True) > 8 and splits(4, True) > 8
-    assert splits(1, True) * 8 <= A.CTAS_PER_SM * SMS        # one round of CTAs
-    assert splits(1, True) >= splits(2, True) >= splits(4, True)
+            assert splits(n, 256) <= A.MAX_SPLITS            # enough pairs to fill the device: no merge kernel needed
+    assert splits(1, 256) > 8 and splits(2, 256) > 8 and splits(4, 256) > 8
+    assert splits(1, 256) * 8 <= A.CTAS_PER_SM * SMS        # one round of CTAs
+    assert splits(1, 256) >= splits(2, 256) >= splits(4, 256)
 
 
 def test_without_clusters_the_merge_kernel_is_paid_for():
@@ -68,4 +84,4 @@ def test_without_clusters_the_merge_kernel_is_paid_for():
 @pytest.mark.parametrize("forced", [1, 3, 11])
 def test_a_fixed_count_for_measurements(monkeypatch, forced):
     monkeypatch.setattr(A, "FORCED_SPLITS", forced)
-    assert splits(1) == forced and splits(200, True) == forced
+    assert splits(1) == forced and splits(200, 256) == forced

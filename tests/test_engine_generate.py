@@ -207,15 +207,20 @@ def test_decode_kernel_for_large_batches_inside_the_engine(tmp_path, cuda_device
 
 
 @pytest.mark.parametrize("name", ["tiny_d", "tiny_e"])
-def test_steps_with_a_long_context_are_steps_of_their_own(tmp_path, cuda_device, monkeypatch, name):
-    """Once some live request's cache has reached the threshold of a long context (lowered here),
-    decode steps are captured separately and the attention cuts contexts into many more slices
-    (merged by a kernel of their own, most of them empty at these lengths): every logit row of
-    long decoding against the whole sequence, before and after the change."""
+def test_steps_are_captured_per_count_of_slices_as_contexts_grow(tmp_path, cuda_device, monkeypatch, name):
+    """The attention cuts the context of a decoded token into slices, how many it chooses from the
+    batch and the longest live context, and it tags the step with the count: the runner keeps a
+    captured step per (batch bucket, tags).  With the cost of a slice made small the count grows
+    with the context within the 140 tokens decoded here (up to 16 slices over three tiles, most
+    of them empty): every logit row of long decoding against the whole sequence, across the
+    changes of kind."""
     import importlib
     R = importlib.import_module("gollmgo_b200.engine.runner")
     A = importlib.import_module("gollmgo_b200.parts.attention")
-    monkeypatch.setattr(A, "LONG_CONTEXT", 60)           # the attention tags such steps; the runner only carries the tag
+    monkeypatch.setattr(A, "PER_SLICE_US", 0.001)
+    monkeypatch.setattr(A, "CLUSTER_OVERHEAD_US", 0.0)
+    monkeypatch.setattr(A, "SPLIT_OVERHEAD_US", 0.01)
+    A._decode_splits.cache_clear()
     from gollmgo_b200.config import EngineConfig
     from gollmgo_b200.engine.batch import StepEntry
     cfg, page, std, jitter = tiny_configs.get(name)
@@ -224,7 +229,7 @@ def test_steps_with_a_long_context_are_steps_of_their_own(tmp_path, cuda_device,
     runner = R.load_runner(d, EngineConfig(dtype="bfloat16", block_size=page, num_blocks=96, max_batch_size=4,
                                            max_token_budget=64, max_model_len=256))
     mixer = runner.model.blocks[0].mixer
-    assert A.decode_splits(2, mixer._ctas_per_split, mixer.num_sms, mixer._cluster_cap, True) > 8
+    assert mixer._splits(2, 40) < mixer._splits(2, 100) <= mixer._splits(2, 200)
     seqs = tt.random_requests(cfg["vocab_size"], [140, 90], seed=9)
     refs = tt.plain_logits(w, cfg, seqs)
     names = list(seqs)
@@ -242,9 +247,10 @@ def test_steps_with_a_long_context_are_steps_of_their_own(tmp_path, cuda_device,
         out = runner.step([StepEntry(n, [seqs[n][first[n] + t - 1]], [0]) for n in step]).cpu().double()
         for j, n in enumerate(step):
             got[n].append(out[j:j + 1])
-    kinds = set(runner._graphs)
-    long = (A.LONG_TAG,)
-    assert 2 in kinds and (2, long) in kinds and (1, long) in kinds, kinds
+    kinds = [k for k in runner._graphs if isinstance(k, tuple)]
+    assert len({tags for b, tags in kinds if b == 2}) >= 2, kinds            # batch 2 passed through several counts
+    assert any(b == 1 for b, _ in kinds), kinds                               # and the last sequence alone too
+    A._decode_splits.cache_clear()
     for n in names:
         rows = torch.cat(got[n])
         ref = refs[n][:rows.shape[0]]
@@ -262,7 +268,8 @@ def test_decode_steps_of_every_batch_size_are_captured_when_the_engine_is_built(
     reqs = list(tt.random_requests(cfg["vocab_size"], [5, 9, 3, 11, 6], seed=9).values())
     eng = Engine(d, dtype="bfloat16", block_size=page, num_blocks=32, max_batch_size=6, max_token_budget=64)
     want = {b for b in GRAPH_BUCKETS if b <= 6}
-    assert {b for b, c in eng.runner._graphs.items() if c.graph is not None} == want
+    bucket_of = lambda key: key[0] if isinstance(key, tuple) else key
+    assert {bucket_of(k) for k, c in eng.runner._graphs.items() if c.graph is not None} == want
     assert eng.runner.cache.free_pages() == 32 and not eng.runner.cache.requests
     graphs = {b: c.graph for b, c in eng.runner._graphs.items()}
     for i, r in enumerate(reqs):                               # different lengths: the batch shrinks step by step
