@@ -21,8 +21,14 @@
 //               memory lane), the row's 64 scores read once with tcgen05.ld and kept in
 //               registers, base-2 exponentials against a reference maximum that only moves
 //               (and O is only rescaled, through tcgen05.ld/st) when a row of the warp has
-//               outgrown it by 2^8; P goes to shared memory in the swizzled K-major layout.
-// Tensor memory per head: columns [0,64) and [64,128) scores, [128, 128 + d) O; head 1 at +256.
+//               outgrown it by 2^8; P goes back into tensor memory, as pairs of bfloat16 over the
+//               first 32 columns of the score buffer it came from, and is the A operand of the
+//               second product straight from there (no trip through shared memory, no proxy
+//               fence, and a head's next scores never wait for its P to be consumed: the two
+//               score buffers double as two P buffers; the tensor core runs its instructions in
+//               the order they were issued, so the scores after next overwrite a buffer only
+//               after the product that read P from it).
+// Tensor memory per head: columns [0,64) and [64,128) scores / P, [128, 128 + d) O; head 1 at +256.
 // All waits are bounded; a wait that runs out sets *status and the CTA winds down.
 #include "attention_common.cuh"
 #include "tc_common.cuh"
@@ -50,6 +56,18 @@ __device__ __forceinline__ void constexpr_mma(unsigned d_tmem, unsigned a_lo, un
       : "memory");
 }
 
+// The same with the A operand in tensor memory (lanes = rows, a 32-bit column = two bfloat16 of k).
+__device__ __forceinline__ void constexpr_mma_ta(unsigned d_tmem, unsigned a_tmem, unsigned b_lo, unsigned b_hi,
+                                                 unsigned idesc, bool accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t.reg .b64 db;\n\t"
+      "setp.ne.b32 p, %5, 0;\n\t"
+      "mov.b64 db, {%2, %3};\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], db, %4, {%6, %6, %6, %6}, p;\n\t}"
+      ::"r"(d_tmem), "r"(a_tmem), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"((unsigned)accumulate), "r"(0u)
+      : "memory");
+}
+
 struct At2Args {
   AttnArgs a;
   int num_pages;          // pages in the cache (an index >= this is filled with zeros)
@@ -73,13 +91,11 @@ attn_prefill_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
   const unsigned q_smem = base;                                   // [2 heads]
   const unsigned k_smem = q_smem + 2 * Q_BYTES;                   // [2 stages]
   const unsigned v_smem = k_smem + 2 * KV_BYTES;                  // [2 stages]
-  const unsigned p_smem = v_smem + 2 * KV_BYTES;                  // [2 heads]
   // barriers: 0 q_full; 1,2 k_full; 3,4 k_empty; 5,6 v_full; 7,8 v_empty;
-  // per head t (base 9 + 7 t): +0,+1 s_full; +2,+3 s_empty; +4 p_full; +5 pv_done
+  // per head t (base 9 + 7 t): +0,+1 s_full; +4 p_full; +5 pv_done
   const unsigned q_full = tc_smem(&bars[0]), k_full0 = tc_smem(&bars[1]), k_empty0 = tc_smem(&bars[3]),
                  v_full0 = tc_smem(&bars[5]), v_empty0 = tc_smem(&bars[7]);
   auto s_full = [&](int t, int s) { return tc_smem(&bars[9 + 7 * t + s]); };
-  auto s_empty = [&](int t, int s) { return tc_smem(&bars[9 + 7 * t + 2 + s]); };
   auto p_full = [&](int t) { return tc_smem(&bars[9 + 7 * t + 4]); };
   auto pv_done = [&](int t) { return tc_smem(&bars[9 + 7 * t + 5]); };
   auto turn = [&](int t) { return tc_smem(&bars[22 + t]); };     // head t may run its exponentials
@@ -91,7 +107,7 @@ attn_prefill_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
       mbar_init(v_full0 + 8 * s, 1); mbar_init(v_empty0 + 8 * s, 2);
     }
     for (int t = 0; t < 2; ++t) {
-      for (int s = 0; s < 2; ++s) { mbar_init(s_full(t, s), 1); mbar_init(s_empty(t, s), 4); }
+      for (int s = 0; s < 2; ++s) mbar_init(s_full(t, s), 1);
       mbar_init(p_full(t), 4);
       mbar_init(pv_done(t), 1);
       mbar_init(turn(t), 4);
@@ -182,11 +198,10 @@ attn_prefill_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
     const unsigned hi_k = 64u | (1u << 14) | (2u << 29);                 // SBO 1024 bytes, version 1, 128-byte swizzle
     const unsigned lbo_k = 1u << 16, lbo_v = (unsigned)(AT2_KHALF >> 4) << 16;
     auto lo_word = [](unsigned addr, unsigned lbo) { return ((addr & 0x3FFFFu) >> 4) | lbo; };
-    unsigned q_lo[2], p_lo[2], k_lo[2], v_lo[2];
+    unsigned q_lo[2], k_lo[2], v_lo[2];
 #pragma unroll
     for (int i = 0; i < 2; ++i) {
       q_lo[i] = lo_word(q_smem + i * Q_BYTES, lbo_k);
-      p_lo[i] = lo_word(p_smem + i * AT2_P_BYTES, lbo_k);
       k_lo[i] = lo_word(k_smem + i * KV_BYTES, lbo_k);
       v_lo[i] = lo_word(v_smem + i * KV_BYTES, lbo_v);
     }
@@ -195,7 +210,8 @@ attn_prefill_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
       const int s = j & 1;
       const unsigned phase = (j >> 1) & 1;
       if (!mbar_wait(k_full0 + 8 * s, phase)) return false;
-      if (!mbar_wait(s_empty(t, s), phase ^ 1)) return false;
+      // score buffer s is free: the product that read P from it was issued before this, and the
+      // softmax warps had left it when they handed that P over
       tc_fence_after();
 #pragma unroll
       for (int k = 0; k < D / 16; ++k) {
@@ -217,13 +233,13 @@ attn_prefill_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
       tc_fence_after();
 #pragma unroll
       for (int k = 0; k < AT2_BK / 16; ++k) {
-        // A = P (K-major: keys contiguous), 16 keys = 32 bytes within the row of 64 keys.
+        // A = P from tensor memory: 16 keys = 8 columns of the score buffer of this step.
         // B = V (MN-major: d contiguous): 16 keys further = 16 rows of 128 bytes; the second
         // half of d is one half tile (LBO) further; groups of 8 keys are 1024 bytes apart (SBO)
-        constexpr_mma(tmem_base + t * 256 + 128, p_lo[t] + ((k * 32) >> 4), hi_k,
-                      v_lo[s] + ((k * 16 * 128) >> 4), hi_k, idesc_pv, j > 0 || k > 0);
+        constexpr_mma_ta(tmem_base + t * 256 + 128, tmem_base + t * 256 + s * 64 + k * 8,
+                         v_lo[s] + ((k * 16 * 128) >> 4), hi_k, idesc_pv, j > 0 || k > 0);
       }
-      tc_commit(pv_done(t));               // O of this head holds the step; its P may be overwritten
+      tc_commit(pv_done(t));               // O of this head holds the step
       tc_commit(v_empty0 + 8 * s);         // this head is done with the value tile
     }
     if (!ok) { atomicExch(args.status, AT2_ERR_MMA); atomicExch(&abort_s, 1); }
@@ -236,7 +252,6 @@ attn_prefill_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
     const bool row_ok = r < nrows;
     const unsigned lane_addr = tmem_base + t * 256 + ((unsigned)(quarter * 32) << 16);
     const unsigned tmem_o = lane_addr + 128;
-    const unsigned my_p = p_smem + t * AT2_P_BYTES + (unsigned)r * 128;
     const float sc = a.scale * AT2_LOG2E;
     float m_ref = -INFINITY, l = 0.f;
     const int stale_hi = (hi + ps - 1) / ps * ps;        // end of the last page that is fetched
@@ -259,10 +274,6 @@ attn_prefill_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
 #pragma unroll
         for (int i = 0; i < 32; ++i) sv[c + i] = __uint_as_float(v[i]) * sc;
       }
-      // the scores are in registers: the buffer can take the scores after next
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(s_empty(t, s));
       if (!interior) {
 #pragma unroll
         for (int i = 0; i < 64; ++i) {
@@ -285,7 +296,11 @@ attn_prefill_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
         l *= alpha;
       }
       if (j > 0) {
-        // the product of the step before must be complete: it read P, and it wrote O
+        // The product of the step before must be complete before O is rescaled.  The wait is
+        // made at every step, although only a rescale needs it: a thread may only ever be one
+        // phase behind this barrier (its parity tells two neighbouring phases apart, no more),
+        // and by now that product has long been issued (the other head's exponentials ran in
+        // between), so the wait costs a test.
         ok = mbar_wait(pv_done(t), (j - 1) & 1) && !*(volatile int*)&abort_s;
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
@@ -327,25 +342,21 @@ attn_prefill_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
       ok = mbar_wait(turn(t), t == 0 ? ((j & 1) ^ 1) : (j & 1)) && !*(volatile int*)&abort_s;
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
-      // p = 2^(s - m_ref), row sum, P to shared memory (bf16, swizzled K-major)
+      // p = 2^(s - m_ref), row sum, P into the first 32 columns of this step's score buffer
+      // (column c = keys 2c, 2c + 1 as a pair of bfloat16)
       const float mr = m_ref == -INFINITY ? 0.f : m_ref;
       float sum = 0.f;
+      unsigned pk[32];
 #pragma unroll
-      for (int c = 0; c < 64; c += 8) {
-        unsigned pk[4];
-#pragma unroll
-        for (int i = 0; i < 8; i += 2) {
-          const float p0 = fast_exp2(sv[c + i] - mr), p1 = fast_exp2(sv[c + i + 1] - mr);   // 2^-inf = 0
-          sum += p0 + p1;
-          __nv_bfloat162 pr = __floats2bfloat162_rn(p0, p1);
-          pk[i >> 1] = *reinterpret_cast<unsigned*>(&pr);
-        }
-        const unsigned addr = my_p + (unsigned)(((c >> 3) ^ (r & 7)) << 4);
-        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(pk[0]), "r"(pk[1]), "r"(pk[2]),
-                     "r"(pk[3]) : "memory");
+      for (int i = 0; i < 64; i += 2) {
+        const float p0 = fast_exp2(sv[i] - mr), p1 = fast_exp2(sv[i + 1] - mr);             // 2^-inf = 0
+        sum += p0 + p1;
+        __nv_bfloat162 pr = __floats2bfloat162_rn(p0, p1);
+        pk[i >> 1] = *reinterpret_cast<unsigned*>(&pr);
       }
       l += sum;
-      fence_async_smem();                  // P is read by the tensor core (async proxy)
+      tc_store32(tmem_s, pk);
+      tc_wait_store();
       tc_fence_before();
       __syncwarp();
       if (lane == 0) { mbar_arrive(p_full(t)); mbar_arrive(turn(1 - t)); }
@@ -435,7 +446,7 @@ int attn_prefill_tc2(const AttnArgs& a, int num_tiles, int T, int num_pages, int
   args.num_pages = num_pages;
   args.status = status;
   const size_t halves = (size_t)(a.d / 64);
-  const size_t smem = 2 * halves * AT2_QHALF + 4 * halves * AT2_KHALF + 2 * AT2_P_BYTES + 1024;   // 2 Q, 2 K, 2 V, 2 P
+  const size_t smem = 2 * halves * AT2_QHALF + 4 * halves * AT2_KHALF + 1024;   // 2 Q, 2 K, 2 V
   cudaError_t e;
   if (a.d == 128) {
     static bool set = false;
