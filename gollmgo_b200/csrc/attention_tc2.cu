@@ -282,9 +282,15 @@ attn_prefill_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
           if (!keep) sv[i] = -INFINITY;
         }
       }
-      float mx = -INFINITY;
+      // (four chains side by side: one chain of 64 dependent operations is 64 latencies long,
+      // and with two softmax warps per scheduler there is little else to issue meanwhile)
+      float mxs[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-      for (int i = 0; i < 64; ++i) mx = fmaxf(mx, sv[i]);
+      for (int i = 0; i < 64; i += 4) {
+#pragma unroll
+        for (int u = 0; u < 4; ++u) mxs[u] = fmaxf(mxs[u], sv[i + u]);
+      }
+      const float mx = fmaxf(fmaxf(mxs[0], mxs[1]), fmaxf(mxs[2], mxs[3]));
       // move the reference maximum only when some row of the warp has outgrown it by 2^8
       const bool grow = mx > m_ref + 8.f;
       const bool rescale = __any_sync(0xffffffffu, grow);
@@ -345,16 +351,16 @@ attn_prefill_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
       // p = 2^(s - m_ref), row sum, P into the first 32 columns of this step's score buffer
       // (column c = keys 2c, 2c + 1 as a pair of bfloat16)
       const float mr = m_ref == -INFINITY ? 0.f : m_ref;
-      float sum = 0.f;
+      float sums[4] = {0.f, 0.f, 0.f, 0.f};
       unsigned pk[32];
 #pragma unroll
       for (int i = 0; i < 64; i += 2) {
         const float p0 = fast_exp2(sv[i] - mr), p1 = fast_exp2(sv[i + 1] - mr);             // 2^-inf = 0
-        sum += p0 + p1;
+        sums[(i >> 1) & 3] += p0 + p1;
         __nv_bfloat162 pr = __floats2bfloat162_rn(p0, p1);
         pk[i >> 1] = *reinterpret_cast<unsigned*>(&pr);
       }
-      l += sum;
+      l += (sums[0] + sums[1]) + (sums[2] + sums[3]);
       tc_store32(tmem_s, pk);
       tc_wait_store();
       tc_fence_before();
