@@ -56,7 +56,7 @@ class RequestCache:
 @dataclass(frozen=True)
 class Appended:
     start: int                         # tokens cached before
-    slots: List[List[int]]             # per group: flat slot (page * page_size + offset) per new token
+    slots: List[np.ndarray]            # per group: flat slot (page * page_size + offset) per new token, int32
 
 
 class CacheManager:
@@ -228,16 +228,18 @@ class CacheManager:
                 self._give_back(gi, rc.pages[gi][idx])
                 rc.pages[gi][idx] = -1
             want = -(-(start + n_tokens) // ps)
-            rc.pages[gi].extend(g.pool.allocate(want - len(rc.pages[gi])))
-            table = rc.pages[gi]
-            slots.append([table[t // ps] * ps + t % ps for t in range(start, start + n_tokens)])
-            self._mirror(gi, rc)
+            have = len(rc.pages[gi])
+            rc.pages[gi].extend(g.pool.allocate(want - have))
+            self._mirror(gi, rc, since=have if not self.any_window else 0)
+            pos = np.arange(start, start + n_tokens, dtype=np.int32)
+            slots.append(self.tab[gi][rc.state_slot, pos // ps] * ps + pos % ps)
         rc.num_tokens = start + n_tokens
         self.ntok[rc.state_slot] = rc.num_tokens
         return Appended(start, slots)
 
-    def _mirror(self, gi: int, rc: RequestCache) -> None:
-        """Bring the flat table of group gi up to date with the request's pages."""
+    def _mirror(self, gi: int, rc: RequestCache, since: int = 0) -> None:
+        """Bring the flat table of group gi up to date with the request's pages (``since``: the
+        entries before it are known to be unchanged)."""
         pages = rc.pages[gi]
         t = self.tab[gi]
         if len(pages) > t.shape[1]:
@@ -245,7 +247,8 @@ class CacheManager:
             wider[:, :t.shape[1]] = t
             self.tab[gi] = t = wider
         row = t[rc.state_slot]
-        row[:len(pages)] = pages
+        if since < len(pages):
+            row[since:len(pages)] = pages[since:]
         row[len(pages):] = -1
 
     def append_one(self, req_id) -> int:

@@ -32,6 +32,9 @@ class StepEntry:
     # the entry's single token is not known on the host yet: it is row `token_src` of the
     # tokens sampled on the device in the step before (tokens[0] is then ignored)
     token_src: int = -1
+    # the caller has checked that every token id is inside the vocabulary (the engine does when a
+    # request is added): the step function does not go over them again
+    checked: bool = False
 
 
 class TileList:
@@ -302,8 +305,7 @@ class BatchBuilder:
                                                                   pin_memory=self.device.type == "cuda")
         h = host.numpy()
         h[:hlay.size] = 0
-        flat_tokens = np.fromiter((t for e in entries for t in e.tokens), dtype=np.int64, count=T)
-        h[lay.token_ids:lay.token_ids + T] = flat_tokens
+        h[lay.token_ids:lay.token_ids + T] = np.concatenate([np.asarray(e.tokens, dtype=np.int64) for e in entries])
         h[lay.token_src:lay.token_src + Tp] = -1
         if any(e.token_src >= 0 for e in entries):
             base = 0
@@ -319,7 +321,7 @@ class BatchBuilder:
         for g in range(G):
             sm = h[lay.slot_mapping[g]:lay.slot_mapping[g] + Tp]
             sm[:] = -1
-            sm[:T] = np.fromiter((s for a in appended for s in a.slots[g]), dtype=np.int32, count=T)
+            sm[:T] = np.concatenate([a.slots[g] for a in appended])
         cu = np.zeros(Bp + 1, dtype=np.int32)
         cu[1:B + 1] = np.cumsum(q_lens)
         cu[B + 1:] = T + np.arange(1, Bp - B + 1)

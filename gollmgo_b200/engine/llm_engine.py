@@ -116,9 +116,9 @@ class Engine:
         if params.seed is None and not params.greedy:
             params = SamplingParams(**{**params.__dict__, "seed": self._seed_rng.getrandbits(63)})
         V = self.spec.vocab_size
-        for t in token_ids:
-            if not (0 <= int(t) < V):
-                raise ValueError(f"token id {t} is outside [0, {V})")
+        if len(token_ids) and not (0 <= min(token_ids) and max(token_ids) < V):
+            bad = next(t for t in token_ids if not (0 <= int(t) < V))
+            raise ValueError(f"token id {bad} is outside [0, {V})")
         seq_id = self._next_id
         self._next_id += 1
         rid = request_id if request_id is not None else f"req-{seq_id}"
@@ -157,7 +157,7 @@ class Engine:
                     toks, src = [0], seq.pending_row
                 if PENDING in toks:
                     raise RuntimeError("an unknown token in the middle of a portion")
-                entries.append(StepEntry(seq.id, toks, [s.num_tokens - 1] if s.samples else [], src))
+                entries.append(StepEntry(seq.id, toks, [s.num_tokens - 1] if s.samples else [], src, checked=True))
                 if s.samples:
                     samplers.append(seq)
             try:
@@ -241,7 +241,7 @@ class Engine:
             return []
         handle, samplers = inflight[0], inflight[1]
         tokens = self.sampler.wait(handle)
-        self.runner.check_kernels()
+        self.runner.check_kernels(wait=False)      # this step's status has arrived with its tokens; a step launched since is not waited for
         now = time.perf_counter()
         eos = set(self.spec.eos_token_ids)
         results = []

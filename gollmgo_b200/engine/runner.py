@@ -72,6 +72,12 @@ class ModelRunner:
         # inputs from here before the host has read them
         self.last_tokens = torch.zeros(max(engine_config.max_batch_size, 1), dtype=torch.int32,
                                        device=self.device)
+        # the status word of the tcgen05 kernels, copied to the host behind every step that ran one
+        # (two steps can be in flight), so that reading it never waits for a step launched since
+        self._status_host = [torch.zeros(1, dtype=torch.int32, pin_memory=True) for _ in range(2)]
+        self._status_event = [torch.cuda.Event(), torch.cuda.Event()]
+        self._status_pending = [False, False]
+        self._status_turn = 0
         self._graphs: Dict[int, "_CapturedStep"] = {}
         self.steps = 0
         self.launch_count = 0
@@ -114,9 +120,10 @@ class ModelRunner:
         total = 0
         for e in entries:
             total += len(e.tokens)
-            for t in e.tokens:
-                if not (0 <= int(t) < V):
-                    raise ValueError(f"request {e.request_id!r}: token id {t} is outside [0, {V})")
+            if not e.checked:
+                for t in e.tokens:
+                    if not (0 <= int(t) < V):
+                        raise ValueError(f"request {e.request_id!r}: token id {t} is outside [0, {V})")
             if e.request_id in self.cache.requests and \
                     self.cache.num_tokens(e.request_id) + len(e.tokens) > self.max_model_len:
                 raise ValueError(f"request {e.request_id!r} would exceed max_model_len "
@@ -138,7 +145,10 @@ class ModelRunner:
                     self.cache.admit(e.request_id)
                     admitted.append(e.request_id)
                 starts[e.request_id] = self.cache.num_tokens(e.request_id)
-            return self._run(entries)
+            logits = self._run(entries)
+            if ops.tc_launched:
+                self._snapshot_status()
+            return logits
         except Exception:
             # a step that fails leaves nothing behind: no token of it counts as cached (what a
             # kernel may have written lies beyond every request's count and is overwritten by
@@ -172,12 +182,32 @@ class ModelRunner:
         self.steps += 1
         return logits
 
-    def check_kernels(self) -> None:
-        """Raise if a kernel reported that it gave up on a bounded wait.  Call where the
-        host has synchronised anyway (it reads one word from the device)."""
-        if ops.tc_launched:
-            ops.tc_launched = False
-            ops.check_tc_status(self.device)
+    def _snapshot_status(self) -> None:
+        ops.tc_launched = False
+        slot = self._status_turn
+        self._status_turn ^= 1
+        if self._status_pending[slot]:                  # a snapshot nobody asked about: it still counts
+            self._read_status(slot)
+        self._status_host[slot].copy_(ops.tc_status(self.device), non_blocking=True)
+        self._status_event[slot].record()
+        self._status_pending[slot] = True
+
+    def _read_status(self, slot: int) -> None:
+        self._status_event[slot].synchronize()
+        self._status_pending[slot] = False
+        code = int(self._status_host[slot][0])
+        if code:
+            ops.tc_status(self.device).zero_()
+            raise ops.KernelError(f"a tcgen05 kernel gave up waiting on a barrier (code {code}); the step's output is not valid")
+
+    def check_kernels(self, wait: bool = True) -> None:
+        """Raise if a kernel of a step reported that it gave up on a bounded wait.  The status
+        word travels to the host behind each step (a copy in stream order), so asking about a
+        step whose results the host has already read costs nothing.  ``wait=False``: only ask
+        about steps whose copy has arrived (a step launched since is left for the next call)."""
+        for slot in (self._status_turn, self._status_turn ^ 1):          # the older one first
+            if self._status_pending[slot] and (wait or self._status_event[slot].query()):
+                self._read_status(slot)
 
     # ------------------------------------------------------------------ captured decode steps
     def _graph_stride(self) -> int:

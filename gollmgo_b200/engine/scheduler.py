@@ -119,6 +119,7 @@ class Scheduler:
         # sliding group gives back first is asked of the cache manager (pages_delta), in the order
         # in which the step will append, so a plan that is accepted here is one the cache accepts.
         free: List[int] = self.cache.free_pages_per_group()
+        page, sliding = self.cache.page_size, self.cache.any_window
         planned: List[Scheduled] = []
         deltas: Dict[int, list] = {}                     # seq id -> its (taken, given back) per group
         planned_new: List[Sequence] = []                # admitted in this step (each takes a state slot)
@@ -133,6 +134,8 @@ class Scheduler:
         def fits_or_preempt(seq: Sequence, n: int) -> bool:
             """Make room for n tokens of seq by preempting later-admitted sequences
             (never an earlier one).  False if seq itself had to go."""
+            if n == 1 and not sliding and seq.num_computed % page:
+                return True                              # lands in a page the sequence holds: nothing to ask or book
             delta = self.cache.pages_delta(seq.id, n)
             while not fits(delta):
                 victim_id = self.admit_order[-1]
@@ -140,7 +143,9 @@ class Scheduler:
                 # a victim already planned in this step loses its plan
                 for i, s in enumerate(planned):
                     if s.seq is victim:
-                        book(deltas.pop(victim.id), -1)
+                        booked = deltas.pop(victim.id, None)
+                        if booked is not None:
+                            book(booked, -1)
                         planned.pop(i)
                         break
                 held = self.cache.pages_held(victim.id)

@@ -70,11 +70,11 @@ def test_slots_follow_the_block_table():
     cm = make(page=4)
     cm.admit("a")
     a1 = cm.append("a", 6)
-    assert a1.start == 0 and a1.slots[0] == [0, 1, 2, 3, 4, 5]
+    assert a1.start == 0 and list(a1.slots[0]) == [0, 1, 2, 3, 4, 5]
     cm.admit("b")
-    assert cm.append("b", 1).slots[0] == [8]
+    assert list(cm.append("b", 1).slots[0]) == [8]
     a2 = cm.append("a", 3)                       # fills page 1, opens page 3
-    assert a2.start == 6 and a2.slots[0] == [6, 7, 12]
+    assert a2.start == 6 and list(a2.slots[0]) == [6, 7, 12]
     assert cm.block_table("a", 0) == [0, 1, 3] and cm.num_tokens("a") == 9
     cm.audit()
 

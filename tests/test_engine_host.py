@@ -75,7 +75,7 @@ class StubRunner:
                 out.append(self.next_token(h))
         return out
 
-    def check_kernels(self):
+    def check_kernels(self, wait=True):
         self.checks += 1
         if self.checks in self.fail_check_at:
             raise RuntimeError("a kernel gave up on a bounded wait")
