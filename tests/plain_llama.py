@@ -8,8 +8,12 @@ safetensors names and the raw ``config.json`` dict.
 
 gollmgo's own model code cannot be built on a CPU (it is CUDA + cuBLAS behind a
 Go host program, and the only CPU code it has are three formula helpers in
-``kernels/gollmgo_ops_test.cu:38-87``), so this file rests on the formulas, not
-on a run of the reference.
+``kernels/gollmgo_ops_test.cu:38-87``), so this file is written from the formulas.
+It is then compared with a run of the reference's unmodified CUDA engine on a
+GPU: ``tests/golden/make_reference_anchor.py`` made ``tests/golden/reference_anchor.npz``
+(a tiny random model through gollmgo_model_forward, and through prefill + paged
+decode), and ``tests/test_reference_anchor.py`` checks this file against it, with
+or without a GPU.
 
 Where the reference ignores a config.json key (rope_theta, rms_norm_eps,
 rope_scaling, tie_word_embeddings, head_dim) the key is honoured here, because
