@@ -386,11 +386,28 @@ def mid_m_ok(x: torch.Tensor, w: torch.Tensor) -> bool:
             and x.stride(0) % 8 == 0 and w.is_contiguous())
 
 
+_MID_M_PLANS = {}
+
+
+def mid_m_plan(M: int, N: int, K: int, gated: bool, device=None):
+    """How gemm_mid_m cuts out[M, N] = x[M, K] @ w^T on the current device: (S, boxes, box_rows,
+    slabs, ctas_per_sm, ctas_at_once).  It launches S * slabs CTAs."""
+    key = (torch.device(device).index if device is not None else torch.cuda.current_device(), M <= 32, N, K, gated)
+    plan = _MID_M_PLANS.get(key)
+    if plan is None:
+        buf = (ctypes.c_int * 6)()
+        with torch.cuda.device(key[0]):
+            _check(lib().gg_gemm_mid_m_plan(M, N, K, 2 if gated else 0, buf))
+        plan = _MID_M_PLANS[key] = tuple(buf)
+    return plan
+
+
 def gemm_mid_m(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, gated: bool = False) -> None:
     """out[M, N] = x[M, K] @ w[N, K]^T for M <= 64 on tcgen05 with the operands swapped (rows
-    of w on the M side of the instruction, tokens on its N side) and K split over a
-    thread-block cluster; out bfloat16 or float32.  ``gated``: w is [2N, K] (gate rows, then
-    up rows) and out = silu(x Wg^T) * (x Wu^T) in bfloat16."""
+    of w on the M side of the instruction, tokens on its N side), the rows of w cut into slabs
+    so that the CTAs fill the machine evenly, and K split over a thread-block cluster where the
+    slabs are few; out bfloat16 or float32.  ``gated``: w is [2N, K] (gate rows, then up rows)
+    and out = silu(x Wg^T) * (x Wu^T) in bfloat16."""
     M, K = x.shape
     N = out.shape[1]
     if w.shape != ((2 * N, K) if gated else (N, K)) or out.shape[0] != M or not out.is_contiguous():

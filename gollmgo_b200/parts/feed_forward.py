@@ -57,7 +57,7 @@ class GatedMLP:
                              hidden=x.hidden, eps=x.eps)
         elif ops.small_m_ok(x, self.w_gate_up):
             ops.gemm_small_m(x, self.w_gate_up, a, gated=True)       # product and activation in one
-        elif use_mid_m(x, self.w_gate_up):
+        elif use_mid_m(x, self.w_gate_up, gated=True):
             ops.gemm_mid_m(x, self.w_gate_up, a, gated=True)          # the same for a few dozen tokens
         elif use_tc(x, self.w_gate_up, self.inter, True):
             ops.gemm_tc(x, self.w_gate_up, a, gated=True, pair=True)  # the same, on tcgen05 (CTA pairs)

@@ -39,36 +39,28 @@ TC_MIN_TOKENS = 1024     # below this the tcgen05 kernel has too few tiles to fi
 
 
 # Steps of 17 to MID_M_TOKENS tokens use this package's swapped-operand tcgen05 kernel
-# (csrc/gemm_mid_m.cu), which takes up to 64.  Measured on whole decode steps of the
-# Llama-3.1-8B shape: 2.7 % faster than the vendor library at 24 tokens, level at 32, 3 %
-# slower at 64 (its 224 row slabs of the gated product fill 296 places unevenly).
-MID_M_TOKENS = int(os.environ.get("GOLLMGO_B200_GEMM_MID_TOKENS", "32"))
-# Up to MID_M_SPLIT_TOKENS tokens it still takes the products with so few rows of W that it
-# splits K eight ways over a cluster (the o and down products of that shape: 12.6 and 25.9 us
-# against the library's 15.5 and 27.0 at 64 tokens).
-MID_M_SPLIT_TOKENS = int(os.environ.get("GOLLMGO_B200_GEMM_MID_SPLIT_TOKENS", "64"))
-_NUM_SMS = {}
+# (csrc/gemm_mid_m.cu) for every product that it runs as one round of CTAs; a product of
+# several rounds (an LM head) stays with the vendor library (201 against 182 us at 64 tokens).
+# The threshold is from whole decode steps of the Llama-3.1-8B shape (ms per step, own kernel
+# for all four products of a layer / library for all): 32 sequences 4.97 / 5.20, 40: 5.45 /
+# 5.60, 48: 5.54 / 5.56, 64: 6.86 / 6.75.  Timed alone, back to back, the own kernel is ahead
+# at 64 tokens as well (qkv 14.6 us against 15.5, o 11.8 / 15.4, gate_up with the activation
+# 42.6 / 45.0 + 2.5, down 25.1 / 27.0): a launch overlaps the end of the same kernel before it
+# better than the end of the attention, so the step decides, not the loop.
+MID_M_TOKENS = int(os.environ.get("GOLLMGO_B200_GEMM_MID_TOKENS", "48"))
+# The products whose K is split eight ways (o and down of that shape) may go further.
+MID_M_SPLIT_TOKENS = int(os.environ.get("GOLLMGO_B200_GEMM_MID_SPLIT_TOKENS", "48"))
 
 
-def _num_sms(device) -> int:
-    n = _NUM_SMS.get(device)
-    if n is None:
-        n = _NUM_SMS[device] = torch.cuda.get_device_properties(device).multi_processor_count
-    return n
-
-
-def use_mid_m(x: torch.Tensor, w: torch.Tensor) -> bool:
-    if GEMM_POLICY == "lib":
+def use_mid_m(x: torch.Tensor, w: torch.Tensor, gated: bool = False) -> bool:
+    if GEMM_POLICY == "lib" or not x.is_cuda or not ops.mid_m_ok(x, w):
         return False
     T = x.shape[0]
-    if not x.is_cuda:
+    N = w.shape[0] // 2 if gated else w.shape[0]
+    S, _, _, slabs, _, at_once = ops.mid_m_plan(T, N, x.shape[1], gated, x.device)
+    if T > MID_M_TOKENS and not (T <= MID_M_SPLIT_TOKENS and S == 8):
         return False
-    slabs, places = -(-w.shape[0] // 128), 2 * _num_sms(x.device)
-    if slabs > places:          # several rounds of CTAs (an LM head): the library is ahead, 167 vs 188 us at 32 tokens
-        return False
-    if T > MID_M_TOKENS and not (T <= MID_M_SPLIT_TOKENS and slabs * 8 <= places):
-        return False
-    return ops.mid_m_ok(x, w)
+    return S * slabs <= at_once
 
 
 def use_tc(x: torch.Tensor, w: torch.Tensor, out_cols: int, gated: bool) -> bool:

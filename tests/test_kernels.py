@@ -568,8 +568,12 @@ def test_gemm_small_m_with_norms_folded_in(ops, cuda_device, M, H, I):
 
 
 @pytest.mark.parametrize("M", [1, 17, 32, 33, 50, 64])
-@pytest.mark.parametrize("N,K", [(48, 64), (100, 120), (4096, 4096), (1000, 14336 + 8), (6144, 4096), (130, 72)])
+@pytest.mark.parametrize("N,K", [(48, 64), (100, 120), (4096, 4096), (1000, 14336 + 8), (6144, 4096), (130, 72),
+                                 (28672, 512), (37991, 200), (9475, 64), (20000, 1024)])
 def test_gemm_mid_m(ops, cuda_device, M, N, K):
+    """Few rows of w (slabs of 128 rows, K split over a cluster) and many (one CTA per SM, slabs
+    of whatever height fills the machine, one or two boxes; several rounds; an odd N, where
+    outputs are stored one by one)."""
     g = torch.Generator(device="cuda").manual_seed(M * 7 + N)
     x = torch.randn(M, K, device="cuda", generator=g).to(torch.bfloat16)
     w = (torch.randn(N, K, device="cuda", generator=g) / math.sqrt(K)).to(torch.bfloat16)
@@ -589,7 +593,7 @@ def test_gemm_mid_m(ops, cuda_device, M, N, K):
 
 
 @pytest.mark.parametrize("M", [17, 40, 64])
-@pytest.mark.parametrize("I,K", [(44, 64), (352, 128), (14336, 4096), (200, 72)])
+@pytest.mark.parametrize("I,K", [(44, 64), (352, 128), (14336, 4096), (200, 72), (19001, 136), (8192, 2048)])
 def test_gemm_mid_m_gated(ops, cuda_device, M, I, K):
     g = torch.Generator(device="cuda").manual_seed(M + I)
     x = torch.randn(M, K, device="cuda", generator=g).to(torch.bfloat16)
