@@ -143,6 +143,9 @@ def cmd_bench(argv) -> int:
     ap.add_argument("--output-len", type=int, default=128)
     ap.add_argument("--warmup-requests", type=int, default=0)
     ap.add_argument("--repetitions", type=int, default=1)
+    ap.add_argument("--concurrency", type=int, default=0,
+                    help="closed loop with this many requests in the engine at a time, the next handed in "
+                         "when one finishes (the reference's serving benchmark: 4); 0: all prompts at once")
     ap.add_argument("--prompt-len-range", default="", metavar="LO,HI",
                     help="prompt lengths drawn uniformly from [LO, HI] (from --workload-seed) instead of --prompt-len")
     ap.add_argument("--output-len-range", default="", metavar="LO,HI",
@@ -185,7 +188,7 @@ def cmd_bench(argv) -> int:
         return out
 
     def run(items):
-        return eng.generate([p for p, _ in items], [q for _, q in items])
+        return eng.generate([p for p, _ in items], [q for _, q in items], concurrency=args.concurrency)
     if args.warmup_requests:
         run(workload(args.warmup_requests, args.workload_seed + 7))
     result = None
@@ -215,6 +218,7 @@ def cmd_bench(argv) -> int:
             "workload_seed": args.workload_seed,
             "prompt_tokens": sum(len(p) for p, _ in items), "output_tokens": toks,
             "warmup_requests": args.warmup_requests, "repetitions": args.repetitions,
+            "concurrency": args.concurrency,
             "prompt_generation": "synthetic token ids", "token_count_mode": "exact",
             "elapsed_seconds": round(elapsed, 4), "tokens_per_second": round(toks / elapsed, 2),
             "total_tokens_per_second": round((toks + sum(len(p) for p, _ in items)) / elapsed, 2),

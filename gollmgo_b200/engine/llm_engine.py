@@ -286,23 +286,30 @@ class Engine:
         return replay(self.runner, lines, out_dir, log=io.StringIO())
 
     # ------------------------------------------------------------------ whole requests
-    def generate(self, prompts: Seq[Seq[int]], params=None, **param_options) -> List[RequestOutput]:
+    def generate(self, prompts: Seq[Seq[int]], params=None, concurrency: int = 0,
+                 **param_options) -> List[RequestOutput]:
         """Generate for every prompt (token ids); returns outputs in the order given.
-        ``params``: one SamplingParams for all, or one per prompt."""
+        ``params``: one SamplingParams for all, or one per prompt.  ``concurrency`` > 0: a closed
+        loop, as the reference's serving benchmark drives its server (bench/PARITY_SUMMARY.md:
+        concurrency 4): at most that many requests are in the engine at a time, and the next
+        prompt is handed in when one of them has finished; 0: all at once."""
         if params is None:
             params = SamplingParams(**param_options)
         plist = list(params) if isinstance(params, (list, tuple)) else [params] * len(prompts)
         if len(plist) != len(prompts):
             raise ValueError("one SamplingParams per prompt, or one for all")
+        if concurrency < 0:
+            raise ValueError("concurrency must be 0 (all at once) or a positive number of requests")
         rids = []
         pending = list(zip(prompts, plist))
-        i = 0
+        i, live = 0, 0
         while i < len(pending) or self.has_unfinished():
-            while i < len(pending) and (self.ecfg.max_queue_depth <= 0
-                                        or len(self.scheduler.waiting) < self.ecfg.max_queue_depth):
+            while i < len(pending) and (concurrency <= 0 or live < concurrency) and (
+                    self.ecfg.max_queue_depth <= 0 or len(self.scheduler.waiting) < self.ecfg.max_queue_depth):
                 rids.append(self.enqueue(pending[i][0], pending[i][1]))
                 i += 1
-            self.step()
+                live += 1
+            live -= sum(1 for r in self.step() if r.finished)
         return [self.output_of(r) for r in rids]
 
     def output_of(self, request_id: str) -> RequestOutput:

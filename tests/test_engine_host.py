@@ -243,3 +243,31 @@ def test_end_token_that_arrives_after_its_sequence_was_preempted():
         runner.cache.audit()
         assert runner.cache.free_pages() == 12 and not runner.cache.requests
     assert hit >= 1, "the sweep never preempted the sequence while its end token was on its way"
+
+
+def test_generate_as_a_closed_loop_keeps_no_more_requests_in_the_engine_than_asked():
+    """concurrency = 3 (the reference's serving benchmark drives its server this way): never more
+    than three requests are admitted or waiting, every prompt is served, in the order given,
+    with the tokens it gets alone; a failed request makes room like a finished one."""
+    eng, runner = make_engine(num_pages=64)
+    runner.fail_step_at = {9}
+    seen = []
+    step = eng.step
+
+    def counted():
+        seen.append(len(eng.scheduler.running) + len(eng.scheduler.waiting))
+        return step()
+    eng.step = counted
+    prompts = [[20 + i, 3, 5 + i % 4] * (1 + i % 3) for i in range(11)]
+    outs = eng.generate(prompts, SamplingParams(max_tokens=6), concurrency=3)
+    assert max(seen) == 3 and len(outs) == len(prompts)
+    failed = [o for o in outs if o.finish_reason == "error"]
+    assert 1 <= len(failed) <= 3
+    for p, o in zip(prompts, outs):
+        assert o.prompt_token_ids == p
+        if o.finish_reason != "error":
+            assert o.token_ids == plain_generate(p, 6)
+    runner.cache.audit()
+    assert not runner.cache.requests
+    with pytest.raises(ValueError, match="concurrency"):
+        eng.generate(prompts[:1], SamplingParams(max_tokens=2), concurrency=-1)
