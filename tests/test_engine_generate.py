@@ -75,6 +75,38 @@ def test_temperature_workload_of_tiny_b_is_seeded_and_batch_independent(models):
     assert eng.runner.cache.free_pages() == 64
 
 
+def test_temperature_top_k_top_p_in_bfloat16_follow_the_plain_sampler(models):
+    """The bfloat16 engine with temperature, top-k and top-p at once.  Its logits are the plain
+    ones up to rounding, so a draw that falls next to a border of the plain distribution may
+    pick the neighbour: with the engine's own tokens as history, every token must be one the
+    plain sampler could have drawn (among the plain top-k, with a slack of the rounding), most
+    must be the very token the plain sampler draws from the same uniform number, and the same
+    seeds give the same tokens again."""
+    from gollmgo_b200 import Engine, SamplingParams
+    d, cfg, page, w = models["tiny_b"]
+    reqs = list(tt.random_requests(cfg["vocab_size"], [3, 21, 37, 70], seed=4).values())
+    K, TOP_P, T, N = 12, 0.9, 0.7, 16
+    params = [SamplingParams(temperature=T, top_k=K, top_p=TOP_P, seed=500 + i, max_tokens=N, ignore_eos=True)
+              for i in range(4)]
+    eng = Engine(d, dtype="bfloat16", block_size=page, num_blocks=64, max_batch_size=4,
+                 max_token_budget=48, prefill_chunk_size=16)
+    first = [o.token_ids for o in eng.generate(reqs, params)]
+    again = [o.token_ids for o in eng.generate(reqs, params)]
+    assert first == again
+    same = total = 0
+    for prompt, p, toks in zip(reqs, params, first):
+        assert len(toks) == N
+        logits = P.forward(w, cfg, prompt + toks)
+        for n, tok in enumerate(toks):
+            row = logits[len(prompt) - 1 + n].to(torch.float32)
+            kth = torch.topk(row, K).values[-1]
+            assert float(row[tok]) >= float(kth) - 4e-2 * float(row.abs().max()), f"token {n} = {tok} is no candidate"
+            same += int(tok == P.sample(row, T, p.seed, n, K, TOP_P))
+            total += 1
+    assert same >= 0.75 * total, f"only {same} of {total} tokens are the plain sampler's"
+    assert eng.runner.cache.free_pages() == 64
+
+
 def test_eos_stops_and_is_delivered(models):
     from gollmgo_b200 import Engine, SamplingParams
     d, cfg, page, w = models["tiny_b"]
