@@ -408,11 +408,12 @@ extern "C" int gg_attn_decode_rope(const void* qkv, long long q_stride, void* kc
 // Decode attention for large batches (bfloat16, head size 64 or 128): the work is cut into
 // equal ranges of tiles instead of whole slices (attention_mma.cu).  Scratch the caller
 // provides: pieces = n_dec * nkv * ceil((nh / nkv) / 16) + gg_attn_decode_flat_ctas(d);
-// part_o float[pieces * 16 * d], part_ml float[pieces * 16 * 2], prefix int[n_dec + 1].
+// part_o float[pieces * 16 * d], part_ml float[pieces * 16 * 2], prefix int[prefix_ints] with
+// prefix_ints >= n_dec + 1 + 2 * n_dec * nkv * ceil((nh / nkv) / 16).
 extern "C" int gg_attn_decode_flat(const void* q, long long q_stride, const void* kcache, const void* vcache,
                                    int dtype, const int* block_tables, int bt_stride, const int* cu_q_lens,
                                    const int* context_lens, const int* dec_seqs, int n_dec, float* part_o,
-                                   float* part_ml, int* prefix, void* out, int nh, int nkv, int d,
+                                   float* part_ml, int* prefix, int prefix_ints, void* out, int nh, int nkv, int d,
                                    int page_size, int window, float scale, cudaStream_t stream) {
   AttnArgs a = {};
   a.q = q; a.q_stride = q_stride; a.kcache = kcache; a.vcache = vcache;
@@ -424,6 +425,8 @@ extern "C" int gg_attn_decode_flat(const void* q, long long q_stride, const void
   if (rc) return rc;
   GG_REQUIRE(n_dec >= 0, "attn_decode_flat: bad n_dec %d", n_dec);
   GG_REQUIRE(part_o && part_ml && prefix, "attn_decode_flat: no scratch given");
+  GG_REQUIRE(nkv > 0 && nh >= nkv && (long long)prefix_ints >= (long long)n_dec + 1 + 2LL * n_dec * nkv * ((nh / nkv + 15) / 16),
+             "attn_decode_flat: prefix scratch of %d ints is too small for %d tokens", prefix_ints, n_dec);
   GG_REQUIRE(attn_mma_supported(dtype, d) && q_stride % 2 == 0,
              "attn_decode_flat: only bfloat16 with head size 64 or 128 (got dtype %d, head size %d)", dtype, d);
   if (n_dec == 0) return GG_OK;

@@ -559,7 +559,8 @@ attn_decode_flat_kernel(AttnArgs a, int n_dec, int* __restrict__ prefix_out) {
     float o[D / 8][4];
     unsigned qf[D / 16][4];
     int hi = 0, lo0 = 0, nrows = 0;
-    bool fresh = true;
+    bool fresh = true, from_first_tile = false;
+    int* range_out = prefix_out + n_dec + 1;               // [pairs][2]: the CTAs with a pair's first and last piece
     const float sc = a.scale * LOG2E;
     for (int it = 0; it < ntiles; ++it) {
       if (it + 1 < ntiles) { load_tile(pp, (it + 1) % STAGES); advance(pp); }
@@ -580,6 +581,7 @@ attn_decode_flat_kernel(AttnArgs a, int n_dec, int* __restrict__ prefix_out) {
 #pragma unroll
         for (int nt = 0; nt < D / 8; ++nt) { o[nt][0] = o[nt][1] = o[nt][2] = o[nt][3] = 0.f; }
         fresh = false;
+        from_first_tile = cp.tt == 0;
       }
       cp_async_wait<STAGES - 1>();
       __syncthreads();
@@ -624,7 +626,12 @@ attn_decode_flat_kernel(AttnArgs a, int n_dec, int* __restrict__ prefix_out) {
           r1[0] = o[nt][2]; r1[1] = o[nt][3];
         }
         __syncthreads();
-        const size_t piece = (size_t)cp.r * n_dec + cp.i + blockIdx.x;
+        const size_t pair = (size_t)cp.r * n_dec + cp.i, piece = pair + blockIdx.x;
+        if (threadIdx.x == 0) {
+          // the merge kernel finds a pair's pieces from these two, without the arithmetic of the ranges
+          if (from_first_tile) range_out[2 * pair] = (int)blockIdx.x;
+          if (last_of_entry) range_out[2 * pair + 1] = (int)blockIdx.x;
+        }
         for (int e = threadIdx.x; e < nrows * D; e += MMA_THREADS) {
           const int r = e / D, col = e - r * D;
           const float M = fmaxf(fmaxf(cm[r], cm[16 + r]), fmaxf(cm[32 + r], cm[48 + r]));
@@ -655,12 +662,14 @@ attn_decode_flat_kernel(AttnArgs a, int n_dec, int* __restrict__ prefix_out) {
 }
 
 // Merge of the pieces of attn_decode_flat_kernel: grid (n_dec, kv head chunks), a block merges
-// the up to 16 heads of its chunk.  A pair's tiles are positions [u0, u1) of the sequence; CTA
-// c took [c U / G, (c + 1) U / G), so it holds a piece of the pair iff its range is not empty
-// and c U < (u0 + 1) G ... (only products are compared; one division per block).
+// the up to 16 heads of its chunk, a thread four neighbouring columns of a head.  The CTAs c
+// with a piece of the pair are range[2 pair] .. range[2 pair + 1] (written by the CTAs that
+// had the pair's first and last tile); CTA c left its piece at pair + c.  Everything a thread
+// needs to find its pieces comes from loads that do not depend on one another, and the pieces
+// of a pair are asked for four at a time before the first is used: the kernel is a few trips
+// to L2 long, and that is all it is.
 __global__ void __launch_bounds__(128) attn_merge_flat_kernel(AttnArgs a, int n_dec, int num_ctas,
                                                               const int* __restrict__ prefix) {
-  __shared__ int range_s[2];
   pdl_trigger();
   pdl_wait();
   const int idx = blockIdx.x, r = blockIdx.y;
@@ -668,47 +677,55 @@ __global__ void __launch_bounds__(128) attn_merge_flat_kernel(AttnArgs a, int n_
   if (b < 0) return;
   const int d = a.d, G = a.nh / a.nkv, gchunks = (G + 15) / 16, R = a.nkv * gchunks;
   const int kvh = r / gchunks, g0 = (r % gchunks) * 16, nrows = min(16, G - g0);
-  const int T_total = prefix[n_dec];
-  const long long U = (long long)R * T_total, Gc = num_ctas;
-  const long long u0 = (long long)r * T_total + prefix[idx], u1 = u0 + (prefix[idx + 1] - prefix[idx]);
+  const size_t q = (size_t)r * n_dec + idx;
+  const int* range = prefix + n_dec + 1;
+  const int tiles = prefix[idx + 1] - prefix[idx], T_total = prefix[n_dec];
+  const int c_first = range[2 * q], c_last = range[2 * q + 1];
   __nv_bfloat16* out = (__nv_bfloat16*)a.out + (size_t)a.cu_q_lens[b] * a.nh * d + (size_t)(kvh * G + g0) * d;
-  if (u1 <= u0 || U <= 0) {
-    for (int e = threadIdx.x; e < nrows * d; e += blockDim.x) out[e] = __float2bfloat16_rn(0.f);
+  const int quads = d >> 2;
+  if (tiles <= 0 || T_total <= 0) {
+    for (int e = threadIdx.x; e < nrows * quads; e += blockDim.x) *reinterpret_cast<uint2*>(out + 4 * e) = make_uint2(0u, 0u);
     return;
   }
-  if (threadIdx.x == 0) {
-    // the last CTA whose range starts at or before u: floor(c U / G) <= u  <=>  c U < (u + 1) G
-    auto last_start_le = [&](long long u) {
-      long long c = u * Gc / U;
-      while (c + 1 < Gc && (c + 1) * U < (u + 1) * Gc) ++c;
-      while (c > 0 && c * U >= (u + 1) * Gc) --c;
-      return (int)c;
-    };
-    range_s[0] = last_start_le(u0);
-    range_s[1] = last_start_le(u1 - 1);
-  }
-  __syncthreads();
-  const int c_first = range_s[0], c_last = range_s[1];
-  const size_t q = (size_t)r * n_dec + idx;
-  const bool gaps = U < Gc;           // fewer tiles than CTAs: CTAs in between may have had nothing to do
-  for (int e = threadIdx.x; e < nrows * d; e += blockDim.x) {
-    const int row = e / d, col = e - row * d;
-    float M = -INFINITY;
-    for (int c = c_first; c <= c_last; ++c) {
-      if (gaps && (c + 1) * U / Gc == c * U / Gc) continue;
-      M = fmaxf(M, a.part_ml[((q + c) * 16 + row) * 2]);
-    }
-    float L = 0.f, acc = 0.f;
-    for (int c = c_first; c <= c_last; ++c) {
-      if (gaps && (c + 1) * U / Gc == c * U / Gc) continue;
-      const float mc = a.part_ml[((q + c) * 16 + row) * 2];
-      if (mc != -INFINITY) {
-        const float f = fast_exp2(mc - M);
-        L += f * a.part_ml[((q + c) * 16 + row) * 2 + 1];
-        acc += f * a.part_o[((q + c) * 16 + row) * d + col];
+  // fewer tiles than CTAs: CTAs in between may have had nothing to do and left no piece
+  const long long U = (long long)R * T_total, Gc = num_ctas;
+  const bool gaps = U < Gc;
+  for (int e = threadIdx.x; e < nrows * quads; e += blockDim.x) {
+    const int row = e / quads, col = (e - row * quads) * 4;
+    float M = -INFINITY, L = 0.f;
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int c0 = c_first; c0 <= c_last; c0 += 4) {
+      float2 ml[4];
+      float4 po[4];
+      bool have[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int c = c0 + u;
+        have[u] = c <= c_last && !(gaps && (c + 1) * U / Gc == c * U / Gc);
+        if (have[u]) {
+          ml[u] = *reinterpret_cast<const float2*>(a.part_ml + ((q + c) * 16 + row) * 2);
+          po[u] = *reinterpret_cast<const float4*>(a.part_o + ((q + c) * 16 + row) * d + col);
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        if (have[u] && ml[u].x != -INFINITY) {
+          const float m_new = fmaxf(M, ml[u].x);
+          const float f_old = fast_exp2(M - m_new), f = fast_exp2(ml[u].x - m_new);       // 2^-inf = 0
+          L = L * f_old + f * ml[u].y;
+          acc.x = acc.x * f_old + f * po[u].x;
+          acc.y = acc.y * f_old + f * po[u].y;
+          acc.z = acc.z * f_old + f * po[u].z;
+          acc.w = acc.w * f_old + f * po[u].w;
+          M = m_new;
+        }
       }
     }
-    out[(size_t)row * d + col] = __float2bfloat16_rn(L > 0.f ? acc / L : 0.f);
+    const float inv = L > 0.f ? 1.f / L : 0.f;
+    uint2 pk;
+    pk.x = pack_bf16(acc.x * inv, acc.y * inv);
+    pk.y = pack_bf16(acc.z * inv, acc.w * inv);
+    *reinterpret_cast<uint2*>(out + (size_t)row * d + col) = pk;
   }
 }
 
@@ -977,7 +994,8 @@ int attn_decode_flat_ctas(int d) {
 }
 
 // Scratch: part_o float[(n_dec * nkv * ceil(G / 16) + CTAs) * 16 * d], part_ml float[(same) * 16 * 2],
-// prefix int[n_dec + 1].
+// prefix int[n_dec + 1 + 2 * n_dec * nkv * ceil(G / 16)] (the tiles before each token, then for each
+// (kv head chunk, token) pair the CTAs with its first and its last piece).
 int attn_decode_flat(const AttnArgs& a, int n_dec, int* prefix, cudaStream_t stream) {
   GG_REQUIRE(power_of_two(a.page_size), "attn_decode: page size %d is not a power of two", a.page_size);
   GG_REQUIRE(n_dec <= FLAT_MAX_SEQS, "attn_decode: %d decoded tokens; the flat kernel takes at most %d", n_dec, FLAT_MAX_SEQS);

@@ -234,6 +234,12 @@ def attn_decode_flat_pieces(n_dec: int, nh: int, nkv: int, d: int) -> int:
     return n_dec * nkv * -(-(nh // nkv) // 16) + attn_decode_flat_ctas(d)
 
 
+def attn_decode_flat_prefix_ints(n_dec: int, nh: int, nkv: int) -> int:
+    """int32 scratch of attn_decode_flat: the tiles before each token, then for each (kv head
+    chunk, token) pair the CTAs that hold its first and last piece."""
+    return n_dec + 1 + 2 * n_dec * nkv * -(-(nh // nkv) // 16)
+
+
 def attn_decode_flat(q: torch.Tensor, q_stride: int, kcache: torch.Tensor, vcache: torch.Tensor,
                      block_tables: torch.Tensor, bt_stride: int, cu_q_lens: torch.Tensor,
                      context_lens: torch.Tensor, dec_seqs: torch.Tensor, n_dec: int,
@@ -241,16 +247,17 @@ def attn_decode_flat(q: torch.Tensor, q_stride: int, kcache: torch.Tensor, vcach
                      nh: int, nkv: int, d: int, page_size: int, window: int, scale: float) -> None:
     """Attention of single decoded tokens for large batches (bfloat16, head size 64 or 128):
     the 64-key tiles of all (token, kv head) pairs are cut into equal ranges, one per CTA,
-    and merged by a second kernel.  ``prefix``: int32 scratch of n_dec + 1."""
+    and merged by a second kernel.  ``prefix``: int32 scratch of attn_decode_flat_prefix_ints()."""
     pieces = attn_decode_flat_pieces(n_dec, nh, nkv, d)
-    if part_o.numel() < pieces * 16 * d or part_ml.numel() < pieces * 16 * 2 or prefix.numel() < n_dec + 1:
+    if part_o.numel() < pieces * 16 * d or part_ml.numel() < pieces * 16 * 2 \
+            or prefix.numel() < attn_decode_flat_prefix_ints(n_dec, nh, nkv):
         raise KernelError("attn_decode_flat: scratch too small")
     if prefix.dtype != torch.int32 or part_o.dtype != torch.float32 or part_ml.dtype != torch.float32:
         raise KernelError("attn_decode_flat: scratch of the wrong type")
     _check(lib().gg_attn_decode_flat(_p(q), ctypes.c_longlong(q_stride), _p(kcache), _p(vcache),
                                      dtype_code(kcache.dtype), _p(block_tables), bt_stride,
                                      _p(cu_q_lens), _p(context_lens), _p(dec_seqs), n_dec,
-                                     _p(part_o), _p(part_ml), _p(prefix), _p(out), nh, nkv, d, page_size,
+                                     _p(part_o), _p(part_ml), _p(prefix), prefix.numel(), _p(out), nh, nkv, d, page_size,
                                      window, ctypes.c_float(scale), _stream()), 2)
 
 

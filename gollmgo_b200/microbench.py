@@ -122,7 +122,7 @@ def attn_decode(args) -> None:
     pieces = ops.attn_decode_flat_pieces(B, nh, nkv, d)
     po = torch.empty(pieces * 16 * d, device="cuda")
     pm = torch.empty(pieces * 16 * 2, device="cuda")
-    prefix = torch.empty(B + 1, dtype=torch.int32, device="cuda")
+    prefix = torch.empty(ops.attn_decode_flat_prefix_ints(B, nh, nkv), dtype=torch.int32, device="cuda")
     t = _time(lambda i: ops.attn_decode_flat(q, q.shape[1], kc, vc, bts[i % len(bts)], stride, cu, ctxs, dec, B,
                                              po, pm, prefix, out, nh, nkv, d, page, 0, 1 / math.sqrt(d)), args.reps)
     print(f"attn_decode_flat (equal ranges of tiles) B={B} context={ctx}: {t:7.1f} us "

@@ -153,7 +153,7 @@ class Attention:
             pieces = ops.attn_decode_flat_pieces(ctx.max_seqs, self.nh, self.nkv, self.d)
             ws.reserve("attn_part_o", pieces * 16 * self.d, torch.float32)
             ws.reserve("attn_part_ml", pieces * 16 * 2, torch.float32)
-            ws.reserve("attn_flat_prefix", ctx.max_seqs + 1, torch.int32)
+            ws.reserve("attn_flat_prefix", ops.attn_decode_flat_prefix_ints(ctx.max_seqs, self.nh, self.nkv), torch.int32)
         self.w_qkv = None
         self.w_o = None
 
@@ -225,7 +225,8 @@ class Attention:
                                  batch.context_lens, batch.dec_seqs, n,
                                  ws.get("attn_part_o", 1, pieces * 16 * self.d),
                                  ws.get("attn_part_ml", 1, pieces * 16 * 2),
-                                 ws.get("attn_flat_prefix", 1, n + 1), out, self.nh, self.nkv, self.d,
+                                 ws.get("attn_flat_prefix", 1, ops.attn_decode_flat_prefix_ints(n, self.nh, self.nkv)), out,
+                                 self.nh, self.nkv, self.d,
                                  self.ctx.page_size, window, self.scale)
             return
         facts = getattr(batch, "facts", None)

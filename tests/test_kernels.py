@@ -263,7 +263,7 @@ def test_attn_decode_flat(ops, cuda_device, nh, nkv, d, page, window, many):
     pieces = ops.attn_decode_flat_pieces(n_dec, nh, nkv, d)
     part_o = torch.full((pieces * 16 * d,), float("nan"), device="cuda")
     part_ml = torch.full((pieces * 16 * 2,), float("nan"), device="cuda")
-    prefix = torch.full((n_dec + 1,), -7, dtype=torch.int32, device="cuda")
+    prefix = torch.full((ops.attn_decode_flat_prefix_ints(n_dec, nh, nkv),), -7, dtype=torch.int32, device="cuda")
     out = torch.zeros(B, nh * d, device="cuda", dtype=dtype)
     ops.attn_decode_flat(q_all, nh * d, kc, vc, bt, stride, cu, ctx_t, dec, n_dec, part_o, part_ml, prefix,
                          out, nh, nkv, d, page, window, 1 / math.sqrt(d))
