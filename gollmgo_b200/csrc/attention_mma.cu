@@ -736,7 +736,8 @@ __global__ void __launch_bounds__(MMA_THREADS) attn_prefill_mma_kernel(AttnArgs 
   constexpr int TILE_BYTES = MMA_BK * D * 2;
   constexpr int STAGES = 2;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, c2 = (lane & 3) * 2;
-  pdl_wait();
+  // the lists that say what this CTA works on were copied in before the step began: they are
+  // read while the kernel ahead (it writes the queries and the newest keys) is still finishing
   const int ps_log2 = 31 - __clz(a.page_size);
   const int b = a.tile_seq[blockIdx.x], q0 = a.tile_q0[blockIdx.x];
   const int h = blockIdx.y, kvh = h / (a.nh / a.nkv);
@@ -751,6 +752,7 @@ __global__ void __launch_bounds__(MMA_THREADS) attn_prefill_mma_kernel(AttnArgs 
   const int ntiles = (hi - kstart + MMA_BK - 1) / MMA_BK;
   const int* bt = a.block_tables + (size_t)b * a.bt_stride;
   const unsigned base = smem_u32(smem_raw);
+  pdl_wait();
 
   load_kv_tile<D>(a, bt, kvh, kstart, lo, hi, base, base + TILE_BYTES, ps_log2);
   cp_async_commit();

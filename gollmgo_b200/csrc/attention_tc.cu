@@ -105,9 +105,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
   tc_fence_after();
   const unsigned tmem_base = tmem_base_s;
   pdl_trigger();
-  pdl_wait();
 
-  // ---- what this CTA works on
+  // ---- what this CTA works on (lists copied in before the step began: read before the wait)
   // grid (heads, tiles): the heads of one tile are neighbours, and the caller lists the tiles
   // with the most keys first, so the long ones start early and the short ones fill the end
   const int b = a.tile_seq[blockIdx.y], q0 = a.tile_q0[blockIdx.y];
@@ -122,6 +121,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
   const int kstart = (lo / ATC_BK) * ATC_BK;
   const int ntiles = (hi - kstart + ATC_BK - 1) / ATC_BK;
   const int ps = a.page_size, pages_per_tile = ATC_BK / ps;
+  pdl_wait();
 
   if (warp == 0) {
     // ---------------- TMA producer: the whole warp; lane p fetches page p of a tile (two

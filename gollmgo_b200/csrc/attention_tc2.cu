@@ -124,9 +124,10 @@ attn_prefill_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
   tc_fence_after();
   const unsigned tmem_base = tmem_base_s;
   pdl_trigger();
-  pdl_wait();
 
   // ---- what this CTA works on: grid (head pairs, tiles), the tiles with the most keys first
+  // (the lists were copied in before the step began: they are read while the kernel ahead,
+  // which writes the queries and the newest keys, is still finishing)
   const int b = a.tile_seq[blockIdx.y], q0 = a.tile_q0[blockIdx.y];
   const int h0 = 2 * blockIdx.x, kvh = h0 / (a.nh / a.nkv);
   const int t0 = a.cu_q_lens[b], qlen = a.cu_q_lens[b + 1] - t0;
@@ -139,6 +140,7 @@ attn_prefill_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
   const int kstart = (lo / AT2_BK) * AT2_BK;
   const int ntiles = (hi - kstart + AT2_BK - 1) / AT2_BK;
   const int ps = a.page_size, pages_per_tile = AT2_BK / ps;
+  pdl_wait();
 
   if (warp == 0) {
     // ---------------- TMA producer

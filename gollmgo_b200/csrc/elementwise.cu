@@ -83,9 +83,21 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ resid, const TA* __restri
   extern __shared__ __align__(16) float xs[];          // H floats + 33 for the reduction
   float* red = xs + H;
   pdl_trigger();
-  pdl_wait();
   const int i = blockIdx.x;
+  // the row list was copied in before the step began and the norm's weight never changes:
+  // both are fetched while the kernel ahead is still finishing
   const int r = rows ? rows[i] : i;
+  constexpr int PRE = 4;                               // float4 of the weight a thread keeps from before the wait
+  float4 gpre[PRE];
+  const bool pre = VEC && H <= PRE * 4 * (int)blockDim.x;
+  if (pre) {
+#pragma unroll
+    for (int u = 0; u < PRE; ++u) {
+      const int c = (threadIdx.x + u * blockDim.x) * 4;
+      gpre[u] = c < H ? *reinterpret_cast<const float4*>(w + c) : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+  }
+  pdl_wait();
   float* xr = resid + (size_t)r * H;
   const TA* dr = delta ? delta + (size_t)r * H : nullptr;
   TA* o = out + (size_t)i * H;
@@ -112,7 +124,17 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ resid, const TA* __restri
   }
   const float total = block_sum(ss, red);
   const float rinv = rsqrtf(total / (float)H + eps);
-  if (VEC) {
+  if (VEC && pre) {
+#pragma unroll
+    for (int u = 0; u < PRE; ++u) {
+      const int c = (threadIdx.x + u * blockDim.x) * 4;
+      if (c < H) {
+        const float4 x = *reinterpret_cast<const float4*>(xs + c);
+        const float4 g = gpre[u];
+        Vec4<TA>::store(o + c, make_float4(x.x * rinv * g.x, x.y * rinv * g.y, x.z * rinv * g.z, x.w * rinv * g.w));
+      }
+    }
+  } else if (VEC) {
     for (int c = threadIdx.x * 4; c < H; c += blockDim.x * 4) {
       const float4 x = *reinterpret_cast<const float4*>(xs + c);
       const float4 g = *reinterpret_cast<const float4*>(w + c);

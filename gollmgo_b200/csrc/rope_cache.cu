@@ -93,9 +93,11 @@ rope_kv_write_vec_kernel(__nv_bfloat16* __restrict__ qkv, const int* __restrict_
                          int d, int page_size, int write_cache) {
   extern __shared__ float cs[];        // cos[d/2], sin[d/2]
   pdl_trigger();
-  pdl_wait();
   const int t = blockIdx.x;
   const int half = d >> 1;
+  // The token's position and cache slot were copied in before the step began and the
+  // frequencies never change: the table of cosines and sines is ready before the kernel
+  // ahead (the qkv product) has finished; only the rows of qkv have to wait for it.
   {
     const double pos = (double)positions[t];
     const double two_pi = 6.283185307179586476925286766559;
@@ -108,8 +110,9 @@ rope_kv_write_vec_kernel(__nv_bfloat16* __restrict__ qkv, const int* __restrict_
       cs[half + p] = s;
     }
   }
-  __syncthreads();
   const int slot = (write_cache && slot_mapping) ? slot_mapping[t] : -1;
+  __syncthreads();
+  pdl_wait();
   const int page = slot >= 0 ? slot / page_size : 0;
   const int off = slot >= 0 ? slot - page * page_size : 0;
   __nv_bfloat16* row = qkv + (size_t)t * (nh + 2 * nkv) * d;
