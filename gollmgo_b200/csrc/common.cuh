@@ -29,6 +29,10 @@ int gg_check_launch(const char* what);
 // kernel calls pdl_wait() before it reads anything another kernel produced and
 // before its first write, and pdl_trigger() once the grid that follows may be
 // scheduled.  Without a predecessor launched this way both are no-ops.
+// What a kernel reads BEFORE pdl_wait() must not be written by a kernel of this library that
+// is directly ahead of it: weights, and the step's packed lists (positions, cache slots, row
+// and tile lists, block tables, context lengths), which the host copies in before the step's
+// first kernel.  Launchers say so where an argument is read that early.
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 

@@ -102,7 +102,9 @@ def add_rmsnorm(resid: torch.Tensor, delta: Optional[torch.Tensor], weight: torc
                 out: torch.Tensor, eps: float, rows: Optional[torch.Tensor] = None,
                 write_back: bool = True) -> None:
     """x = resid[r] (+ delta[r]); resid[r] = x if write_back; out[i] = rmsnorm(x) * weight,
-    r = rows[i] if rows is given else i.  resid float32, weight float32, out/delta same dtype."""
+    r = rows[i] if rows is given else i.  resid float32, weight float32, out/delta same dtype.
+    ``rows`` and ``weight`` are read before the kernel ahead of this one has finished: they must
+    not be that kernel's output (the engine gives the step's packed row list)."""
     _cuda(resid, delta, weight, out, rows)
     H = resid.shape[-1]
     n = rows.numel() if rows is not None else out.shape[0]
@@ -128,7 +130,9 @@ def rope_kv_write(qkv: torch.Tensor, positions: torch.Tensor, slot_mapping: Opti
                   vcache: Optional[torch.Tensor], nh: int, nkv: int, d: int, page_size: int,
                   interleaved: bool = False, write_cache: bool = True) -> None:
     """Rotate q and k heads of qkv [T, (nh+2nkv)*d] in place and scatter k, v into the
-    paged cache [pages, nkv, page_size, d] at slot_mapping[t]."""
+    paged cache [pages, nkv, page_size, d] at slot_mapping[t].  ``positions``, ``slot_mapping``
+    and ``inv_freq`` are read before the kernel ahead of this one has finished: they must not be
+    that kernel's output (the engine gives the step's packed lists)."""
     _cuda(qkv, positions, slot_mapping, inv_freq, kcache, vcache)
     T = qkv.shape[0]
     if qkv.shape[1] != (nh + 2 * nkv) * d:
