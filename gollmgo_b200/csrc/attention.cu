@@ -16,6 +16,7 @@
 // current call's keys and masks by position alone; this one does not share those
 // two properties.
 #include "attention_common.cuh"
+#include <stdlib.h>
 
 #define ATT_BQ 16
 #define ATT_BK 64
@@ -330,7 +331,11 @@ extern "C" int gg_attn_prefill(const void* q, long long q_stride, const void* kc
   if (rc) return rc;
   if (allow_tc && tile128_seq && status && q_stride % 8 == 0) {
     a.tile_seq = tile128_seq; a.tile_q0 = tile128_q0;
-    // allow_tc: 1 = the best tcgen05 kernel for the shape, 2 = the one-head-per-CTA kernel only
+    // allow_tc: 1 = the best tcgen05 kernel for the shape, 2 = the one-head-per-CTA kernel only,
+    // 3 = two heads per CTA in steps of 64 keys (what 1 gave before there were steps of 128)
+    static const bool wide = !(getenv("GOLLMGO_B200_ATTN_STEP") && atoi(getenv("GOLLMGO_B200_ATTN_STEP")) == 64);
+    if (allow_tc == 1 && wide && attn_tc3_supported(dtype, d, page_size, nh, nkv))
+      return attn_prefill_tc3(a, num_tiles128, T, num_pages, status, stream);
     if (allow_tc != 2 && attn_tc2_supported(dtype, d, page_size, nh, nkv))
       return attn_prefill_tc2(a, num_tiles128, T, num_pages, status, stream);
     if (attn_tc_supported(dtype, d, page_size))

@@ -50,6 +50,9 @@ int attn_prefill_tc(const AttnArgs& a, int num_tiles, int T, int num_pages, int*
 // the same with two heads of one kv head per CTA (attention_tc2.cu): even groups of heads, pages of up to 64 tokens
 bool attn_tc2_supported(int dtype, int d, int page_size, int nh, int nkv);
 int attn_prefill_tc2(const AttnArgs& a, int num_tiles, int T, int num_pages, int* status, cudaStream_t stream);
+// the same in steps of 128 keys (attention_tc3.cu)
+bool attn_tc3_supported(int dtype, int d, int page_size, int nh, int nkv);
+int attn_prefill_tc3(const AttnArgs& a, int num_tiles, int T, int num_pages, int* status, cudaStream_t stream);
 
 __device__ __forceinline__ unsigned smem_u32(const void* p) {
   return (unsigned)__cvta_generic_to_shared(p);

@@ -140,7 +140,8 @@ def attn_prefill(args) -> None:
     t128 = torch.arange(0, T, 128, dtype=torch.int32, device="cuda").flip(0).contiguous()   # longest first
     out = torch.empty(T, nh * d, device="cuda", dtype=torch.bfloat16)
     flops = 2.0 * 2.0 * nh * d * T * T / 2
-    for name, tc in (("tcgen05, best for the shape", 1), ("tcgen05, one head per CTA", 2), ("mma.sync", 0)):
+    for name, tc in (("tcgen05, best for the shape", 1), ("tcgen05, two heads per CTA, steps of 64 keys", 3),
+                     ("tcgen05, one head per CTA", 2), ("mma.sync", 0)):
         if tc and d not in (64, 128):
             continue
         t = _time(lambda i: ops.attn_prefill(q, q.shape[1], kc, vc, tables[i % 4:i % 4 + 1].contiguous(), stride, cu,

@@ -348,7 +348,7 @@ def test_attn_decode_rope_refuses_what_it_cannot_do(ops, cuda_device):
                              8, 2, 80, 16, 0, 0.1, i, i, torch.ones(40, dtype=torch.float64, device="cuda"))
 
 
-@pytest.mark.parametrize("allow_mma", [False, True, "tc", "tc1"])
+@pytest.mark.parametrize("allow_mma", [False, True, "tc", "tc1", "tc2"])
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("nh,nkv,d,page,window", [
     (4, 2, 16, 16, 0), (4, 1, 32, 8, 0), (5, 5, 48, 32, 24), (32, 8, 128, 16, 0), (6, 3, 96, 16, 40),
@@ -356,13 +356,14 @@ def test_attn_decode_rope_refuses_what_it_cannot_do(ops, cuda_device):
     (8, 2, 64, 16, 0), (4, 2, 128, 64, 90), (12, 2, 64, 32, 33)])
 def test_attn_prefill(ops, cuda_device, dtype, nh, nkv, d, page, window, allow_mma):
     """Portions of several sequences in one launch: (cached before, portion length).
-    "tc": the best tcgen05 kernel for the shape (two heads of a kv head per CTA where the
-    heads come in even groups); "tc1": the tcgen05 kernel with one head per CTA."""
+    "tc": the best tcgen05 kernel for the shape (two heads of a kv head per CTA in steps of 128
+    keys where the heads come in even groups); "tc2": the same in steps of 64 keys; "tc1": the
+    tcgen05 kernel with one head per CTA."""
     if allow_mma is True and not (dtype == torch.bfloat16 and d in (64, 128)):
         pytest.skip("the mma.sync kernel takes bfloat16 with head size 64 or 128")
-    if allow_mma in ("tc", "tc1") and not (dtype == torch.bfloat16 and d in (64, 128)):
+    if allow_mma in ("tc", "tc1", "tc2") and not (dtype == torch.bfloat16 and d in (64, 128)):
         pytest.skip("the tcgen05 kernels take bfloat16 with head size 64 or 128")
-    if allow_mma == "tc1" and (nh // nkv) % 2:
+    if allow_mma in ("tc1", "tc2") and (nh // nkv) % 2:
         pytest.skip("odd groups of heads: \"tc\" already is the one-head kernel")
     torch.manual_seed(5)
     shapes = [(0, 1), (0, 2), (0, 16), (0, 17), (5, 2), (13, 40), (64, 64), (100, 33), (250, 3), (0, 130),
@@ -402,8 +403,8 @@ def test_attn_prefill(ops, cuda_device, dtype, nh, nkv, d, page, window, allow_m
     ops.attn_prefill(buf, width, kc, vc, bt, stride, cu, ctx_t, tile_seq, tile_q0, len(tiles), out,
                      nh, nkv, d, page, window, 1 / math.sqrt(d), t64_seq, t64_q0, len(tiles64),
                      allow_mma=bool(allow_mma), tile128_seq=t128_seq, tile128_q0=t128_q0,
-                     num_tiles128=len(tiles128), allow_tc={"tc": 1, "tc1": 2}.get(allow_mma, 0))
-    if allow_mma in ("tc", "tc1"):
+                     num_tiles128=len(tiles128), allow_tc={"tc": 1, "tc1": 2, "tc2": 3}.get(allow_mma, 0))
+    if allow_mma in ("tc", "tc1", "tc2"):
         ops.check_tc_status("cuda")
     torch.testing.assert_close(out.double(), torch.cat(refs).reshape(T, nh * d), **tol(dtype))
 
