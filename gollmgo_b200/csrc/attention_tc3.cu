@@ -68,6 +68,28 @@ __device__ __forceinline__ void at3_mma_ta(unsigned d_tmem, unsigned a_tmem, uns
       : "memory");
 }
 
+// Arithmetic of sm_100 that halves the softmax's instruction count: the maximum of three, and
+// two float32 operations in one instruction on a pair of registers.
+__device__ __forceinline__ float at3_max3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
+// (x0, x1) * m + c
+__device__ __forceinline__ void at3_fma2(float& r0, float& r1, float x0, float x1, float m, float c) {
+  asm("{\n\t.reg .b64 pa, pb, pc, pd;\n\t"
+      "mov.b64 pa, {%2, %3};\n\tmov.b64 pb, {%4, %4};\n\tmov.b64 pc, {%5, %5};\n\t"
+      "fma.rn.f32x2 pd, pa, pb, pc;\n\tmov.b64 {%0, %1}, pd;\n\t}"
+      : "=f"(r0), "=f"(r1) : "f"(x0), "f"(x1), "f"(m), "f"(c));
+}
+// (a0, a1) += (x0, x1)
+__device__ __forceinline__ void at3_add2(float& a0, float& a1, float x0, float x1) {
+  asm("{\n\t.reg .b64 pa, pb, pd;\n\t"
+      "mov.b64 pa, {%0, %1};\n\tmov.b64 pb, {%2, %3};\n\t"
+      "add.rn.f32x2 pd, pa, pb;\n\tmov.b64 {%0, %1}, pd;\n\t}"
+      : "+f"(a0), "+f"(a1) : "f"(x0), "f"(x1));
+}
+
 struct At3Args {
   AttnArgs a;
   int num_pages;          // pages in the cache (an index >= this is filled with zeros)
@@ -260,14 +282,16 @@ attn_prefill_tc3_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
       if (!ok) break;
       tc_fence_after();
       const bool interior = kb >= lo && kb + AT3_BK - 1 <= first && (a.window <= 0 || kb > first + nrows - 1 - a.window);
-      // the row's 128 scores, once, into registers (scaled to base 2; masked ones -inf)
+      // the row's 128 scores, once, into registers (as they come: the scale to base 2 is folded
+      // into the exponential's argument; masked ones -inf).  The four loads are in flight together.
       float sv[AT3_BK];
+      {
+        unsigned raw[AT3_BK];
 #pragma unroll
-      for (int c = 0; c < AT3_BK; c += 32) {
-        unsigned v[32];
-        tc_load32(lane_addr + c, v);
+        for (int c = 0; c < AT3_BK; c += 32) tc_load32_nowait(lane_addr + c, raw + c);
+        tc_wait_load();
 #pragma unroll
-        for (int i = 0; i < 32; ++i) sv[c + i] = __uint_as_float(v[i]) * sc;
+        for (int i = 0; i < AT3_BK; ++i) sv[i] = __uint_as_float(raw[i]);
       }
       if (!interior) {
 #pragma unroll
@@ -277,13 +301,15 @@ attn_prefill_tc3_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
           if (!keep) sv[i] = -INFINITY;
         }
       }
+      // the maximum, three at a time in four chains (a chain of 128 dependent operations would be
+      // 128 latencies long, and there is one softmax warp per scheduler at work at a time)
       float mxs[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-      for (int i = 0; i < AT3_BK; i += 4) {
+      for (int i = 0; i < AT3_BK; i += 8) {
 #pragma unroll
-        for (int u = 0; u < 4; ++u) mxs[u] = fmaxf(mxs[u], sv[i + u]);
+        for (int u = 0; u < 4; ++u) mxs[u] = at3_max3(mxs[u], sv[i + 2 * u], sv[i + 2 * u + 1]);
       }
-      const float mx = fmaxf(fmaxf(mxs[0], mxs[1]), fmaxf(mxs[2], mxs[3]));
+      const float mx = fmaxf(fmaxf(mxs[0], mxs[1]), fmaxf(mxs[2], mxs[3])) * sc;      // sc > 0
       // move the reference maximum only when some row of the warp has outgrown it by 2^8
       const bool grow = mx > m_ref + 8.f;
       const bool rescale = __any_sync(0xffffffffu, grow);
@@ -341,17 +367,19 @@ attn_prefill_tc3_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
       ok = mbar_wait(turn(t), t == 0 ? ((j & 1) ^ 1) : (j & 1)) && !*(volatile int*)&abort_s;
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
-      // p = 2^(s - m_ref), row sum, P into the first 64 columns of the score buffer
-      // (column c = keys 2c, 2c + 1 as a pair of bfloat16)
-      const float mr = m_ref == -INFINITY ? 0.f : m_ref;
+      // p = 2^(s * scale - m_ref), row sum, P into the first 64 columns of the score buffer
+      // (column c = keys 2c, 2c + 1 as a pair of bfloat16); the argument and the sum two at a time
+      const float neg_mr = m_ref == -INFINITY ? 0.f : -m_ref;
       float sums[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
       for (int c = 0; c < AT3_BK; c += 64) {
         unsigned pk[32];
 #pragma unroll
         for (int i = 0; i < 64; i += 2) {
-          const float p0 = fast_exp2(sv[c + i] - mr), p1 = fast_exp2(sv[c + i + 1] - mr);     // 2^-inf = 0
-          sums[(i >> 1) & 3] += p0 + p1;
+          float a0, a1;
+          at3_fma2(a0, a1, sv[c + i], sv[c + i + 1], sc, neg_mr);           // -inf stays -inf
+          const float p0 = fast_exp2(a0), p1 = fast_exp2(a1);               // 2^-inf = 0
+          at3_add2(sums[i & 2], sums[(i & 2) + 1], p0, p1);
           __nv_bfloat162 pr = __floats2bfloat162_rn(p0, p1);
           pk[i >> 1] = *reinterpret_cast<unsigned*>(&pr);
         }
