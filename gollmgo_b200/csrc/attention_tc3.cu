@@ -320,26 +320,18 @@ attn_prefill_tc3_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
         m_ref = m_new;
         l *= alpha;
       }
-      if (j > 0) {
-        // The product of the step before must be complete before O is rescaled.  The wait is
-        // made at every step, although only a rescale needs it: a thread may only ever be one
-        // phase behind this barrier (its parity tells two neighbouring phases apart, no more).
-        // These scores were multiplied after that product, so it costs a test.
-        ok = mbar_wait(pv_done(t), (j - 1) & 1) && !*(volatile int*)&abort_s;
-        ok = __all_sync(0xffffffffu, ok);
-        if (!ok) break;
-        tc_fence_after();
-        if (rescale) {
+      if (j > 0 && rescale) {
+        // The product of the step before is complete: these scores were multiplied after it by
+        // the same thread, and the commit behind them (s_full) covers everything it had issued.
 #pragma unroll
-          for (int c = 0; c < D; c += 32) {
-            unsigned v[32];
-            tc_load32(tmem_o + c, v);
+        for (int c = 0; c < D; c += 32) {
+          unsigned v[32];
+          tc_load32(tmem_o + c, v);
 #pragma unroll
-            for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * alpha);
-            tc_store32(tmem_o + c, v);
-          }
-          tc_wait_store();
+          for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * alpha);
+          tc_store32(tmem_o + c, v);
         }
+        tc_wait_store();
       }
       // The last page of the last tile may hold rows past the context: whatever the page's
       // owner before left there.  Their P is zero, but zero times a NaN or an infinity is not:
