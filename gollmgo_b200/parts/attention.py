@@ -26,7 +26,7 @@ from .registry import build_position, register_mixer
 # takes the sizes (tcgen05 for head sizes 64 and 128 in prompt portions, mma.sync for decode), "mma" = no tcgen05 kernel,
 # "general" = only the general kernel.
 ATTN_POLICY = os.environ.get("GOLLMGO_B200_ATTN", "auto")
-SHORT_PROMPT_KEYS = int(os.environ.get("GOLLMGO_B200_ATTN_SHORT_KEYS", "512"))   # see Attention._few_short_tiles
+SHORT_PROMPT_KEYS = int(os.environ.get("GOLLMGO_B200_ATTN_SHORT_KEYS", "256"))   # see Attention._few_short_tiles
 # Steps of decoded tokens only: rotation and cache write inside the decode attention kernel.
 FUSE_DECODE_ROPE = os.environ.get("GOLLMGO_B200_FUSE_ROPE", "1") != "0"
 # Decode steps with at least this many times more (token, kv head) pairs than CTAs fit at once
@@ -175,11 +175,10 @@ class Attention:
 
     def _few_short_tiles(self, tiles128: int, batch) -> bool:
         """Prompt portions that leave the tcgen05 kernel's tiles (128 rows of two heads) on fewer
-        than half of the SMs, with at most 512 keys each: the mma.sync kernel's tiles of 64 rows
-        of one head spread the same work over four times the CTAs and start faster.  Measured
-        inside prompt steps of the Llama-3.1-8B shape, per layer: 256 tokens 15.7 us against 23.4,
-        512 tokens 26.5 against 29.7; 1024 tokens 71.1 against 42.9, where the tcgen05 kernel
-        stays."""
+        than half of the SMs, with at most 256 keys each: the mma.sync kernel's tiles of 64 rows
+        of one head spread the same work over four times the CTAs and start faster.  Measured on
+        whole prompt steps of the Llama-3.1-8B shape (ms, tcgen05 / mma.sync): 64 tokens 4.10 /
+        3.84, 128 tokens 4.45 / 4.24, 256 tokens 5.2-5.6 / 5.3-5.4, 512 tokens 8.3-8.5 / 8.6."""
         if tiles128 * ((self.nh + 1) // 2) * 2 > self.num_sms:
             return False
         return max(s + n for s, n in zip(batch.q_starts, batch.q_lens) if n > 1) <= SHORT_PROMPT_KEYS
