@@ -353,7 +353,7 @@ def test_attn_decode_rope_refuses_what_it_cannot_do(ops, cuda_device):
 @pytest.mark.parametrize("nh,nkv,d,page,window", [
     (4, 2, 16, 16, 0), (4, 1, 32, 8, 0), (5, 5, 48, 32, 24), (32, 8, 128, 16, 0), (6, 3, 96, 16, 40),
     (6, 2, 64, 8, 0), (3, 1, 64, 32, 50), (5, 5, 128, 16, 70), (2, 1, 128, 8, 0), (4, 4, 128, 64, 130),
-    (8, 2, 64, 16, 0), (4, 2, 128, 64, 90), (12, 2, 64, 32, 33)])
+    (8, 2, 64, 16, 0), (4, 2, 128, 64, 90), (12, 2, 64, 32, 33), (16, 4, 128, 16, 0), (20, 2, 128, 128, 300)])
 def test_attn_prefill(ops, cuda_device, dtype, nh, nkv, d, page, window, allow_mma):
     """Portions of several sequences in one launch: (cached before, portion length).
     "tc": the best tcgen05 kernel for the shape (two heads of a kv head per CTA in steps of 128
