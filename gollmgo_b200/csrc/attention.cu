@@ -309,6 +309,16 @@ int attn_merge_launch(const AttnArgs& a, int dtype, int n_dec, cudaStream_t stre
   return gg_check_launch("attn_merge");
 }
 
+// Which tcgen05 prompt kernel a launch with allow_tc = 1 runs for a shape on this build and
+// device: 3 = two heads per CTA in steps of 128 keys, 2 = the same in steps of 64, 1 = one head
+// per CTA, 0 = none (the mma.sync or the general kernel).
+extern "C" int gg_attn_prefill_choice(int dtype, int d, int page_size, int nh, int nkv) {
+  static const bool wide = !(getenv("GOLLMGO_B200_ATTN_STEP") && atoi(getenv("GOLLMGO_B200_ATTN_STEP")) == 64);
+  if (wide && attn_tc3_supported(dtype, d, page_size, nh, nkv)) return 3;
+  if (attn_tc2_supported(dtype, d, page_size, nh, nkv)) return 2;
+  return attn_tc_supported(dtype, d, page_size) ? 1 : 0;
+}
+
 // Three tile lists describe the same portions cut into 16, 64 and 128 query rows, for the
 // general kernel, the mma.sync kernel and the tcgen05 kernel; the launcher picks the kernel
 // from dtype, head size and what the caller allows.  T = rows of the q buffer, num_pages =

@@ -227,6 +227,13 @@ def attn_decode_rope(qkv: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tens
 ATTN_FLAT_MAX_SEQS = 1024   # decoded tokens attn_decode_flat takes in one launch (FLAT_MAX_SEQS in attention_mma.cu)
 
 
+def attn_prefill_choice(dtype: torch.dtype, d: int, page_size: int, nh: int, nkv: int) -> int:
+    """Which tcgen05 prompt kernel attn_prefill(allow_tc=True) runs for a shape on this build and
+    device: 3 = two heads per CTA in steps of 128 keys, 2 = the same in steps of 64, 1 = one head
+    per CTA, 0 = none."""
+    return int(lib().gg_attn_prefill_choice(dtype_code(dtype), d, page_size, nh, nkv))
+
+
 def attn_decode_flat_ctas(d: int) -> int:
     """CTAs that attn_decode_flat launches for head size d (for sizing its scratch)."""
     return int(lib().gg_attn_decode_flat_ctas(d))

@@ -409,6 +409,18 @@ def test_attn_prefill(ops, cuda_device, dtype, nh, nkv, d, page, window, allow_m
     torch.testing.assert_close(out.double(), torch.cat(refs).reshape(T, nh * d), **tol(dtype))
 
 
+def test_the_prompt_kernel_in_steps_of_128_keys_is_the_one_that_runs(ops, cuda_device):
+    """It needs the register count the compiler gave the kernel to cover what its warps hand
+    back and take (a build where it does not falls back to steps of 64 keys without a word):
+    on this build it must be there, for the shapes of the benchmarks."""
+    assert ops.attn_prefill_choice(torch.bfloat16, 128, 16, 32, 8) == 3
+    assert ops.attn_prefill_choice(torch.bfloat16, 64, 16, 32, 8) == 3
+    assert ops.attn_prefill_choice(torch.bfloat16, 128, 128, 4, 2) == 3
+    assert ops.attn_prefill_choice(torch.bfloat16, 128, 16, 5, 5) == 1          # odd groups: one head per CTA
+    assert ops.attn_prefill_choice(torch.bfloat16, 96, 16, 4, 2) == 0
+    assert ops.attn_prefill_choice(torch.float32, 128, 16, 4, 2) == 0
+
+
 def test_attention_refuses_what_it_cannot_do(ops, cuda_device):
     z = torch.zeros(4, device="cuda")
     zi = torch.zeros(4, dtype=torch.int32, device="cuda")
