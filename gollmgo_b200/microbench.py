@@ -5,6 +5,7 @@ on inputs larger than L2 (a ring of weight copies, or a cache of many sequences)
     python -m gollmgo_b200.microbench gemm_tc      [--tokens 2048]
     python -m gollmgo_b200.microbench attn_decode  [--batch 64] [--context 2048]
     python -m gollmgo_b200.microbench attn_prefill [--tokens 2048]
+    python -m gollmgo_b200.microbench step_timeline [--batch 8] [--context 2048] [--prompt-tokens 0]
 
 Sizes default to the Llama-3.1-8B shape.  With ``--reps 2`` a run is short enough to
 sit under a profiler.
@@ -174,9 +175,76 @@ def sample(args) -> None:
         print(f"sample ({name}) rows={B} vocab={V}: {t:7.1f} us", flush=True)
 
 
+def step_timeline(args) -> None:
+    """Kernel timeline of one step of the whole model through CUPTI (torch.profiler): per kernel
+    name the launches of the step, their summed durations and the idle time before them.  A
+    decode step of --batch sequences at --context tokens (a captured graph for the batches the
+    engine captures), or with --tokens a prompt step of that many tokens.  With programmatic
+    dependent launch a kernel's duration includes the time it waits for the one before, so the
+    durations of neighbours overlap; the step's total is the span from first start to last end."""
+    import collections
+    import json
+    import os
+    import time
+    from torch.profiler import ProfilerActivity, profile
+    from . import Engine, EngineConfig
+    from .engine.batch import StepEntry
+    with open(os.path.join(os.path.dirname(os.path.abspath(__file__)), "bench_shapes", args.shape + ".json")) as f:
+        cfg = json.load(f)
+    B, C, T = args.batch, args.context, args.prompt_tokens
+    room = (C + 256) if not T else T + 64
+    ecfg = EngineConfig(dtype="bfloat16", block_size=args.page_size,
+                        num_blocks=(B + 1) * (-(-room // args.page_size)) + 64, max_batch_size=max(B, 8),
+                        max_token_budget=max(2048, T) + B, prefill_chunk_size=max(2048, T),
+                        max_model_len=max(room, 2048) + 64, max_queue_depth=0)
+    eng = Engine(config=cfg, weights_seed=0, engine_config=ecfg)
+    runner = eng.runner
+    gen = torch.Generator().manual_seed(1)
+    V = cfg["vocab_size"]
+    rp = lambda k: torch.randint(0, V, (k,), generator=gen).tolist()
+    if T:
+        def one(i=[0]):
+            i[0] += 1
+            rid = f"p{i[0]}"
+            runner.step([StepEntry(rid, rp(T), [T - 1])])
+            runner.release(rid)
+    else:
+        ids = [f"d{j}" for j in range(B)]
+        for rid in ids:
+            for c0 in range(0, C, 2048):
+                runner.step([StepEntry(rid, rp(min(2048, C - c0)), [])])
+        toks = rp(B)
+        out = torch.empty(B, dtype=torch.int32, device=runner.device)
+
+        def one():
+            ops.argmax(runner.step([StepEntry(rid, [toks[j]], [0]) for j, rid in enumerate(ids)]), out)
+    for _ in range(6):
+        one()
+    torch.cuda.synchronize()
+    with profile(activities=[ProfilerActivity.CUDA]) as prof:
+        one()
+        torch.cuda.synchronize()
+    ks = sorted(((e.time_range.start, e.time_range.end, e.name) for e in prof.events()
+                 if "cuda" in str(e.device_type).lower()), key=lambda k: k[0])
+    t0, prev = ks[0][0], ks[0][0]
+    agg = collections.OrderedDict()
+    for s0, e0, name in ks:
+        a = agg.setdefault(name[:72], [0, 0.0, 0.0, 0.0])       # launches, duration, idle before, time to the end before
+        a[0] += 1
+        a[1] += e0 - s0
+        a[2] += max(0.0, s0 - prev)
+        a[3] += max(0.0, e0 - max(prev, s0)) if e0 > prev else 0.0
+        prev = max(prev, e0)
+    what = f"prompt step of {T} tokens" if T else f"decode step, batch {B}, context {C}"
+    print(f"{args.shape}: {what}: {len(ks)} launches, {(ks[-1][1] - t0) / 1e3:.3f} ms from first start to last end")
+    print("launches  duration us (each)   end-to-end us (each)   idle before us   kernel")
+    for name, (n, d, g, eff) in sorted(agg.items(), key=lambda kv: -kv[1][3]):
+        print(f"{n:8d}  {d:9.1f} ({d / n:6.1f})   {eff:9.1f} ({eff / n:6.1f})   {g:8.1f}   {name}")
+
+
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(prog="python -m gollmgo_b200.microbench")
-    ap.add_argument("kernel", choices=["gemm_small_m", "gemm_tc", "attn_decode", "attn_prefill", "sample"])
+    ap.add_argument("kernel", choices=["gemm_small_m", "gemm_tc", "attn_decode", "attn_prefill", "sample", "step_timeline"])
     ap.add_argument("--tokens", type=int, default=None)
     ap.add_argument("--batch", type=int, default=64)
     ap.add_argument("--context", type=int, default=2048)
@@ -189,11 +257,13 @@ def main(argv=None) -> int:
     ap.add_argument("--kv-heads", type=int, default=8)
     ap.add_argument("--head-dim", type=int, default=128)
     ap.add_argument("--page-size", type=int, default=16)
+    ap.add_argument("--shape", default="llama_3_1_8b", help="step_timeline: a file of bench_shapes/")
+    ap.add_argument("--prompt-tokens", type=int, default=0, help="step_timeline: a prompt step of so many tokens instead of a decode step")
     args = ap.parse_args(argv)
     if args.tokens is None:
         args.tokens = 8 if args.kernel == "gemm_small_m" else 2048
     {"gemm_small_m": gemm_small_m, "gemm_tc": gemm_tc, "attn_decode": attn_decode, "attn_prefill": attn_prefill,
-     "sample": sample}[args.kernel](args)
+     "sample": sample, "step_timeline": step_timeline}[args.kernel](args)
     return 0
 
 
